@@ -1,0 +1,181 @@
+#!/usr/bin/env python
+"""Headline benchmark: dense push+pull goodput (the reference's test_kv_app_benchmark shape).
+
+Every GPU is a worker and a server shard.  One step = every worker pushes one fp32 tensor
+(values ~N(0,1)) to the key-range-sharded servers, the server handle sums the workers'
+tensors and applies SGD (lr 0.01) to its fp32 master weights, and every worker pulls the
+updated tensor.  Goodput per GPU = (bytes pushed + bytes pulled by that worker) / time;
+``value`` is the sum over all GPUs.  Per-GPU work is fixed as N grows (weak scaling).
+
+    python bench.py --gpus 1 --steps 50 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 50 --warmup 5
+
+``--impl reference`` runs the unmodified reference library (baseline/_ref) on the same
+shape through its own KVWorker/KVServer API over its ZMQ van.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "push_pull_goodput_GBps"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="pushpull", choices=["pushpull", "resnet50", "bert"])
+    ap.add_argument("--size-mb", type=float, default=256.0, help="tensor bytes per worker (MiB)")
+    ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--ctas", type=int, default=0)
+    ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--batch", type=int, default=0)
+    return ap.parse_args()
+
+
+def _dist_init(args):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def run_pushpull(args):
+    import torch
+    import torch.distributed as dist
+
+    import ps_lite_b200 as ps
+    from ps_lite_b200 import _lib, kvstore
+    from ps_lite_b200.parallel import ServerOptimizer
+    from ps_lite_b200.utils.timing import ClockSampler, max_over_ranks
+
+    rank, world, local = _dist_init(args)
+    dev = torch.device("cuda", local)
+    gdt = torch.float32 if args.dtype == "fp32" else torch.bfloat16
+    isz = 4 if args.dtype == "fp32" else 2
+    n = int(args.size_mb * (1 << 20)) // isz
+    n = max(8 * world, n // (8 * world) * (8 * world))
+    nbytes = n * isz
+    ctx = kvstore.init(heap_bytes=2 * nbytes + (64 << 20), device=dev)
+    kv = kvstore.KVStore(ctx)
+    # sum over workers + SGD lr 0.01; contiguous key ranges, one per server
+    opt = ServerOptimizer("sgd", lr=0.01, scale=1.0)
+    table = kv.declare(0, n, grad_dtype=gdt, out_dtype=gdt, optimizer=opt, num_ctas=args.ctas)
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234 + rank)
+    table.grad.copy_(torch.randn(n, device=dev, generator=g).to(gdt))
+    lib = _lib.device_lib()
+
+    # ---- device-timed: K fused push+pull rounds on resident gradients --------------------
+    for _ in range(args.warmup):
+        table.push_pull()
+    torch.cuda.synchronize()
+    ctx.host_barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ctx.host_barrier()
+    torch.cuda.synchronize()
+    launches0 = lib.psdev_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        table.push_pull()
+    e1.record()
+    torch.cuda.synchronize()
+    launches = lib.psdev_launch_count() - launches0
+    ctx.host_barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1), dev)
+    clocks = sampler.stop() if rank == 0 else None
+    table.check()
+    ms_per_step = ms / args.steps
+    per_gpu = 2.0 * nbytes / (ms_per_step * 1e-3) / 1e9
+    value = per_gpu * world
+
+    # ---- end to end: pinned host gradients in, pulled weights back to pinned host ---------
+    e2e = None
+    if not args.skip_e2e:
+        hin = torch.randn(n, dtype=torch.float32).to(gdt).pin_memory()
+        hout = torch.empty(n, dtype=gdt).pin_memory()
+        for _ in range(max(3, min(args.warmup, 5))):
+            kv.wait(kv.push_pull(0, hin, hout))
+        torch.cuda.synchronize()
+        ctx.host_barrier()
+        torch.cuda.synchronize()
+        k2 = max(3, min(args.steps, 20))
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(k2):
+            kv.wait(kv.push_pull(0, hin, hout))
+        s1.record()
+        torch.cuda.synchronize()
+        ctx.host_barrier()
+        ms2 = max_over_ranks(s0.elapsed_time(s1), dev) / k2
+        e2e = {"value": round(world * 2.0 * nbytes / (ms2 * 1e-3) / 1e9, 3), "unit": "GB/s",
+               "ms_per_step": round(ms2, 4), "steps": k2,
+               "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
+               "api": "KVStore.push_pull(pinned host tensor, out=pinned host tensor); wait(ts)"}
+
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": args.dtype, "data": "synthetic N(0,1) gradients, random-init weights",
+            "impl": "ours",
+            "config": {"model": "dense push+pull (test_kv_app_benchmark shape)",
+                       "tensor_bytes_per_worker": nbytes, "global_bytes": nbytes * world,
+                       "global_batch": world, "seq_len": n,
+                       "parallelism": f"dp{world} workers x {world} key-range server shards",
+                       "server_handle": "sum over workers + SGD lr=0.01 on fp32 master",
+                       "per_gpu_goodput_GBps": round(per_gpu, 3),
+                       "l2": "inputs larger than L2 (gradient+weight+master per step > 126 MB)"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+        }
+        print(json.dumps(out), flush=True)
+    kvstore.finalize()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    from baseline import ref_arm
+    ref_arm.main(args)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        try:
+            run_reference(args)
+        except Exception as exc:  # the arm must always answer with one JSON line
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference",
+                                  "unavailable": f"{type(exc).__name__}: {exc}"[:300]}))
+        return
+    if args.workload == "pushpull":
+        run_pushpull(args)
+    else:
+        from benchmarks import workloads
+        workloads.run(args)
+
+
+if __name__ == "__main__":
+    main()

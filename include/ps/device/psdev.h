@@ -1,0 +1,157 @@
+/*
+ * psdev: the device data plane of the parameter server (C ABI).
+ *
+ * Every process drives one GPU and plays both roles of a parameter server:
+ * it is a worker (it owns a gradient buffer and a pulled-weight buffer) and a
+ * server shard (it owns fp32 master weights and optimizer state for the key
+ * blocks whose index is congruent to its rank).  All worker-side buffers live
+ * in a "symmetric heap": an arena of identical layout on every rank, mapped
+ * into every process, so a kernel on one GPU reaches the same tensor on a peer
+ * at `peer_base[p] + offset`.
+ *
+ * The reference library moves these bytes as ZMQ/RDMA messages between
+ * processes (src/zmq_van.h:131-227, src/ibverbs_van.h:632-957) and applies the
+ * server handle on a CPU thread (include/ps/kv_app.h:440-463).  Here the
+ * transfer, the reduction over workers and the server-side update are a single
+ * kernel that loads and stores peer HBM over NVLink.
+ *
+ * All functions return 0 on success or a negative psdev error / positive
+ * cudaError_t value.  None of them synchronises the stream unless stated.
+ */
+#ifndef PS_DEVICE_PSDEV_H_
+#define PS_DEVICE_PSDEV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PSDEV_MAX_RANKS 8
+#define PSDEV_NUM_CHANNELS 64
+/* bytes reserved at the start of every heap for flags, epochs and status */
+#define PSDEV_CTRL_BYTES 65536
+#define PSDEV_IPC_HANDLE_BYTES 64
+
+/* element types of gradients (wire) and of pulled weights */
+enum { PSDEV_F32 = 0, PSDEV_BF16 = 1 };
+
+/* built-in server handles (the "request handle" of a KVServer, run on device) */
+enum {
+  PSDEV_OPT_SUM = 0,      /* store += scale * sum_w g          (KVServerDefaultHandle) */
+  PSDEV_OPT_SGD = 1,      /* w -= lr * (g + wd*w)                                       */
+  PSDEV_OPT_MOMENTUM = 2, /* m = mu*m + g + wd*w ; w -= lr*m                            */
+  PSDEV_OPT_ADAM = 3,     /* Adam / AdamW with host-computed bias corrections           */
+  PSDEV_OPT_ASSIGN = 4    /* w = scale * sum_w g   (initialisation push)                */
+};
+
+/* which halves of the round trip a launch performs */
+enum { PSDEV_OP_PUSH = 1, PSDEV_OP_PULL = 2, PSDEV_OP_PUSHPULL = 3 };
+
+/* error codes (negative); also stored in the per-channel device status word */
+enum {
+  PSDEV_OK = 0,
+  PSDEV_ERR_ARG = -1,
+  PSDEV_ERR_TIMEOUT_ENTRY = -2, /* a peer never announced its gradients   */
+  PSDEV_ERR_TIMEOUT_EXIT = -3,  /* a peer never finished reading/writing  */
+  PSDEV_ERR_UNSUPPORTED = -4,
+  PSDEV_ERR_NOMEM = -5,
+  PSDEV_ERR_TIMEOUT_PIPE = -6   /* an mbarrier wait inside a GEMM pipeline ran out */
+};
+
+/* The ranks of one job as seen from this process. */
+typedef struct {
+  int32_t rank;
+  int32_t world;
+  void* peer_base[PSDEV_MAX_RANKS]; /* heap base of every rank in this address space */
+  void* mc_base;                    /* NVLS multicast alias of the heap, or NULL       */
+} psdev_world_t;
+
+/* Hyper-parameters of the server handle; unused fields are ignored. */
+typedef struct {
+  int32_t kind;      /* PSDEV_OPT_* */
+  float scale;       /* applied to the summed gradient (1/W for averaging)        */
+  float lr;
+  float momentum;    /* MOMENTUM: mu                                               */
+  float weight_decay;
+  float beta1, beta2, eps; /* ADAM                                                 */
+  float bias1, bias2;      /* ADAM: 1-beta1^t and sqrt(1-beta2^t), from the host   */
+  int32_t decoupled_wd;    /* ADAM: 1 = AdamW                                      */
+} psdev_opt_t;
+
+/*
+ * One dense table: `n` elements, cut into blocks of `blk` elements; block j is
+ * owned by server rank j % world (blk = ceil(n/world) gives the reference's
+ * contiguous ranges, include/ps/../src/postoffice.cc:169-180; a small blk gives
+ * a block-cyclic layout that balances any sub-range).  Element i of block j is
+ * stored by its owner at state index (j / world) * blk + (i - j*blk).
+ */
+typedef struct {
+  uint64_t grad_off;   /* heap offset of the worker's gradient buffer           */
+  uint64_t weight_off; /* heap offset of the worker's pulled-weight buffer      */
+  int64_t n;
+  int64_t blk;         /* multiple of 8                                          */
+  float* master;       /* owner state, local memory: fp32 weights                */
+  float* state1;       /* momentum / Adam m, or NULL                             */
+  float* state2;       /* Adam v, or NULL                                        */
+  int32_t grad_dtype;  /* PSDEV_F32 | PSDEV_BF16                                 */
+  int32_t out_dtype;   /* dtype of the pulled-weight buffer                      */
+} psdev_table_t;
+
+/* ---- symmetric heap ------------------------------------------------------ */
+int psdev_heap_create(size_t bytes, void** base, unsigned char* ipc_handle /*64 B*/);
+int psdev_heap_open(const unsigned char* ipc_handle, void** peer_base);
+int psdev_heap_close(void* peer_base);
+int psdev_heap_destroy(void* base);
+/* Enable direct access from the current device to `peer_device` (same process). */
+int psdev_enable_peer(int peer_device);
+
+/* first-fit sub-allocator over [PSDEV_CTRL_BYTES, bytes): pure host bookkeeping,
+ * deterministic, so every rank that issues the same calls gets the same offsets */
+void* psdev_suballoc_new(size_t heap_bytes);
+void psdev_suballoc_delete(void* sa);
+int64_t psdev_suballoc_alloc(void* sa, size_t bytes, size_t align); /* <0: no room */
+int psdev_suballoc_free(void* sa, int64_t offset);
+size_t psdev_suballoc_in_use(void* sa);
+
+/* ---- channel state ------------------------------------------------------- */
+/* Reads (synchronously) the status word and epoch of a channel of the local heap. */
+int psdev_channel_status(void* local_base, int channel, int32_t* status, uint64_t* epoch);
+/* Clears status (not the epoch) of a channel after an error was handled. */
+int psdev_channel_clear(void* local_base, int channel);
+
+/* ---- dense push / pull --------------------------------------------------- */
+/*
+ * Runs `op` on elements [begin, end) of table `t` (both multiples of 8).
+ *   PUSH     : each owner sums the workers' gradients of its blocks over NVLink,
+ *              applies the handle to master/state.
+ *   PULL     : each owner casts its master blocks and stores them into every
+ *              worker's weight buffer.
+ *   PUSHPULL : both in one pass; the summed gradient never touches memory.
+ * `sync` != 0: ranks rendezvous through epoch flags in the heap on `channel`
+ * (every rank must issue the same sequence of calls per channel).  `sync` == 0:
+ * no flags are touched (used when the caller has already ordered the ranks, and
+ * to run all ranks' roles back to back on one GPU).
+ * `timeout_ns` bounds every flag wait; on expiry the kernel records an error in
+ * the channel status and returns without touching the data.
+ */
+int psdev_dense_op(const psdev_world_t* w, const psdev_table_t* t, int op,
+                   int64_t begin, int64_t end, const psdev_opt_t* opt,
+                   int channel, int num_ctas, uint64_t timeout_ns, int sync,
+                   void* stream);
+
+/* Number of kernels this library has launched in this process (for reporting). */
+uint64_t psdev_launch_count(void);
+
+/* Flag-only rendezvous of all ranks on a channel (device barrier). */
+int psdev_device_barrier(const psdev_world_t* w, int channel, uint64_t timeout_ns,
+                         void* stream);
+
+/* Peer bandwidth probe: copies `bytes` from `src` to `dst` with 16 B accesses. */
+int psdev_copy_probe(void* dst, const void* src, size_t bytes, int num_ctas, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PS_DEVICE_PSDEV_H_ */

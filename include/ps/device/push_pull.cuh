@@ -1,0 +1,304 @@
+// Fused dense push / pull kernel template.
+//
+// One launch per rank.  The rank acts as the server of the key blocks it owns inside the
+// requested element range: for each 16-byte vector it
+//   (push)  loads the vector from every worker's gradient buffer (its own HBM and up to
+//           seven peers over NVLink), sums in fp32 in rank order, scales, and applies the
+//           server handle `Opt` to its fp32 master weights and optimizer state;
+//   (pull)  casts the new weights and stores them into every worker's weight buffer.
+// The summed gradient is never written to memory, and there is no message, no staging
+// buffer and no library collective: the reduce-scatter and the all-gather are the loads
+// and stores of this kernel.
+//
+// This replaces the reference's push path (KVWorker::Send slicing + van transfer,
+// include/ps/kv_app.h:574-613, and the CPU server handle, :440-463) and its pull path
+// (server response + worker-side sort/memcpy reassembly, :616-717).
+//
+// A user-defined server handle is any struct with the static interface of the Opt*
+// structs below; instantiate `dense_kernel<GT, OT, MyOpt, true, true>` in your own .cu.
+#pragma once
+#include "ps/device/dev_common.cuh"
+
+namespace psdev {
+
+constexpr int kDenseThreads = 512;
+constexpr int kDenseTile = 8192;  // elements per work item
+
+struct DenseArgs {
+  void* base[PSDEV_MAX_RANKS];
+  int rank, world;
+  unsigned long long grad_off, weight_off;
+  long long blk, begin, end;
+  long long first_owned;  // first block index owned by this rank that meets [begin,end)
+  long long n_owned;      // how many owned blocks meet the range
+  long long tiles_per_blk;
+  float* master;
+  float* s1;
+  float* s2;
+  psdev_opt_t opt;
+  int channel, sync;
+  unsigned long long timeout_ns;
+};
+
+// ---- server handles ---------------------------------------------------------------
+// apply(w, g, s1, s2, o): g is the scaled sum over workers; w, s1, s2 are updated in place.
+struct OptSum {
+  static constexpr int kStates = 0;
+  __device__ static __forceinline__ void apply(float& w, float g, float&, float&,
+                                               const psdev_opt_t&) {
+    w += g;
+  }
+};
+struct OptAssign {
+  static constexpr int kStates = 0;
+  __device__ static __forceinline__ void apply(float& w, float g, float&, float&,
+                                               const psdev_opt_t&) {
+    w = g;
+  }
+};
+struct OptSgd {
+  static constexpr int kStates = 0;
+  __device__ static __forceinline__ void apply(float& w, float g, float&, float&,
+                                               const psdev_opt_t& o) {
+    g = fmaf(o.weight_decay, w, g);
+    w = fmaf(-o.lr, g, w);
+  }
+};
+struct OptMomentum {
+  static constexpr int kStates = 1;
+  __device__ static __forceinline__ void apply(float& w, float g, float& m, float&,
+                                               const psdev_opt_t& o) {
+    g = fmaf(o.weight_decay, w, g);
+    m = fmaf(o.momentum, m, g);
+    w = fmaf(-o.lr, m, w);
+  }
+};
+struct OptAdam {
+  static constexpr int kStates = 2;
+  __device__ static __forceinline__ void apply(float& w, float g, float& m, float& v,
+                                               const psdev_opt_t& o) {
+    if (o.decoupled_wd) {
+      w *= (1.f - o.lr * o.weight_decay);
+    } else {
+      g = fmaf(o.weight_decay, w, g);
+    }
+    m = fmaf(o.beta1, m, (1.f - o.beta1) * g);
+    v = fmaf(o.beta2, v, (1.f - o.beta2) * g * g);
+    const float denom = sqrtf(v) / o.bias2 + o.eps;
+    w -= (o.lr / o.bias1) * (m / denom);
+  }
+};
+
+// ---- vector helpers -----------------------------------------------------------------
+template <typename T>
+struct VecOf;
+template <>
+struct VecOf<float> {
+  static constexpr int kPer16 = 4;
+  __device__ static __forceinline__ void unpack(const uint4& u, float* f) {
+    f[0] = __uint_as_float(u.x);
+    f[1] = __uint_as_float(u.y);
+    f[2] = __uint_as_float(u.z);
+    f[3] = __uint_as_float(u.w);
+  }
+};
+template <>
+struct VecOf<__nv_bfloat16> {
+  static constexpr int kPer16 = 8;
+  __device__ static __forceinline__ void unpack(const uint4& u, float* f) {
+    float2 a = bf16x2_to_f2(u.x), b = bf16x2_to_f2(u.y), c = bf16x2_to_f2(u.z),
+           d = bf16x2_to_f2(u.w);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+    f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+  }
+};
+
+template <typename OT, int VEC>
+__device__ __forceinline__ void store_out(OT* dst, const float* w) {
+  if constexpr (sizeof(OT) == 4) {
+#pragma unroll
+    for (int q = 0; q < VEC / 4; ++q) {
+      uint4 u = make_uint4(__float_as_uint(w[4 * q]), __float_as_uint(w[4 * q + 1]),
+                           __float_as_uint(w[4 * q + 2]), __float_as_uint(w[4 * q + 3]));
+      st_v4(dst + 4 * q, u);
+    }
+  } else {
+    if constexpr (VEC == 8) {
+      uint4 u = make_uint4(f2_to_bf16x2(w[0], w[1]), f2_to_bf16x2(w[2], w[3]),
+                           f2_to_bf16x2(w[4], w[5]), f2_to_bf16x2(w[6], w[7]));
+      st_v4(dst, u);
+    } else {
+      uint2 u = make_uint2(f2_to_bf16x2(w[0], w[1]), f2_to_bf16x2(w[2], w[3]));
+      st_v2(dst, u);
+    }
+  }
+}
+
+template <int VEC>
+__device__ __forceinline__ void load_f32(const float* p, float* f) {
+#pragma unroll
+  for (int q = 0; q < VEC / 4; ++q) {
+    float4 v = *reinterpret_cast<const float4*>(p + 4 * q);
+    f[4 * q] = v.x; f[4 * q + 1] = v.y; f[4 * q + 2] = v.z; f[4 * q + 3] = v.w;
+  }
+}
+template <int VEC>
+__device__ __forceinline__ void store_f32(float* p, const float* f) {
+#pragma unroll
+  for (int q = 0; q < VEC / 4; ++q)
+    *reinterpret_cast<float4*>(p + 4 * q) =
+        make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+}
+
+// ---- rendezvous ---------------------------------------------------------------------
+// Entry: announce "my gradients of this epoch are in place and my weight buffer may be
+// overwritten", then wait for the same announcement from every rank.  Returns the epoch,
+// or 0 after a timeout (the channel status then holds the error).
+__device__ __forceinline__ unsigned long long channel_enter(void* const* base, int rank,
+                                                            int world, int channel,
+                                                            unsigned long long timeout_ns,
+                                                            unsigned long long* s_epoch,
+                                                            int* s_err) {
+  Ctrl* my = ctrl_of(base[rank]);
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    *s_epoch = ld_volatile_u64(&my->epoch[channel]) + 1ull;
+    *s_err = 0;
+  }
+  __syncthreads();
+  const unsigned long long e = *s_epoch;
+  if (blockIdx.x == 0 && tid < world) {
+    __threadfence_system();
+    st_release_sys(&ctrl_of(base[tid])->flag_in[channel][rank], e);
+  }
+  if (tid < world) {
+    if (!wait_flag_ge(&my->flag_in[channel][tid], e, timeout_ns)) {
+      atomicOr(&my->late_mask[channel], 1u << tid);
+      atomicMin(&my->status[channel], (int)PSDEV_ERR_TIMEOUT_ENTRY);
+      *s_err = 1;
+    }
+  }
+  __syncthreads();
+  return *s_err ? 0ull : e;
+}
+
+// Exit: the last CTA of the grid tells every rank "I no longer read your gradients and
+// my stores into your weight buffer are complete", waits for the same from everyone, and
+// advances the local epoch.
+__device__ __forceinline__ void channel_leave(void* const* base, int rank, int world,
+                                              int channel, unsigned long long e,
+                                              unsigned long long timeout_ns, int* s_last) {
+  Ctrl* my = ctrl_of(base[rank]);
+  const int tid = threadIdx.x;
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();
+    *s_last = (atomicAdd(&my->done[channel], 1u) == gridDim.x - 1);
+  }
+  __syncthreads();
+  if (!*s_last) return;
+  __threadfence();
+  const bool healthy = (e != 0ull) && (*(volatile int*)&my->status[channel] == 0);
+  if (healthy && tid < world) {
+    st_release_sys(&ctrl_of(base[tid])->flag_out[channel][rank], e);
+    if (!wait_flag_ge(&my->flag_out[channel][tid], e, timeout_ns)) {
+      atomicOr(&my->late_mask[channel], 1u << tid);
+      atomicMin(&my->status[channel], (int)PSDEV_ERR_TIMEOUT_EXIT);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    my->done[channel] = 0;
+    if (e != 0ull) my->epoch[channel] = e;
+    __threadfence();
+  }
+}
+
+// ---- the kernel -----------------------------------------------------------------------
+template <typename GT, typename OT, class Opt, bool REDUCE, bool BCAST>
+__global__ void __launch_bounds__(kDenseThreads)
+    dense_kernel(const __grid_constant__ DenseArgs a) {
+  constexpr int VEC = REDUCE ? VecOf<GT>::kPer16 : (sizeof(OT) == 2 ? 8 : 4);
+  __shared__ unsigned long long s_epoch;
+  __shared__ int s_err, s_last;
+  const int W = a.world, R = a.rank;
+  unsigned long long e = 1;
+  if (a.sync) {
+    e = channel_enter(a.base, R, W, a.channel, a.timeout_ns, &s_epoch, &s_err);
+  }
+  if (e != 0ull && a.n_owned > 0) {
+    const long long ntiles = a.n_owned * a.tiles_per_blk;
+    for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+      const long long k = t / a.tiles_per_blk;
+      const long long sub = t - k * a.tiles_per_blk;
+      const long long j = a.first_owned + k * W;  // global block index
+      const long long blk_lo = j * a.blk;
+      long long lo = blk_lo + sub * kDenseTile;
+      long long hi = lo + kDenseTile;
+      const long long blk_hi = blk_lo + a.blk;
+      if (hi > blk_hi) hi = blk_hi;
+      if (lo < a.begin) lo = a.begin;
+      if (hi > a.end) hi = a.end;
+      const long long st_base = (j / W) * a.blk - blk_lo;  // state index = st_base + i
+      for (long long i = lo + (long long)threadIdx.x * VEC; i < hi;
+           i += (long long)kDenseThreads * VEC) {
+        float w[VEC], m[VEC], v[VEC];
+        const long long si = st_base + i;
+        if constexpr (REDUCE) {
+          uint4 gv[PSDEV_MAX_RANKS];
+#pragma unroll
+          for (int p = 0; p < PSDEV_MAX_RANKS; ++p) {
+            if (p < W) {
+              const GT* src = reinterpret_cast<const GT*>(
+                                  reinterpret_cast<const char*>(a.base[p]) + a.grad_off) + i;
+              gv[p] = ld_sys_v4(src);
+            }
+          }
+          load_f32<VEC>(a.master + si, w);
+          if constexpr (Opt::kStates >= 1) load_f32<VEC>(a.s1 + si, m);
+          if constexpr (Opt::kStates >= 2) load_f32<VEC>(a.s2 + si, v);
+          float g[VEC];
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) g[q] = 0.f;
+#pragma unroll
+          for (int p = 0; p < PSDEV_MAX_RANKS; ++p) {
+            if (p < W) {
+              float f[VEC];
+              VecOf<GT>::unpack(gv[p], f);
+#pragma unroll
+              for (int q = 0; q < VEC; ++q) g[q] += f[q];
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < VEC; ++q) {
+            float mm = Opt::kStates >= 1 ? m[q] : 0.f;
+            float vv = Opt::kStates >= 2 ? v[q] : 0.f;
+            Opt::apply(w[q], g[q] * a.opt.scale, mm, vv, a.opt);
+            if (Opt::kStates >= 1) m[q] = mm;
+            if (Opt::kStates >= 2) v[q] = vv;
+          }
+          store_f32<VEC>(a.master + si, w);
+          if constexpr (Opt::kStates >= 1) store_f32<VEC>(a.s1 + si, m);
+          if constexpr (Opt::kStates >= 2) store_f32<VEC>(a.s2 + si, v);
+        } else {
+          load_f32<VEC>(a.master + si, w);
+        }
+        if constexpr (BCAST) {
+#pragma unroll
+          for (int pp = 0; pp < PSDEV_MAX_RANKS; ++pp) {
+            if (pp < W) {
+              int p = R + pp;
+              if (p >= W) p -= W;
+              OT* dst = reinterpret_cast<OT*>(reinterpret_cast<char*>(a.base[p]) +
+                                              a.weight_off) + i;
+              store_out<OT, VEC>(dst, w);
+            }
+          }
+        }
+      }
+    }
+  }
+  if (a.sync) channel_leave(a.base, R, W, a.channel, e, a.timeout_ns, &s_last);
+}
+
+}  // namespace psdev

@@ -1,0 +1,1 @@
+"""models of ps_lite_b200."""

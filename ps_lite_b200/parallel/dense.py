@@ -1,0 +1,169 @@
+"""Dense key-value tables on the device data plane.
+
+A :class:`DenseTable` is the device form of a set of ``(key -> fixed-length value)`` pairs
+pushed and pulled by every worker (reference: ``KVWorker::ZPush/ZPull/ZPushPull``,
+include/ps/kv_app.h:243-306, with the values of key block ``j`` owned by server
+``j % num_servers``; the reference's uniform contiguous ranges, src/postoffice.cc:169-180,
+are the special case ``blk = ceil(n / num_servers)``).
+
+Worker side (in the symmetric heap, same offset on every rank): ``grad`` and ``weight``.
+Server side (local memory): fp32 ``master`` and optimizer state for the owned blocks.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+import math
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .heap import SymmetricHeap
+
+_DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+
+
+@dataclasses.dataclass
+class ServerOptimizer:
+    """Server-side request handle applied to pushed gradients (fused into the push kernel).
+
+    ``kind``: ``"sum"`` (the reference's ``KVServerDefaultHandle``: ``store += val``,
+    include/ps/kv_app.h:440-463), ``"assign"``, ``"sgd"``, ``"momentum"``, ``"adam"``,
+    ``"adamw"``.
+    """
+    kind: str = "sum"
+    lr: float = 0.01
+    momentum: float = 0.9
+    weight_decay: float = 0.0
+    beta1: float = 0.9
+    beta2: float = 0.999
+    eps: float = 1e-8
+    scale: float = 1.0  # multiplies the sum over workers (use 1/world to average)
+
+    _KINDS = {"sum": _lib.OPT_SUM, "assign": _lib.OPT_ASSIGN, "sgd": _lib.OPT_SGD,
+              "momentum": _lib.OPT_MOMENTUM, "adam": _lib.OPT_ADAM, "adamw": _lib.OPT_ADAM}
+
+    @property
+    def num_states(self) -> int:
+        return {"momentum": 1, "adam": 2, "adamw": 2}.get(self.kind, 0)
+
+    def to_struct(self, step: int = 1) -> _lib.Opt:
+        o = _lib.Opt()
+        o.kind = self._KINDS[self.kind]
+        o.scale, o.lr, o.momentum, o.weight_decay = self.scale, self.lr, self.momentum, self.weight_decay
+        o.beta1, o.beta2, o.eps = self.beta1, self.beta2, self.eps
+        o.bias1 = 1.0 - self.beta1 ** step
+        o.bias2 = math.sqrt(1.0 - self.beta2 ** step)
+        o.decoupled_wd = 1 if self.kind == "adamw" else 0
+        return o
+
+
+def default_timeout_s() -> float:
+    import os
+    return float(os.environ.get("PSB200_DEVICE_TIMEOUT_S", "20"))
+
+
+class DenseTable:
+    """``n`` values sharded block-cyclically over the ranks of ``heap``.
+
+    Every rank must construct its tables in the same order with the same arguments.
+    """
+
+    def __init__(self, heap: SymmetricHeap, n: int, grad_dtype=torch.float32,
+                 out_dtype=torch.float32, blk: Optional[int] = None,
+                 optimizer: Optional[ServerOptimizer] = None, channel: int = 0,
+                 num_ctas: int = 0):
+        self.heap = heap
+        W = heap.world
+        self.n_user = int(n)
+        self.n = (int(n) + 7) & ~7
+        if blk is None:  # contiguous ranges, one per server
+            blk = (self.n + W - 1) // W
+        self.blk = max(8, (int(blk) + 7) & ~7)
+        self.nblocks = (self.n + self.blk - 1) // self.blk
+        self.local_blocks = (self.nblocks + W - 1) // W
+        self.local_len = self.local_blocks * self.blk
+        self.grad_dtype, self.out_dtype = grad_dtype, out_dtype
+        self.optimizer = optimizer or ServerOptimizer("sum")
+        self.channel, self.num_ctas = int(channel), int(num_ctas)
+        self.step = 0
+        gsz = torch.empty((), dtype=grad_dtype).element_size()
+        osz = torch.empty((), dtype=out_dtype).element_size()
+        self.grad_off = heap.alloc(self.n * gsz)
+        self.weight_off = heap.alloc(self.n * osz)
+        self.grad = heap.tensor(self.grad_off, self.n, grad_dtype)
+        self.weight = heap.tensor(self.weight_off, self.n, out_dtype)
+        dev = heap.device
+        self.master = torch.zeros(self.local_len, dtype=torch.float32, device=dev)
+        ns = self.optimizer.num_states
+        self.state1 = torch.zeros(self.local_len, dtype=torch.float32, device=dev) if ns >= 1 else None
+        self.state2 = torch.zeros(self.local_len, dtype=torch.float32, device=dev) if ns >= 2 else None
+        self._world = heap.world_struct()
+        self._table = _lib.Table()
+        t = self._table
+        t.grad_off, t.weight_off, t.n, t.blk = self.grad_off, self.weight_off, self.n, self.blk
+        t.master = self.master.data_ptr()
+        t.state1 = self.state1.data_ptr() if self.state1 is not None else None
+        t.state2 = self.state2.data_ptr() if self.state2 is not None else None
+        t.grad_dtype, t.out_dtype = _DT[grad_dtype], _DT[out_dtype]
+        self.grad.zero_()
+        self.weight.zero_()
+
+    # -- ownership helpers (host math mirrored by the kernels) ------------------------------
+    def owner_of(self, i: int) -> int:
+        return (i // self.blk) % self.heap.world
+
+    def owned_index(self) -> torch.Tensor:
+        """Global element indices of the values this rank owns, in state order."""
+        W, R = self.heap.world, self.heap.rank
+        blocks = torch.arange(R, self.nblocks, W, device=self.heap.device)
+        idx = blocks[:, None] * self.blk + torch.arange(self.blk, device=self.heap.device)[None, :]
+        return idx.reshape(-1)
+
+    def load_master(self, full: torch.Tensor) -> None:
+        """Initialise the owned part of the master weights from a full fp32 vector."""
+        idx = self.owned_index()
+        valid = idx < min(self.n_user, full.numel())
+        flat = full.reshape(-1).to(self.heap.device, torch.float32)
+        self.master.zero_()
+        self.master[: idx.numel()][valid] = flat[idx[valid]]
+
+    def gather_master(self, out: torch.Tensor) -> None:
+        """Scatter the owned master values into a full-size fp32 vector (others untouched)."""
+        idx = self.owned_index()
+        valid = idx < min(self.n_user, out.numel())
+        out.reshape(-1)[idx[valid]] = self.master[: idx.numel()][valid]
+
+    # -- operations ---------------------------------------------------------------------------
+    def _run(self, op: int, begin: int, end: Optional[int], sync: bool,
+             stream: Optional[torch.cuda.Stream], timeout_s: Optional[float], opt_step: bool):
+        end = self.n if end is None else end
+        if op & _lib.OP_PUSH and opt_step:
+            self.step += 1
+        o = self.optimizer.to_struct(max(self.step, 1))
+        s = stream or torch.cuda.current_stream(self.heap.device)
+        tmo = int((timeout_s if timeout_s is not None else default_timeout_s()) * 1e9)
+        rc = self.heap.lib.psdev_dense_op(C.byref(self._world), C.byref(self._table), op,
+                                          int(begin), int(end), C.byref(o), self.channel,
+                                          self.num_ctas, tmo, 1 if sync else 0, s.cuda_stream)
+        _lib.check(rc, "psdev_dense_op")
+
+    def push(self, begin: int = 0, end: Optional[int] = None, *, sync: bool = True, stream=None,
+             timeout_s=None, opt_step: bool = True) -> None:
+        """Reduce every worker's ``grad[begin:end]`` into the owners and apply the handle."""
+        self._run(_lib.OP_PUSH, begin, end, sync, stream, timeout_s, opt_step)
+
+    def pull(self, begin: int = 0, end: Optional[int] = None, *, sync: bool = True, stream=None,
+             timeout_s=None) -> None:
+        """Owners store ``master[begin:end]`` into every worker's ``weight`` buffer."""
+        self._run(_lib.OP_PULL, begin, end, sync, stream, timeout_s, False)
+
+    def push_pull(self, begin: int = 0, end: Optional[int] = None, *, sync: bool = True,
+                  stream=None, timeout_s=None, opt_step: bool = True) -> None:
+        """Push and pull in one kernel pass (``ZPushPull``, include/ps/kv_app.h:290-306)."""
+        self._run(_lib.OP_PUSHPULL, begin, end, sync, stream, timeout_s, opt_step)
+
+    def check(self) -> None:
+        """Raise if a device wait on this table's channel ran out."""
+        self.heap.check_channel(self.channel)

@@ -1,0 +1,174 @@
+"""Symmetric device heap shared by the ranks of one box.
+
+Each rank allocates an arena of the same size, exports it, and maps every peer's arena.
+Buffers are carved out with a deterministic first-fit allocator, so the same sequence of
+``alloc`` calls yields the same offsets on every rank and a kernel can address a peer's
+copy of a tensor as ``peer_base[p] + offset``.
+
+This is the device counterpart of the reference's registered memory pool and address
+exchange for RDMA (src/ibverbs_van.h:86-214 ``SimpleMempool``; :632-724 rendezvous).
+Handles travel through ``torch.distributed`` (any backend) when a process group is
+given, or through a caller-supplied ``exchange`` callable (for example the control plane
+of the host runtime).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Callable, Optional, Sequence
+
+import torch
+
+from .. import _lib
+
+
+class _RawCuda:
+    """Adapter exposing a raw device range through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int, keepalive=None):
+        self.__cuda_array_interface__ = {
+            "shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False), "version": 2,
+        }
+        self._keepalive = keepalive
+
+
+def tensor_from_ptr(ptr: int, nbytes: int, device: torch.device, keepalive=None) -> torch.Tensor:
+    """A uint8 tensor aliasing ``nbytes`` of device memory at ``ptr`` (no copy)."""
+    return torch.as_tensor(_RawCuda(ptr, nbytes, keepalive), device=device)
+
+
+class SymmetricHeap:
+    """One rank's view of the job-wide symmetric heap."""
+
+    def __init__(self, nbytes: int, rank: int = 0, world: int = 1, group=None,
+                 device: Optional[torch.device] = None,
+                 exchange: Optional[Callable[[bytes], Sequence[bytes]]] = None,
+                 _bases: Optional[Sequence[int]] = None, _owner: bool = True):
+        if world < 1 or world > _lib.MAX_RANKS:
+            raise ValueError(f"world must be in [1, {_lib.MAX_RANKS}]")
+        self.lib = _lib.device_lib()
+        self.rank, self.world = int(rank), int(world)
+        self.device = torch.device(device) if device is not None else torch.device(
+            "cuda", torch.cuda.current_device())
+        self.nbytes = int(nbytes) & ~255
+        self._owner = _owner
+        self._opened: list[int] = []
+        self._sub = self.lib.psdev_suballoc_new(self.nbytes)
+        self._siblings: list["SymmetricHeap"] = []
+        if _bases is not None:  # view created by `emulated`
+            self.bases = list(_bases)
+            self._base = self.bases[self.rank]
+            return
+        with torch.cuda.device(self.device):
+            base = C.c_void_p()
+            handle = C.create_string_buffer(_lib.IPC_HANDLE_BYTES)
+            _lib.check(self.lib.psdev_heap_create(self.nbytes, C.byref(base), handle),
+                       "psdev_heap_create")
+            self._base = base.value
+            self.bases = [0] * world
+            self.bases[rank] = self._base
+            if world > 1:
+                mine = bytes(handle.raw)
+                if exchange is not None:
+                    handles = list(exchange(mine))
+                else:
+                    import torch.distributed as dist
+                    handles = [None] * world
+                    dist.all_gather_object(handles, mine, group=group)
+                for p, h in enumerate(handles):
+                    if p == rank:
+                        continue
+                    ptr = C.c_void_p()
+                    _lib.check(self.lib.psdev_heap_open(h, C.byref(ptr)), f"psdev_heap_open({p})")
+                    self.bases[p] = ptr.value
+                    self._opened.append(ptr.value)
+
+    # -- single-GPU emulation of a multi-rank job --------------------------------------
+    @classmethod
+    def emulated(cls, nbytes: int, world: int, device=None) -> list["SymmetricHeap"]:
+        """``world`` heaps on one GPU in one process; element r is rank r's view.
+
+        Kernels that rendezvous must not be launched on these views (all "ranks" share a
+        GPU); they are for running every rank's role back to back with ``sync=False``.
+        """
+        dev = torch.device(device) if device is not None else torch.device(
+            "cuda", torch.cuda.current_device())
+        owners = [cls(nbytes, 0, 1, device=dev) for _ in range(world)]
+        bases = [h._base for h in owners]
+        views = [cls(nbytes, r, world, device=dev, _bases=bases, _owner=False)
+                 for r in range(world)]
+        for v in views:
+            v._siblings = owners  # keep the allocations alive
+        return views
+
+    # -- allocation ------------------------------------------------------------------------
+    def alloc(self, nbytes: int, align: int = 256) -> int:
+        off = self.lib.psdev_suballoc_alloc(self._sub, int(nbytes), int(align))
+        if off < 0:
+            raise _lib.PsdevError(int(off), f"symmetric heap alloc of {nbytes} bytes")
+        return int(off)
+
+    def free(self, offset: int) -> None:
+        _lib.check(self.lib.psdev_suballoc_free(self._sub, int(offset)), "suballoc_free")
+
+    @property
+    def in_use(self) -> int:
+        return int(self.lib.psdev_suballoc_in_use(self._sub))
+
+    def tensor(self, offset: int, numel: int, dtype: torch.dtype, rank: Optional[int] = None
+               ) -> torch.Tensor:
+        """Typed view of ``numel`` elements at ``offset`` in rank ``rank``'s arena."""
+        r = self.rank if rank is None else rank
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        if offset < 0 or offset + nbytes > self.nbytes:
+            raise ValueError("view outside the heap")
+        raw = tensor_from_ptr(self.bases[r] + offset, nbytes, self.device, keepalive=self)
+        return raw.view(dtype)
+
+    def world_struct(self) -> _lib.World:
+        w = _lib.World()
+        w.rank, w.world = self.rank, self.world
+        for p in range(self.world):
+            w.peer_base[p] = self.bases[p]
+        w.mc_base = None
+        return w
+
+    # -- channel state -----------------------------------------------------------------------
+    def channel_status(self, channel: int) -> tuple[int, int]:
+        """(status, epoch) of a channel; synchronises the device."""
+        st, ep = C.c_int32(), C.c_uint64()
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.psdev_channel_status(self._base, channel, C.byref(st),
+                                                     C.byref(ep)), "channel_status")
+        return st.value, ep.value
+
+    def check_channel(self, channel: int) -> None:
+        st, _ = self.channel_status(channel)
+        if st != 0:
+            raise _lib.PsdevError(st, f"device channel {channel} on rank {self.rank}")
+
+    def clear_channel(self, channel: int) -> None:
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.psdev_channel_clear(self._base, channel), "channel_clear")
+
+    def barrier(self, channel: int = _lib.NUM_CHANNELS - 1, timeout_s: float = 20.0,
+                stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Device-side barrier of all ranks (flag exchange in peer memory)."""
+        s = stream or torch.cuda.current_stream(self.device)
+        w = self.world_struct()
+        _lib.check(self.lib.psdev_device_barrier(C.byref(w), channel, int(timeout_s * 1e9),
+                                                 s.cuda_stream), "device_barrier")
+
+    def close(self) -> None:
+        if self._sub:
+            self.lib.psdev_suballoc_delete(self._sub)
+            self._sub = None
+        if not self._owner:
+            return
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for p in self._opened:
+                self.lib.psdev_heap_close(p)
+            self._opened = []
+            if self._base:
+                self.lib.psdev_heap_destroy(self._base)
+                self._base = 0

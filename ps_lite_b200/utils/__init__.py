@@ -1,0 +1,1 @@
+"""utils of ps_lite_b200."""

@@ -1,0 +1,143 @@
+"""Fused dense push/pull kernel against a plain PyTorch fp32 statement of the same update."""
+import itertools
+
+import pytest
+import torch
+
+from ps_lite_b200.utils.oracle import dense_update
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk_tables(world, n, gdt, odt, blk, opt, dev):
+    from ps_lite_b200.parallel import DenseTable, SymmetricHeap
+    nbytes = 65536 + 4 * (n + 64) * 8 + (1 << 20)
+    if world == 1:
+        heaps = [SymmetricHeap(nbytes, 0, 1, device=dev)]
+    else:
+        heaps = SymmetricHeap.emulated(nbytes, world, device=dev)
+    tables = [DenseTable(h, n, gdt, odt, blk=blk, optimizer=opt) for h in heaps]
+    return heaps, tables
+
+
+def _tol(gdt, odt):
+    if odt == torch.bfloat16:
+        return dict(rtol=1e-2, atol=1e-2)
+    return dict(rtol=2e-5, atol=2e-5)
+
+
+@pytest.mark.parametrize("kind", ["sum", "sgd", "momentum", "adam", "adamw"])
+@pytest.mark.parametrize("gdt,odt", [(torch.float32, torch.float32),
+                                     (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32),
+                                     (torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("world,n,blk", [(1, 100_000, None), (4, 70_000, 1024),
+                                         (8, 33_333, None), (8, 262_144 + 8, 4096)])
+def test_push_pull_matches_oracle(cuda_device, kind, gdt, odt, world, n, blk):
+    from ps_lite_b200.parallel import ServerOptimizer
+    torch.manual_seed(1234)
+    opt = ServerOptimizer(kind, lr=0.05, momentum=0.9, weight_decay=0.01, eps=1e-6,
+                          scale=1.0 / world)
+    heaps, tables = _mk_tables(world, n, gdt, odt, blk, opt, cuda_device)
+    npad = tables[0].n
+    w0 = torch.randn(npad, device=cuda_device)
+    w0[n:] = 0
+    for t in tables:
+        t.load_master(w0)
+    ref_w = w0.clone()
+    s1 = torch.zeros_like(ref_w)
+    s2 = torch.zeros_like(ref_w)
+    for step in range(1, 4):
+        grads = []
+        for t in tables:
+            g = torch.randn(npad, device=cuda_device).to(gdt)
+            g[n:] = 0
+            t.grad.copy_(g)
+            grads.append(g)
+        for t in tables:  # every rank's server role, one after the other
+            t.push_pull(sync=False)
+        torch.cuda.synchronize()
+        dense_update(ref_w, grads, kind, lr=0.05, momentum=0.9, weight_decay=0.01, eps=1e-6,
+                     scale=1.0 / world, step=step, s1=s1, s2=s2)
+        for t in tables:
+            torch.testing.assert_close(t.weight[:n].float(), ref_w[:n].to(odt).float(),
+                                       **_tol(gdt, odt))
+    full = torch.zeros(npad, device=cuda_device)
+    for t in tables:
+        t.gather_master(full)
+    torch.testing.assert_close(full[:n], ref_w[:n], rtol=2e-5, atol=2e-5)
+    for h in heaps:
+        h.close()
+
+
+@pytest.mark.parametrize("world", [1, 8])
+def test_push_then_pull_and_subranges(cuda_device, world):
+    """Separate Push and Pull, issued slice by slice, equal one whole-table PushPull."""
+    from ps_lite_b200.parallel import ServerOptimizer
+    torch.manual_seed(7)
+    n = 50_000
+    opt = ServerOptimizer("momentum", lr=0.1, momentum=0.9)
+    heaps, tables = _mk_tables(world, n, torch.bfloat16, torch.bfloat16, 2048, opt, cuda_device)
+    npad = tables[0].n
+    w0 = torch.randn(npad, device=cuda_device)
+    for t in tables:
+        t.load_master(w0)
+    ref_w, s1 = w0.clone(), torch.zeros(npad, device=cuda_device)
+    grads = []
+    for t in tables:
+        g = torch.randn(npad, device=cuda_device).to(torch.bfloat16)
+        t.grad.copy_(g)
+        grads.append(g)
+    cuts = [0, 8, 4096 + 16, 20_000, 20_008, npad]
+    for b, e in zip(cuts[:-1], cuts[1:]):
+        for t in tables:
+            t.push(b, e, sync=False, opt_step=(b == 0))
+    for b, e in zip(cuts[:-1], cuts[1:]):
+        for t in tables:
+            t.pull(b, e, sync=False)
+    torch.cuda.synchronize()
+    dense_update(ref_w, grads, "momentum", lr=0.1, momentum=0.9, s1=s1)
+    for t in tables:
+        torch.testing.assert_close(t.weight.float(), ref_w.to(torch.bfloat16).float(),
+                                   rtol=1e-2, atol=1e-2)
+    for h in heaps:
+        h.close()
+
+
+def test_entry_wait_runs_out_and_reports(cuda_device):
+    """A rank whose peer never announces itself gives up after the limit and says who was late."""
+    from ps_lite_b200 import _lib
+    from ps_lite_b200.parallel import DenseTable, ServerOptimizer, SymmetricHeap
+    heaps = SymmetricHeap.emulated(1 << 21, 2, device=cuda_device)
+    t0 = DenseTable(heaps[0], 4096, optimizer=ServerOptimizer("sum"), channel=3)
+    t0.grad.fill_(1.0)
+    t0.push_pull(sync=True, timeout_s=0.2)   # rank 1 never launches: its flag is never set
+    torch.cuda.synchronize()
+    status, epoch = heaps[0].channel_status(3)
+    assert status == -2
+    assert torch.all(t0.master == 0)  # the data was not touched
+    with pytest.raises(_lib.PsdevError):
+        t0.check()
+    heaps[0].clear_channel(3)
+    assert heaps[0].channel_status(3)[0] == 0
+    # the context is still usable
+    t1 = DenseTable(heaps[0], 4096, optimizer=ServerOptimizer("sum"), channel=4)
+    t1.grad.fill_(2.0)
+    heaps[1].tensor(t1.grad_off, 4096, torch.float32).fill_(3.0)
+    t1.push_pull(sync=False)
+    torch.cuda.synchronize()
+    assert torch.all(t1.master[:2048] == 5.0)
+
+
+def test_world1_sync_flags_advance_epoch(cuda_device):
+    from ps_lite_b200.parallel import DenseTable, ServerOptimizer, SymmetricHeap
+    heap = SymmetricHeap(1 << 22, 0, 1, device=cuda_device)
+    t = DenseTable(heap, 100_000, optimizer=ServerOptimizer("sum"), channel=1)
+    t.grad.fill_(1.0)
+    for _ in range(5):
+        t.push_pull(sync=True)
+    heap.barrier()
+    torch.cuda.synchronize()
+    assert heap.channel_status(1) == (0, 5)
+    assert torch.all(t.weight[:100_000] == 5.0)
+    heap.close()
