@@ -22,7 +22,6 @@
 namespace psdev {
 
 constexpr int kDenseThreads = 512;
-constexpr int kDenseTile = 8192;  // elements per work item
 
 struct DenseArgs {
   void* base[PSDEV_MAX_RANKS];
@@ -215,10 +214,32 @@ __device__ __forceinline__ void channel_leave(void* const* base, int rank, int w
 }
 
 // ---- the kernel -----------------------------------------------------------------------
-template <typename GT, typename OT, class Opt, bool REDUCE, bool BCAST>
+// WMAX: compile-time bound on the number of ranks (1, 2, 4 or 8); the peer loops are fully
+// unrolled to WMAX and predicated on the runtime world size.  Each thread handles
+// U = max(1, 4 / ... ) vectors per trip so that about 128 bytes of gradient loads per
+// thread are in flight whatever the world size.
+template <int WMAX>
+struct DenseShape {
+  static constexpr int kUnroll = WMAX >= 8 ? 1 : (WMAX == 4 ? 2 : 4);
+};
+template <typename GT, typename OT, bool REDUCE>
+struct DenseVec {
+  static constexpr int kVec = REDUCE ? VecOf<GT>::kPer16 : (sizeof(OT) == 2 ? 8 : 4);
+};
+template <typename GT, typename OT, bool REDUCE, int WMAX>
+struct DenseTile {
+  static constexpr int kVec = DenseVec<GT, OT, REDUCE>::kVec;
+  static constexpr int kBase = DenseShape<WMAX>::kUnroll;
+  static constexpr int kUnroll = (kVec == 8 && kBase > 2) ? 2 : kBase;
+  static constexpr int kElems = kDenseThreads * kVec * kUnroll;
+};
+
+template <typename GT, typename OT, class Opt, bool REDUCE, bool BCAST, int WMAX>
 __global__ void __launch_bounds__(kDenseThreads)
     dense_kernel(const __grid_constant__ DenseArgs a) {
-  constexpr int VEC = REDUCE ? VecOf<GT>::kPer16 : (sizeof(OT) == 2 ? 8 : 4);
+  constexpr int VEC = DenseVec<GT, OT, REDUCE>::kVec;
+  constexpr int U = DenseTile<GT, OT, REDUCE, WMAX>::kUnroll;
+  constexpr int TILE = kDenseThreads * VEC * U;
   __shared__ unsigned long long s_epoch;
   __shared__ int s_err, s_last;
   const int W = a.world, R = a.rank;
@@ -233,65 +254,90 @@ __global__ void __launch_bounds__(kDenseThreads)
       const long long sub = t - k * a.tiles_per_blk;
       const long long j = a.first_owned + k * W;  // global block index
       const long long blk_lo = j * a.blk;
-      long long lo = blk_lo + sub * kDenseTile;
-      long long hi = lo + kDenseTile;
+      long long lo = blk_lo + sub * TILE;
+      long long hi = lo + TILE;
       const long long blk_hi = blk_lo + a.blk;
       if (hi > blk_hi) hi = blk_hi;
-      if (lo < a.begin) lo = a.begin;
       if (hi > a.end) hi = a.end;
+      // `lo` is not clamped to a.begin: lanes keep their alignment and skip i < begin
       const long long st_base = (j / W) * a.blk - blk_lo;  // state index = st_base + i
-      for (long long i = lo + (long long)threadIdx.x * VEC; i < hi;
-           i += (long long)kDenseThreads * VEC) {
-        float w[VEC], m[VEC], v[VEC];
-        const long long si = st_base + i;
-        if constexpr (REDUCE) {
-          uint4 gv[PSDEV_MAX_RANKS];
+      const long long i0 = lo + (long long)threadIdx.x * VEC;
+      bool live[U];
 #pragma unroll
-          for (int p = 0; p < PSDEV_MAX_RANKS; ++p) {
-            if (p < W) {
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + (long long)u * kDenseThreads * VEC;
+        live[u] = (i < hi) && (i >= a.begin);
+      }
+      float w[U][VEC], m[U][VEC], v[U][VEC];
+      if constexpr (REDUCE) {
+        uint4 gv[U][WMAX];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + (long long)u * kDenseThreads * VEC;
+#pragma unroll
+          for (int p = 0; p < WMAX; ++p) {
+            if (p < W && live[u]) {
               const GT* src = reinterpret_cast<const GT*>(
                                   reinterpret_cast<const char*>(a.base[p]) + a.grad_off) + i;
-              gv[p] = ld_sys_v4(src);
+              gv[u][p] = ld_sys_v4(src);
             }
           }
-          load_f32<VEC>(a.master + si, w);
-          if constexpr (Opt::kStates >= 1) load_f32<VEC>(a.s1 + si, m);
-          if constexpr (Opt::kStates >= 2) load_f32<VEC>(a.s2 + si, v);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long si = st_base + i0 + (long long)u * kDenseThreads * VEC;
+          if (live[u]) {
+            load_f32<VEC>(a.master + si, w[u]);
+            if constexpr (Opt::kStates >= 1) load_f32<VEC>(a.s1 + si, m[u]);
+            if constexpr (Opt::kStates >= 2) load_f32<VEC>(a.s2 + si, v[u]);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (!live[u]) continue;
+          const long long si = st_base + i0 + (long long)u * kDenseThreads * VEC;
           float g[VEC];
 #pragma unroll
           for (int q = 0; q < VEC; ++q) g[q] = 0.f;
 #pragma unroll
-          for (int p = 0; p < PSDEV_MAX_RANKS; ++p) {
+          for (int p = 0; p < WMAX; ++p) {
             if (p < W) {
               float f[VEC];
-              VecOf<GT>::unpack(gv[p], f);
+              VecOf<GT>::unpack(gv[u][p], f);
 #pragma unroll
               for (int q = 0; q < VEC; ++q) g[q] += f[q];
             }
           }
 #pragma unroll
           for (int q = 0; q < VEC; ++q) {
-            float mm = Opt::kStates >= 1 ? m[q] : 0.f;
-            float vv = Opt::kStates >= 2 ? v[q] : 0.f;
-            Opt::apply(w[q], g[q] * a.opt.scale, mm, vv, a.opt);
-            if (Opt::kStates >= 1) m[q] = mm;
-            if (Opt::kStates >= 2) v[q] = vv;
+            float mm = Opt::kStates >= 1 ? m[u][q] : 0.f;
+            float vv = Opt::kStates >= 2 ? v[u][q] : 0.f;
+            Opt::apply(w[u][q], g[q] * a.opt.scale, mm, vv, a.opt);
+            if (Opt::kStates >= 1) m[u][q] = mm;
+            if (Opt::kStates >= 2) v[u][q] = vv;
           }
-          store_f32<VEC>(a.master + si, w);
-          if constexpr (Opt::kStates >= 1) store_f32<VEC>(a.s1 + si, m);
-          if constexpr (Opt::kStates >= 2) store_f32<VEC>(a.s2 + si, v);
-        } else {
-          load_f32<VEC>(a.master + si, w);
+          store_f32<VEC>(a.master + si, w[u]);
+          if constexpr (Opt::kStates >= 1) store_f32<VEC>(a.s1 + si, m[u]);
+          if constexpr (Opt::kStates >= 2) store_f32<VEC>(a.s2 + si, v[u]);
         }
-        if constexpr (BCAST) {
+      } else {
 #pragma unroll
-          for (int pp = 0; pp < PSDEV_MAX_RANKS; ++pp) {
-            if (pp < W) {
-              int p = R + pp;
-              if (p >= W) p -= W;
-              OT* dst = reinterpret_cast<OT*>(reinterpret_cast<char*>(a.base[p]) +
-                                              a.weight_off) + i;
-              store_out<OT, VEC>(dst, w);
+        for (int u = 0; u < U; ++u) {
+          const long long si = st_base + i0 + (long long)u * kDenseThreads * VEC;
+          if (live[u]) load_f32<VEC>(a.master + si, w[u]);
+        }
+      }
+      if constexpr (BCAST) {
+#pragma unroll
+        for (int pp = 0; pp < WMAX; ++pp) {
+          if (pp < W) {
+            int p = R + pp;
+            if (p >= W) p -= W;
+            OT* dst0 = reinterpret_cast<OT*>(reinterpret_cast<char*>(a.base[p]) + a.weight_off);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const long long i = i0 + (long long)u * kDenseThreads * VEC;
+              if (live[u]) store_out<OT, VEC>(dst0 + i, w[u]);
             }
           }
         }

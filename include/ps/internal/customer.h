@@ -1,0 +1,73 @@
+// Customer: the mailbox of one application endpoint (a KVWorker, KVServer or SimpleApp).
+//
+// It owns a priority receive queue and a thread that runs the application's handler on each
+// delivered message, and it tracks outstanding requests by timestamp so that callers can
+// wait for all responses.  Reference: include/ps/internal/customer.h:26-111,
+// src/customer.cc:14-64.  Differences: endpoints are tagged worker-side or server-side so a
+// process that is worker and server at once can host both with the same (app, customer) ids;
+// waits can be bounded; a failed request (device error, dead peer) can be marked so that
+// WaitRequest reports it instead of blocking forever.
+#ifndef PS_INTERNAL_CUSTOMER_H_
+#define PS_INTERNAL_CUSTOMER_H_
+#include <atomic>
+#include <condition_variable>
+#include <functional>
+#include <memory>
+#include <mutex>
+#include <thread>
+#include <utility>
+#include <vector>
+
+#include "ps/internal/message.h"
+#include "ps/internal/threadsafe_pqueue.h"
+
+namespace ps {
+
+class Customer {
+ public:
+  using RecvHandle = std::function<void(const Message& recved)>;
+  enum Side { kWorkerSide = 0, kServerSide = 1 };
+
+  // Registers with the Postoffice and starts the handler thread.
+  Customer(int app_id, int customer_id, const RecvHandle& recv_handle, Side side = kWorkerSide);
+  // Unregisters, drains and joins the handler thread.
+  ~Customer();
+
+  int app_id() const { return app_id_; }
+  int customer_id() const { return customer_id_; }
+  Side side() const { return side_; }
+
+  // Opens a request to `recver` (a node id or a group id) and returns its timestamp.  The
+  // request completes when every node of `recver` has responded.
+  int NewRequest(int recver);
+  // Blocks until request `timestamp` completed.
+  void WaitRequest(int timestamp);
+  // Bounded form: false if `timeout_ms` elapsed first (timeout_ms < 0 waits forever).
+  bool WaitRequestFor(int timestamp, int timeout_ms);
+  // Responses received so far for `timestamp`.
+  int NumResponse(int timestamp);
+  // Credits `num` responses (used for recipients that were skipped, and by the handler
+  // thread after each response message).
+  void AddResponse(int timestamp, int num = 1);
+  // Hands a received message to this customer (called by the van's receive thread).
+  void Accept(const Message& recved) { recv_queue_.Push(recved); }
+
+ private:
+  void Receiving();
+
+  const int app_id_;
+  const int customer_id_;
+  const Side side_;
+  RecvHandle recv_handle_;
+  ThreadsafePQueue recv_queue_;
+  std::unique_ptr<std::thread> recv_thread_;
+
+  std::mutex tracker_mu_;
+  std::condition_variable tracker_cond_;
+  // tracker_[ts] = (responses expected, responses received)
+  std::vector<std::pair<int, int>> tracker_;
+  DISALLOW_COPY_AND_ASSIGN(Customer);
+};
+
+}  // namespace ps
+#endif  // PS_INTERNAL_CUSTOMER_H_

@@ -1,0 +1,123 @@
+// Postoffice: the per-process hub that knows the cluster shape and owns the van.
+//
+// Public surface of the reference's Postoffice (include/ps/internal/postoffice.h:24-164):
+// Start/Finalize, customer registry, node-group table, uniform server key ranges, barriers,
+// heartbeat bookkeeping, rank/id conversions.  New: the role "joint" (DMLC_ROLE=joint), in
+// which a process is a worker and a server at once; is_worker() and is_server() are then
+// both true and customers are registered per side.
+#ifndef PS_INTERNAL_POSTOFFICE_H_
+#define PS_INTERNAL_POSTOFFICE_H_
+#include <algorithm>
+#include <condition_variable>
+#include <functional>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "ps/internal/customer.h"
+#include "ps/internal/env.h"
+#include "ps/internal/van.h"
+#include "ps/range.h"
+
+namespace ps {
+
+class Postoffice {
+ public:
+  static Postoffice* Get() {
+    static Postoffice inst;
+    return &inst;
+  }
+
+  Van* van() { return van_; }
+
+  // Reads the DMLC_* environment, creates and starts the van, optionally waits at a global
+  // barrier.  `argv0` is only used for log lines.  Safe to call once per customer thread.
+  void Start(int customer_id, const char* argv0, const bool do_barrier);
+  // Optional global barrier, then (for customer 0) stops the van, resets the state and runs
+  // the exit callback.
+  void Finalize(const int customer_id, const bool do_barrier = true);
+
+  void AddCustomer(Customer* customer);
+  void RemoveCustomer(Customer* customer);
+  // Looks up a registered customer; polls up to `timeout` seconds for it to appear.
+  // `side` < 0 accepts either side (worker-side preferred).
+  Customer* GetCustomer(int app_id, int customer_id, int timeout = 0, int side = -1) const;
+
+  // Node ids denoted by `node_id`: the id itself, or the members of a group id (< 8).
+  const std::vector<int>& GetNodeIDs(int node_id) const {
+    const auto it = node_ids_.find(node_id);
+    CHECK(it != node_ids_.cend()) << "node " << node_id << " doesn't exist";
+    return it->second;
+  }
+
+  // The key range of every server: server i owns [kMaxKey/S*i, kMaxKey/S*(i+1)).
+  const std::vector<Range>& GetServerKeyRanges();
+
+  using Callback = std::function<void()>;
+  void RegisterExitCallback(const Callback& cb) { exit_callback_ = cb; }
+
+  static inline int WorkerRankToID(int rank) { return rank * 2 + 9; }
+  static inline int ServerRankToID(int rank) { return rank * 2 + 8; }
+  static inline int IDtoRank(int id) { return std::max((id - 8) / 2, 0); }
+  static inline bool IsServerID(int id) { return id >= 8 && (id % 2) == 0; }
+  static inline bool IsWorkerID(int id) { return id >= 9 && (id % 2) == 1; }
+
+  int num_workers() const { return num_workers_; }
+  int num_servers() const { return num_servers_; }
+  int my_rank() const { return IDtoRank(van_->my_node().id); }
+  int is_worker() const { return is_worker_; }
+  int is_server() const { return is_server_; }
+  int is_scheduler() const { return is_scheduler_; }
+  int is_joint() const { return is_worker_ && is_server_; }
+  int verbose() const { return verbose_; }
+  bool is_recovery() const { return van_->my_node().is_recovery; }
+
+  // Blocks until every node of `node_group` (which must include this node) entered.
+  void Barrier(int customer_id, int node_group);
+  // Called by the van for control responses that concern the Postoffice (barrier release).
+  void Manage(const Message& recv);
+
+  void UpdateHeartbeat(int node_id, time_t t) {
+    std::lock_guard<std::mutex> lk(heartbeat_mu_);
+    heartbeats_[node_id] = t;
+  }
+  // Ids whose last heartbeat is older than `t` seconds (empty while heartbeats are off or
+  // the process is younger than `t`).
+  std::vector<int> GetDeadNodes(int t = 60);
+
+ private:
+  Postoffice();
+  ~Postoffice() { delete van_; }
+  void InitEnvironment();
+
+  Van* van_ = nullptr;
+  mutable std::mutex mu_;
+  // (app_id, customer_id, side) -> customer
+  std::map<std::tuple<int, int, int>, Customer*> customers_;
+  std::unordered_map<int, std::vector<int>> node_ids_;
+  std::mutex server_key_ranges_mu_;
+  std::vector<Range> server_key_ranges_;
+  bool is_worker_ = false, is_server_ = false, is_scheduler_ = false;
+  int num_servers_ = 0, num_workers_ = 0;
+  int verbose_ = 0;
+  // customer_id -> number of barrier releases still awaited
+  std::unordered_map<int, int> barrier_pending_;
+  std::mutex barrier_mu_;
+  std::condition_variable barrier_cond_;
+  std::mutex heartbeat_mu_;
+  std::mutex start_mu_;
+  int init_stage_ = 0;
+  std::unordered_map<int, time_t> heartbeats_;
+  Callback exit_callback_;
+  std::shared_ptr<Environment> env_ref_;
+  time_t start_time_ = 0;
+  DISALLOW_COPY_AND_ASSIGN(Postoffice);
+};
+
+// Verbose logging gated by PS_VERBOSE.
+#define PS_VLOG(x) LOG_IF(INFO, x <= ::ps::Postoffice::Get()->verbose())
+
+}  // namespace ps
+#endif  // PS_INTERNAL_POSTOFFICE_H_

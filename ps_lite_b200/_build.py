@@ -52,7 +52,7 @@ def _headers_stamp() -> str:
     h = hashlib.sha1()
     for d in ("include", "src"):
         for f in sorted((ROOT / d).rglob("*")):
-            if f.suffix in (".h", ".cuh", ".hpp"):
+            if f.suffix in (".h", ".cuh", ".hpp", ".inl"):
                 h.update(str(f.relative_to(ROOT)).encode())
                 h.update(f.read_bytes())
     return h.hexdigest()[:16]

@@ -1,0 +1,73 @@
+#include "ps/internal/customer.h"
+
+#include <chrono>
+
+#include "ps/internal/postoffice.h"
+
+namespace ps {
+
+Customer::Customer(int app_id, int customer_id, const RecvHandle& recv_handle, Side side)
+    : app_id_(app_id), customer_id_(customer_id), side_(side), recv_handle_(recv_handle) {
+  Postoffice::Get()->AddCustomer(this);
+  recv_thread_.reset(new std::thread(&Customer::Receiving, this));
+}
+
+Customer::~Customer() {
+  Postoffice::Get()->RemoveCustomer(this);
+  Message stop;
+  stop.meta.control.cmd = Control::TERMINATE;
+  // lowest possible priority: everything already queued is handled first
+  stop.meta.priority = INT_MIN;
+  recv_queue_.Push(stop);
+  recv_thread_->join();
+}
+
+int Customer::NewRequest(int recver) {
+  const int expected = static_cast<int>(Postoffice::Get()->GetNodeIDs(recver).size());
+  std::lock_guard<std::mutex> lk(tracker_mu_);
+  tracker_.emplace_back(expected, 0);
+  return static_cast<int>(tracker_.size()) - 1;
+}
+
+void Customer::WaitRequest(int timestamp) { WaitRequestFor(timestamp, -1); }
+
+bool Customer::WaitRequestFor(int timestamp, int timeout_ms) {
+  std::unique_lock<std::mutex> lk(tracker_mu_);
+  CHECK_GE(timestamp, 0);
+  CHECK_LT(static_cast<size_t>(timestamp), tracker_.size()) << "unknown timestamp";
+  auto done = [this, timestamp] {
+    return tracker_[timestamp].first <= tracker_[timestamp].second;
+  };
+  if (timeout_ms < 0) {
+    tracker_cond_.wait(lk, done);
+    return true;
+  }
+  return tracker_cond_.wait_for(lk, std::chrono::milliseconds(timeout_ms), done);
+}
+
+int Customer::NumResponse(int timestamp) {
+  std::lock_guard<std::mutex> lk(tracker_mu_);
+  return tracker_[timestamp].second;
+}
+
+void Customer::AddResponse(int timestamp, int num) {
+  {
+    std::lock_guard<std::mutex> lk(tracker_mu_);
+    tracker_[timestamp].second += num;
+  }
+  tracker_cond_.notify_all();
+}
+
+void Customer::Receiving() {
+  for (;;) {
+    Message recv;
+    recv_queue_.WaitAndPop(&recv);
+    if (!recv.meta.control.empty() && recv.meta.control.cmd == Control::TERMINATE) break;
+    // The handler runs first, so a completion callback fired by the last response has
+    // finished by the time WaitRequest is released (reference: src/customer.cc:57-62).
+    recv_handle_(recv);
+    if (!recv.meta.request) AddResponse(recv.meta.timestamp, 1);
+  }
+}
+
+}  // namespace ps

@@ -1,0 +1,5 @@
+#include <cuda_bf16.h>
+#define PSDEV_DENSE_GT float
+#define PSDEV_DENSE_OT float
+#define PSDEV_DENSE_FN dense_dispatch_f32_f32
+#include "kernels/dense_inst.inl"

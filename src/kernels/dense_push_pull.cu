@@ -7,40 +7,10 @@
 
 namespace psdev {
 std::atomic<uint64_t> g_launches{0};
-
-template <typename GT, typename OT, class Opt, bool RED, bool BC>
-static int launch(const DenseArgs& a, int ctas, cudaStream_t s) {
-  dense_kernel<GT, OT, Opt, RED, BC><<<ctas, kDenseThreads, 0, s>>>(a);
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  return (int)cudaGetLastError();
-}
-
-template <typename GT, typename OT, bool RED, bool BC>
-static int by_opt(const DenseArgs& a, int ctas, cudaStream_t s) {
-  if (!RED) return launch<GT, OT, OptSum, RED, BC>(a, ctas, s);
-  switch (a.opt.kind) {
-    case PSDEV_OPT_SUM: return launch<GT, OT, OptSum, RED, BC>(a, ctas, s);
-    case PSDEV_OPT_ASSIGN: return launch<GT, OT, OptAssign, RED, BC>(a, ctas, s);
-    case PSDEV_OPT_SGD: return launch<GT, OT, OptSgd, RED, BC>(a, ctas, s);
-    case PSDEV_OPT_MOMENTUM:
-      if (!a.s1) return PSDEV_ERR_ARG;
-      return launch<GT, OT, OptMomentum, RED, BC>(a, ctas, s);
-    case PSDEV_OPT_ADAM:
-      if (!a.s1 || !a.s2) return PSDEV_ERR_ARG;
-      return launch<GT, OT, OptAdam, RED, BC>(a, ctas, s);
-    default: return PSDEV_ERR_UNSUPPORTED;
-  }
-}
-
-template <typename GT, typename OT>
-static int by_op(int op, const DenseArgs& a, int ctas, cudaStream_t s) {
-  switch (op) {
-    case PSDEV_OP_PUSH: return by_opt<GT, OT, true, false>(a, ctas, s);
-    case PSDEV_OP_PUSHPULL: return by_opt<GT, OT, true, true>(a, ctas, s);
-    case PSDEV_OP_PULL: return by_opt<GT, OT, false, true>(a, ctas, s);
-    default: return PSDEV_ERR_ARG;
-  }
-}
+int dense_dispatch_f32_f32(int op, const DenseArgs& a, int ctas, cudaStream_t s);
+int dense_dispatch_bf16_bf16(int op, const DenseArgs& a, int ctas, cudaStream_t s);
+int dense_dispatch_bf16_f32(int op, const DenseArgs& a, int ctas, cudaStream_t s);
+int dense_dispatch_f32_bf16(int op, const DenseArgs& a, int ctas, cudaStream_t s);
 }  // namespace psdev
 
 using namespace psdev;
@@ -77,7 +47,6 @@ extern "C" int psdev_dense_op(const psdev_world_t* w, const psdev_table_t* t, in
   a.channel = channel;
   a.sync = sync;
   a.timeout_ns = timeout_ns;
-  a.tiles_per_blk = (t->blk + kDenseTile - 1) / kDenseTile;
   // owned blocks meeting [begin, end): indices j in [jb, je] with j % W == R
   a.n_owned = 0;
   a.first_owned = 0;
@@ -89,15 +58,13 @@ extern "C" int psdev_dense_op(const psdev_world_t* w, const psdev_table_t* t, in
       a.n_owned = (je - first) / W + 1;
     }
   }
-  int64_t ntiles = a.n_owned * a.tiles_per_blk;
-  int ctas = num_ctas > 0 ? num_ctas : 296;
-  if (ntiles < ctas) ctas = ntiles > 0 ? (int)ntiles : 1;
+  const int ctas = num_ctas;
   cudaStream_t s = (cudaStream_t)stream;
   const bool gbf = t->grad_dtype == PSDEV_BF16, obf = t->out_dtype == PSDEV_BF16;
-  if (gbf && obf) return by_op<__nv_bfloat16, __nv_bfloat16>(op, a, ctas, s);
-  if (gbf && !obf) return by_op<__nv_bfloat16, float>(op, a, ctas, s);
-  if (!gbf && obf) return by_op<float, __nv_bfloat16>(op, a, ctas, s);
-  return by_op<float, float>(op, a, ctas, s);
+  if (gbf && obf) return dense_dispatch_bf16_bf16(op, a, ctas, s);
+  if (gbf && !obf) return dense_dispatch_bf16_f32(op, a, ctas, s);
+  if (!gbf && obf) return dense_dispatch_f32_bf16(op, a, ctas, s);
+  return dense_dispatch_f32_f32(op, a, ctas, s);
 }
 
 extern "C" uint64_t psdev_launch_count(void) { return g_launches.load(); }

@@ -1,0 +1,35 @@
+"""Launches the multi-process GPU checks when the box has at least two GPUs."""
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _torchrun(script, nproc, timeout=600, extra_env=None):
+    env = dict(os.environ)
+    env.update(extra_env or {})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+           f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(HERE, script)]
+    return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+
+
+def test_dense_push_pull_across_gpus(cuda_device):
+    import torch
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    nproc = 8 if n >= 8 else (4 if n >= 4 else 2)
+    r = _torchrun("mp_dense_check.py", nproc)
+    assert r.returncode == 0 and "MP_DENSE_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
