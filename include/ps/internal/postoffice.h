@@ -102,8 +102,19 @@ class Postoffice {
   bool is_worker_ = false, is_server_ = false, is_scheduler_ = false;
   int num_servers_ = 0, num_workers_ = 0;
   int verbose_ = 0;
-  // customer_id -> number of barrier releases still awaited
-  std::unordered_map<int, int> barrier_pending_;
+  // One barrier round per node group: the first caller sends the requests, later callers
+  // of the same round join it, and the round ends when every id of this process has been
+  // released by the scheduler.
+  struct Round {
+    bool in_flight = false;
+    int pending = 0;
+    uint64_t generation = 0;
+  };
+  std::unordered_map<int, Round> rounds_;
+  int started_customers_ = 0;
+  int finalizing_customers_ = 0;
+  uint64_t finalize_generation_ = 0;
+  bool start_barrier_begun_ = false, start_barrier_done_ = false;
   std::mutex barrier_mu_;
   std::condition_variable barrier_cond_;
   std::mutex heartbeat_mu_;

@@ -17,6 +17,7 @@
 #ifndef PS_INTERNAL_VAN_H_
 #define PS_INTERNAL_VAN_H_
 #include <atomic>
+#include <chrono>
 #include <ctime>
 #include <memory>
 #include <mutex>
@@ -34,6 +35,7 @@
 namespace ps {
 
 class Resender;
+class Customer;
 
 class Van {
  public:
@@ -66,6 +68,10 @@ class Van {
   int GetTimestamp() { return timestamp_++; }
   bool IsReady() const { return ready_.load(); }
 
+  // Tells the receive loop that a customer registered, so that messages that arrived
+  // before their application endpoint existed are delivered now.
+  void Kick();
+
   // Traffic counters (payload + meta bytes), readable at any time.
   size_t send_bytes() const { return send_bytes_.load(); }
   size_t recv_bytes() const { return recv_bytes_.load(); }
@@ -89,6 +95,8 @@ class Van {
   // Backend-specific setup before Bind (e.g. creating the I/O thread).
   virtual void StartBackend() {}
   virtual void StopBackend() {}
+  // True for a backend in which this single process is scheduler, server and worker.
+  virtual bool IsStandalone() const { return false; }
 
   Node scheduler_;
   Node my_node_;
@@ -108,6 +116,8 @@ class Van {
   void ProcessBarrierCommand(Message* msg);
   void ProcessHeartbeat(Message* msg);
   void ProcessDataMsg(Message* msg);
+  Customer* FindCustomer(const Message& msg);
+  void RetryParked();
   void SchedulerRegister(Message* msg);
   void SchedulerAssignAndBroadcast();
   void SchedulerAdmitRecovery(const Node& newcomer, int reuse_server_id, int reuse_worker_id);
@@ -132,6 +142,13 @@ class Van {
   ThreadsafeQueue<Message> inbox_;  // complete messages awaiting the receive loop
 
   Resender* resender_ = nullptr;
+
+  // data messages whose customer does not exist yet (touched by the receive loop only)
+  struct Parked {
+    Message msg;
+    std::chrono::steady_clock::time_point since;
+  };
+  std::vector<Parked> parked_;
 
   // scheduler state
   struct Registration {

@@ -1,1 +1,1 @@
-"""launch of ps_lite_b200."""
+"""Job launchers: local processes, ssh, mpirun; all set the DMLC_* environment contract."""

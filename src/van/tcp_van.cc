@@ -1,0 +1,487 @@
+// Socket van: length-prefixed frames over TCP (or Unix-domain sockets with DMLC_LOCAL=1),
+// one epoll thread for all receives, one lazily opened sending connection per peer process.
+//
+// It takes the place of the reference's ZMQVan (src/zmq_van.h:37-248) without libzmq.  What is
+// kept: one listening endpoint per process, sends serialised per destination, zero-copy
+// hand-over of received frames to SArray (each data frame is read straight into the buffer
+// that the SArray then owns), DMLC_LOCAL for same-host IPC, DMLC_USE_KUBERNETES to bind the
+// wildcard address, random-port retries on bind.  What differs: the frame header carries the
+// sender and receiver node ids explicitly (ZMQ derived the sender from the socket identity,
+// src/zmq_van.h:234-248), which is what lets one process host several ids.
+//
+// Frame: [FrameHeader][n_data x u64 lengths][meta bytes (PBMeta)][data 0]...[data n-1]
+#include <arpa/inet.h>
+#include <errno.h>
+#include <fcntl.h>
+#include <netdb.h>
+#include <netinet/in.h>
+#include <netinet/tcp.h>
+#include <sys/epoll.h>
+#include <sys/eventfd.h>
+#include <sys/socket.h>
+#include <limits.h>
+#include <sys/uio.h>
+#include <sys/un.h>
+#include <unistd.h>
+
+#include <chrono>
+#include <cstring>
+#include <map>
+#include <random>
+
+#include "ps/internal/pb_codec.h"
+#include "ps/internal/postoffice.h"
+#include "van/backends.h"
+
+namespace ps {
+namespace {
+
+constexpr uint32_t kMagic = 0x32425350u;  // "PSB2"
+constexpr uint32_t kMaxFrames = 64;
+
+struct FrameHeader {
+  uint32_t magic;
+  int32_t sender;
+  int32_t recver;
+  uint32_t meta_len;
+  uint32_t n_data;
+};
+static_assert(sizeof(FrameHeader) == 20, "frame header layout");
+
+std::string UnixPath(int port) { return "/tmp/psb200_" + std::to_string(port) + ".sock"; }
+
+bool WriteAll(int fd, struct iovec* iov, int iovcnt) {
+  while (iovcnt > 0) {
+    struct msghdr mh {};
+    mh.msg_iov = iov;
+    mh.msg_iovlen = static_cast<size_t>(iovcnt > IOV_MAX ? IOV_MAX : iovcnt);
+    // MSG_NOSIGNAL: a peer that has gone away yields EPIPE here, not a SIGPIPE
+    ssize_t n = ::sendmsg(fd, &mh, MSG_NOSIGNAL);
+    if (n < 0) {
+      if (errno == EINTR) continue;
+      return false;
+    }
+    size_t left = static_cast<size_t>(n);
+    while (iovcnt > 0 && left >= iov->iov_len) {
+      left -= iov->iov_len;
+      ++iov;
+      --iovcnt;
+    }
+    if (iovcnt > 0 && left > 0) {
+      iov->iov_base = static_cast<char*>(iov->iov_base) + left;
+      iov->iov_len -= left;
+    }
+  }
+  return true;
+}
+
+// Receive-side state of one accepted connection.
+struct InConn {
+  int fd = -1;
+  enum Phase { kHeader, kLens, kMeta, kData } phase = kHeader;
+  FrameHeader hdr{};
+  std::vector<uint64_t> lens;
+  std::string meta;
+  Message msg;
+  size_t frame = 0;       // index of the data frame being read
+  char* dst = nullptr;    // where the current phase reads into
+  size_t need = 0, got = 0;
+  char* frame_buf = nullptr;  // buffer of the data frame being read (not yet owned by msg)
+};
+
+struct OutConn {
+  std::mutex mu;
+  int fd = -1;
+  std::string host;
+  int port = 0;
+};
+
+class TcpVan : public Van {
+ public:
+  explicit TcpVan(bool priority) { set_priority_mode(priority); }
+  ~TcpVan() override {}
+
+ protected:
+  void StartBackend() override {
+    local_ = GetEnv("DMLC_LOCAL", 0) != 0;
+    epfd_ = epoll_create1(EPOLL_CLOEXEC);
+    CHECK_GE(epfd_, 0) << "epoll_create1: " << strerror(errno);
+    wakefd_ = eventfd(0, EFD_NONBLOCK | EFD_CLOEXEC);
+    CHECK_GE(wakefd_, 0);
+    struct epoll_event ev {};
+    ev.events = EPOLLIN;
+    ev.data.fd = wakefd_;
+    epoll_ctl(epfd_, EPOLL_CTL_ADD, wakefd_, &ev);
+    io_stop_ = false;
+    io_thread_.reset(new std::thread(&TcpVan::IoLoop, this));
+  }
+
+  void StopBackend() override {
+    io_stop_ = true;
+    uint64_t one = 1;
+    ssize_t r = ::write(wakefd_, &one, sizeof(one));
+    (void)r;
+    if (io_thread_) io_thread_->join();
+    io_thread_.reset();
+    for (auto& kv : in_) {
+      ::close(kv.first);
+      delete[] kv.second.frame_buf;
+    }
+    in_.clear();
+    {
+      std::lock_guard<std::mutex> lk(out_mu_);
+      for (auto& kv : out_) {
+        std::lock_guard<std::mutex> l2(kv.second->mu);
+        if (kv.second->fd >= 0) ::close(kv.second->fd);
+        kv.second->fd = -1;
+      }
+      out_.clear();
+      id_addr_.clear();
+    }
+    if (listen_fd_ >= 0) ::close(listen_fd_);
+    listen_fd_ = -1;
+    if (!unix_path_.empty()) ::unlink(unix_path_.c_str());
+    unix_path_.clear();
+    ::close(wakefd_);
+    ::close(epfd_);
+    wakefd_ = epfd_ = -1;
+  }
+
+  int Bind(const Node& node, int max_retry) override {
+    std::mt19937 rng(static_cast<unsigned>(getpid()) * 2654435761u +
+                     static_cast<unsigned>(time(nullptr)));
+    int port = node.port;
+    for (int attempt = 0; attempt <= max_retry; ++attempt) {
+      int fd = TryListen(port);
+      if (fd >= 0) {
+        listen_fd_ = fd;
+        struct epoll_event ev {};
+        ev.events = EPOLLIN;
+        ev.data.fd = fd;
+        epoll_ctl(epfd_, EPOLL_CTL_ADD, fd, &ev);
+        return port;
+      }
+      port = 10000 + static_cast<int>(rng() % 40000);
+    }
+    return -1;
+  }
+
+  void Connect(const Node& node) override {
+    CHECK_NE(node.id, Node::kEmpty);
+    CHECK_NE(node.port, Node::kEmpty);
+    std::lock_guard<std::mutex> lk(out_mu_);
+    const std::string key = node.hostname + ":" + std::to_string(node.port);
+    auto it = id_addr_.find(node.id);
+    if (it != id_addr_.end() && it->second != key) {
+      // the id moved to a new address (a recovered node): drop the old path if unused
+      const std::string old = it->second;
+      bool still_used = false;
+      for (auto& kv : id_addr_) still_used |= (kv.first != node.id && kv.second == old);
+      if (!still_used) {
+        auto oc = out_.find(old);
+        if (oc != out_.end()) {
+          std::lock_guard<std::mutex> l2(oc->second->mu);
+          if (oc->second->fd >= 0) ::close(oc->second->fd);
+          oc->second->fd = -1;
+          out_.erase(oc);
+        }
+      }
+    }
+    id_addr_[node.id] = key;
+    if (!out_.count(key)) {
+      auto c = std::make_shared<OutConn>();
+      c->host = node.hostname;
+      c->port = node.port;
+      out_[key] = c;
+    }
+  }
+
+  int SendMsg(const Message& msg) override {
+    const int id = msg.meta.recver;
+    CHECK_NE(id, Meta::kEmpty);
+    std::shared_ptr<OutConn> c;
+    {
+      std::lock_guard<std::mutex> lk(out_mu_);
+      auto it = id_addr_.find(id);
+      if (it == id_addr_.end()) {
+        LOG(WARNING) << "there is no path to node " << id;
+        return -1;
+      }
+      c = out_[it->second];
+    }
+    std::string meta;
+    pb::EncodeMeta(msg.meta, &meta);
+    const size_t n = msg.data.size();
+    CHECK_LE(n, (size_t)kMaxFrames);
+    FrameHeader h{kMagic, msg.meta.sender, msg.meta.recver, static_cast<uint32_t>(meta.size()),
+                  static_cast<uint32_t>(n)};
+    std::vector<uint64_t> lens(n);
+    std::vector<struct iovec> iov;
+    iov.reserve(3 + n);
+    iov.push_back({&h, sizeof(h)});
+    size_t total = sizeof(h) + meta.size();
+    for (size_t i = 0; i < n; ++i) {
+      CHECK(msg.data[i].mem_kind() == MemKind::kHost)
+          << "device-resident payloads travel through the device data plane, not the socket van";
+      lens[i] = msg.data[i].size();
+      total += lens[i] + 8;
+    }
+    if (n) iov.push_back({lens.data(), n * sizeof(uint64_t)});
+    iov.push_back({const_cast<char*>(meta.data()), meta.size()});
+    for (size_t i = 0; i < n; ++i)
+      if (lens[i]) iov.push_back({msg.data[i].data(), static_cast<size_t>(lens[i])});
+
+    std::lock_guard<std::mutex> lk(c->mu);
+    for (int attempt = 0; attempt < 2; ++attempt) {
+      if (c->fd < 0) c->fd = Dial(c->host, c->port);
+      if (c->fd < 0) return -1;
+      std::vector<struct iovec> tmp = iov;
+      if (WriteAll(c->fd, tmp.data(), static_cast<int>(tmp.size()))) return static_cast<int>(total);
+      // the peer went away (for instance it was replaced): reconnect once
+      ::close(c->fd);
+      c->fd = -1;
+    }
+    return -1;
+  }
+
+ private:
+  int TryListen(int port) {
+    int fd;
+    if (local_) {
+      fd = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
+      if (fd < 0) return -1;
+      struct sockaddr_un addr {};
+      addr.sun_family = AF_UNIX;
+      const std::string path = UnixPath(port);
+      strncpy(addr.sun_path, path.c_str(), sizeof(addr.sun_path) - 1);
+      ::unlink(path.c_str());
+      if (bind(fd, reinterpret_cast<struct sockaddr*>(&addr), sizeof(addr)) != 0) {
+        ::close(fd);
+        return -1;
+      }
+      unix_path_ = path;
+    } else {
+      fd = socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
+      if (fd < 0) return -1;
+      int one = 1;
+      setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+      struct sockaddr_in addr {};
+      addr.sin_family = AF_INET;
+      addr.sin_addr.s_addr = htonl(INADDR_ANY);  // also what DMLC_USE_KUBERNETES asks for
+      addr.sin_port = htons(static_cast<uint16_t>(port));
+      if (bind(fd, reinterpret_cast<struct sockaddr*>(&addr), sizeof(addr)) != 0) {
+        ::close(fd);
+        return -1;
+      }
+    }
+    if (listen(fd, 256) != 0) {
+      ::close(fd);
+      return -1;
+    }
+    fcntl(fd, F_SETFL, fcntl(fd, F_GETFL, 0) | O_NONBLOCK);
+    return fd;
+  }
+
+  // Blocking connect with retries: peers may still be starting.
+  int Dial(const std::string& host, int port) {
+    const int water = GetEnv("DMLC_PS_WATER_MARK", 0);
+    const auto deadline = std::chrono::steady_clock::now() +
+                          std::chrono::seconds(GetEnv("PS_CONNECT_TIMEOUT", 60));
+    while (!stopping()) {
+      int fd = -1;
+      bool ok = false;
+      if (local_) {
+        fd = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
+        struct sockaddr_un addr {};
+        addr.sun_family = AF_UNIX;
+        strncpy(addr.sun_path, UnixPath(port).c_str(), sizeof(addr.sun_path) - 1);
+        ok = fd >= 0 && connect(fd, reinterpret_cast<struct sockaddr*>(&addr), sizeof(addr)) == 0;
+      } else {
+        struct addrinfo hints {}, *res = nullptr;
+        hints.ai_family = AF_INET;
+        hints.ai_socktype = SOCK_STREAM;
+        if (getaddrinfo(host.c_str(), std::to_string(port).c_str(), &hints, &res) == 0 && res) {
+          fd = socket(res->ai_family, res->ai_socktype | SOCK_CLOEXEC, res->ai_protocol);
+          ok = fd >= 0 && connect(fd, res->ai_addr, res->ai_addrlen) == 0;
+          freeaddrinfo(res);
+        }
+      }
+      if (ok) {
+        int one = 1;
+        if (!local_) setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+        int buf = water > 0 ? water : (4 << 20);
+        setsockopt(fd, SOL_SOCKET, SO_SNDBUF, &buf, sizeof(buf));
+        return fd;
+      }
+      if (fd >= 0) ::close(fd);
+      if (std::chrono::steady_clock::now() > deadline) break;
+      std::this_thread::sleep_for(std::chrono::milliseconds(20));
+    }
+    LOG(WARNING) << "cannot connect to " << host << ":" << port;
+    return -1;
+  }
+
+  void Arm(InConn* c, InConn::Phase phase, char* dst, size_t need) {
+    c->phase = phase;
+    c->dst = dst;
+    c->need = need;
+    c->got = 0;
+  }
+
+  // Moves the connection to its next phase once the current one has all its bytes.
+  // Returns false on a protocol error.
+  bool Advance(InConn* c) {
+    for (;;) {
+      switch (c->phase) {
+        case InConn::kHeader:
+          if (c->hdr.magic != kMagic || c->hdr.n_data > kMaxFrames) return false;
+          c->lens.assign(c->hdr.n_data, 0);
+          c->msg = Message();
+          c->frame = 0;
+          if (c->hdr.n_data) {
+            Arm(c, InConn::kLens, reinterpret_cast<char*>(c->lens.data()),
+                c->hdr.n_data * sizeof(uint64_t));
+            return true;
+          }
+          // fall through to meta
+          c->phase = InConn::kLens;
+          continue;
+        case InConn::kLens:
+          c->meta.resize(c->hdr.meta_len);
+          Arm(c, InConn::kMeta, &c->meta[0], c->hdr.meta_len);
+          if (c->need) return true;
+          continue;
+        case InConn::kMeta: {
+          c->msg.meta.sender = c->hdr.sender;
+          c->msg.meta.recver = c->hdr.recver;
+          if (!pb::DecodeMeta(c->meta.data(), c->meta.size(), &c->msg.meta)) return false;
+          c->msg.meta.sender = c->hdr.sender;
+          c->msg.meta.recver = c->hdr.recver;
+          c->frame = 0;
+          c->phase = InConn::kData;
+          if (!NextFrame(c)) return true;  // message complete (delivered)
+          if (c->need) return true;
+          continue;
+        }
+        case InConn::kData: {
+          // frame `c->frame` is complete: hand its buffer to the message
+          SArray<char> arr;
+          arr.reset(c->frame_buf, c->lens[c->frame], [](char* p) { delete[] p; });
+          c->frame_buf = nullptr;
+          c->msg.data.push_back(arr);
+          ++c->frame;
+          if (!NextFrame(c)) return true;
+          if (c->need) return true;
+          continue;
+        }
+      }
+    }
+  }
+
+  // Arms the read of data frame c->frame, or delivers the message when none is left.
+  // Returns false when the message was delivered and the connection re-armed for a header.
+  bool NextFrame(InConn* c) {
+    if (c->frame >= c->lens.size()) {
+      size_t bytes = c->meta.size();
+      for (uint64_t l : c->lens) bytes += l;
+      c->msg.meta.data_size = static_cast<int>(bytes - c->meta.size());
+      Deliver(std::move(c->msg));
+      Arm(c, InConn::kHeader, reinterpret_cast<char*>(&c->hdr), sizeof(FrameHeader));
+      return false;
+    }
+    const size_t len = c->lens[c->frame];
+    c->frame_buf = new char[len ? len : 1];
+    Arm(c, InConn::kData, c->frame_buf, len);
+    return true;
+  }
+
+  void CloseIn(int fd) {
+    epoll_ctl(epfd_, EPOLL_CTL_DEL, fd, nullptr);
+    ::close(fd);
+    auto it = in_.find(fd);
+    if (it != in_.end()) {
+      delete[] it->second.frame_buf;
+      in_.erase(it);
+    }
+  }
+
+  void OnReadable(int fd) {
+    auto it = in_.find(fd);
+    if (it == in_.end()) return;
+    InConn* c = &it->second;
+    for (;;) {
+      if (c->need == c->got) {
+        if (!Advance(c)) {
+          LOG(WARNING) << "protocol error on an incoming connection; closing it";
+          CloseIn(fd);
+          return;
+        }
+      }
+      ssize_t n = ::read(fd, c->dst + c->got, c->need - c->got);
+      if (n > 0) {
+        c->got += static_cast<size_t>(n);
+        continue;
+      }
+      if (n == 0) {
+        CloseIn(fd);
+        return;
+      }
+      if (errno == EINTR) continue;
+      if (errno == EAGAIN || errno == EWOULDBLOCK) return;
+      CloseIn(fd);
+      return;
+    }
+  }
+
+  void IoLoop() {
+    struct epoll_event evs[64];
+    while (!io_stop_.load()) {
+      int n = epoll_wait(epfd_, evs, 64, 200);
+      if (n < 0) {
+        if (errno == EINTR) continue;
+        break;
+      }
+      for (int i = 0; i < n; ++i) {
+        const int fd = evs[i].data.fd;
+        if (fd == wakefd_) {
+          uint64_t v;
+          ssize_t r = ::read(wakefd_, &v, sizeof(v));
+          (void)r;
+        } else if (fd == listen_fd_) {
+          for (;;) {
+            int cfd = accept4(listen_fd_, nullptr, nullptr, SOCK_NONBLOCK | SOCK_CLOEXEC);
+            if (cfd < 0) break;
+            int buf = 4 << 20;
+            setsockopt(cfd, SOL_SOCKET, SO_RCVBUF, &buf, sizeof(buf));
+            InConn& c = in_[cfd];
+            c.fd = cfd;
+            Arm(&c, InConn::kHeader, reinterpret_cast<char*>(&c.hdr), sizeof(FrameHeader));
+            struct epoll_event ev {};
+            ev.events = EPOLLIN;
+            ev.data.fd = cfd;
+            epoll_ctl(epfd_, EPOLL_CTL_ADD, cfd, &ev);
+          }
+        } else {
+          OnReadable(fd);
+        }
+      }
+    }
+  }
+
+  bool local_ = false;
+  int epfd_ = -1, wakefd_ = -1, listen_fd_ = -1;
+  std::string unix_path_;
+  std::atomic<bool> io_stop_{false};
+  std::unique_ptr<std::thread> io_thread_;
+  std::map<int, InConn> in_;  // touched only by the I/O thread (and StopBackend after join)
+
+  std::mutex out_mu_;
+  std::unordered_map<int, std::string> id_addr_;               // node id -> "host:port"
+  std::unordered_map<std::string, std::shared_ptr<OutConn>> out_;  // one path per process
+};
+
+}  // namespace
+
+Van* NewTcpVan(bool priority) { return new TcpVan(priority); }
+
+}  // namespace ps
