@@ -1,0 +1,200 @@
+"""Python binding of the host runtime, wire codec against google.protobuf, launchers."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _pb_classes():
+    """PBMeta built from the field list of the wire contract (no protoc needed)."""
+    from google.protobuf import descriptor_pb2, descriptor_pool, message_factory
+    fd = descriptor_pb2.FileDescriptorProto(name="meta.proto", package="ps", syntax="proto2")
+    T = descriptor_pb2.FieldDescriptorProto
+    O, Q, R = T.LABEL_OPTIONAL, T.LABEL_REQUIRED, T.LABEL_REPEATED
+
+    def msg(name, fields):
+        m = fd.message_type.add(name=name)
+        for n, num, typ, label, tn, packed in fields:
+            f = m.field.add(name=n, number=num, type=typ, label=label)
+            if tn:
+                f.type_name = tn
+            if packed:
+                f.options.packed = True
+    I, B, S, Y, U, M = T.TYPE_INT32, T.TYPE_BOOL, T.TYPE_STRING, T.TYPE_BYTES, T.TYPE_UINT64, T.TYPE_MESSAGE
+    msg("PBNode", [("role", 1, I, Q, None, 0), ("id", 2, I, O, None, 0), ("hostname", 3, S, O, None, 0),
+                   ("port", 4, I, O, None, 0), ("is_recovery", 5, B, O, None, 0),
+                   ("customer_id", 10, I, O, None, 0)])
+    msg("PBControl", [("cmd", 1, I, Q, None, 0), ("node", 2, M, R, ".ps.PBNode", 0),
+                      ("barrier_group", 3, I, O, None, 0), ("msg_sig", 4, U, O, None, 0)])
+    msg("PBMeta", [("head", 1, I, O, None, 0), ("body", 2, Y, O, None, 0),
+                   ("control", 3, M, O, ".ps.PBControl", 0), ("request", 4, B, O, None, 0),
+                   ("push", 5, B, O, None, 0), ("simple_app", 6, B, O, None, 0),
+                   ("app_id", 7, I, O, None, 0), ("timestamp", 8, I, O, None, 0),
+                   ("data_type", 9, I, R, None, 1), ("customer_id", 10, I, O, None, 0),
+                   ("data_size", 11, I, O, None, 0), ("pull", 12, B, O, None, 0),
+                   ("priority", 13, I, O, None, 0)])
+    pool = descriptor_pool.DescriptorPool()
+    pool.Add(fd)
+    return message_factory.GetMessageClass(pool.FindMessageTypeByName("ps.PBMeta"))
+
+
+def test_codec_bytes_equal_protobuf():
+    from ps_lite_b200 import host
+    PBMeta = _pb_classes()
+    rng = np.random.default_rng(0)
+    EMPTY = 2**31 - 1
+    for trial in range(200):
+        head = int(rng.integers(-5, 1000)) if trial % 3 else EMPTY
+        app = int(rng.integers(0, 50)) if trial % 2 else EMPTY
+        ts = int(rng.integers(0, 10**6)) if trial % 5 else EMPTY
+        cust = int(rng.integers(0, 4))
+        prio = int(rng.integers(-3, 100))
+        flags = [bool(x) for x in rng.integers(0, 2, 4)]
+        dts = [int(x) for x in rng.integers(0, 12, int(rng.integers(0, 4)))]
+        body = bytes(rng.integers(0, 256, int(rng.integers(0, 30)), dtype=np.uint8))
+        kind = trial % 4  # 0 data, 1 add_node, 2 barrier, 3 ack
+        ref = PBMeta(head=head, request=flags[0], push=flags[1], simple_app=flags[3],
+                     customer_id=cust, pull=flags[2], priority=prio)
+        if app != EMPTY:
+            ref.app_id = app
+        if ts != EMPTY:
+            ref.timestamp = ts
+        if body:
+            ref.body = body
+        ref.data_type.extend(dts)
+        kw = dict(head=head, app_id=app, timestamp=ts, customer_id=cust, priority=prio,
+                  request=flags[0], push=flags[1], pull=flags[2], simple_app=flags[3],
+                  data_types=dts, body=body)
+        if kind == 1:
+            nodes = [dict(role=int(rng.integers(0, 3)), id=int(rng.integers(8, 40)),
+                          hostname=f"10.0.0.{i}", port=int(rng.integers(1000, 60000)),
+                          is_recovery=bool(i % 2), customer_id=i) for i in range(int(rng.integers(1, 5)))]
+            ref.control.cmd = 2
+            for n in nodes:
+                ref.control.node.add(role=n["role"], id=n["id"], hostname=n["hostname"],
+                                     port=n["port"], is_recovery=n["is_recovery"],
+                                     customer_id=n["customer_id"])
+            kw.update(control_cmd=2, nodes=nodes)
+        elif kind == 2:
+            ref.control.cmd = 3
+            ref.control.barrier_group = 7
+            kw.update(control_cmd=3, barrier_group=7)
+        elif kind == 3:
+            sig = int(rng.integers(0, 2**63))
+            ref.control.cmd = 4
+            ref.control.msg_sig = sig
+            kw.update(control_cmd=4, msg_sig=sig)
+        mine = host.encode_meta(**kw)
+        assert mine == ref.SerializeToString(), (trial, mine.hex(), ref.SerializeToString().hex())
+        # and what protobuf writes is read back identically
+        back = host.decode_meta(ref.SerializeToString())
+        assert (back.head, back.customer_id, back.priority) == (head, cust, prio)
+        assert back.app_id == app and back.timestamp == ts
+        assert [back.data_types[i] for i in range(back.num_data_types)] == dts
+        raw = bytes(memoryview(back).cast('B'))[host.MetaStruct.body.offset:][:back.body_len]
+        assert raw == body
+
+
+def test_decode_rejects_garbage():
+    from ps_lite_b200 import host
+    with pytest.raises(host.PSError):
+        host.decode_meta(b"\x0a\xff\xff\xff")  # length runs past the end
+
+
+WORKER_SCRIPT = r'''
+import os, sys
+import numpy as np
+sys.path.insert(0, os.environ["PSB_ROOT"])
+from ps_lite_b200 import host
+host.start(0)
+server = None
+calls = []
+if host.is_server():
+    store = {}
+    def handle(srv, req):
+        # user-defined server-side update written in Python: w -= 0.5 * g
+        out = []
+        for i, k in enumerate(req["keys"]):
+            if req["push"]:
+                store[int(k)] = store.get(int(k), 0.0) - 0.5 * float(req["vals"][i])
+            out.append(store.get(int(k), 0.0))
+        if req["pull"]:
+            srv.respond(req, req["keys"], np.array(out, np.float32))
+        else:
+            srv.respond(req)
+    server = host.KVServer(0, handle if os.environ.get("PSB_PY_HANDLE") == "1" else None)
+if host.is_worker():
+    kv = host.KVWorker(0, 0)
+    n = 1000
+    keys = (np.arange(n, dtype=np.uint64) * np.uint64((2**64 - 1) // n)) + np.uint64(3)
+    vals = np.arange(n, dtype=np.float32)
+    for _ in range(4):
+        kv.wait(kv.push(keys, vals))
+    host.barrier(host.WORKER_GROUP)
+    out = np.zeros(n, np.float32)
+    kv.wait(kv.pull(keys, out))
+    scale = 4 * host.num_workers() * (-0.5 if os.environ.get("PSB_PY_HANDLE") == "1" else 1.0)
+    assert np.allclose(out, scale * vals), (out[:5], vals[:5])
+    out2 = np.zeros(n, np.float32)
+    kv.wait(kv.push_pull(keys, vals, out2))
+    lo, hi = host.server_key_range(0)
+    assert lo == 0 and hi > 0
+    sent, recv = host.traffic()
+    assert sent > n * 12 and recv > 0
+    print("PY_WORKER_OK", host.my_rank(), flush=True)
+    kv.close()
+host.finalize(0)
+if server: server.close()
+'''
+
+
+@pytest.mark.parametrize("py_handle", ["0", "1"], ids=["default-handle", "python-handle"])
+@pytest.mark.parametrize("layout", [dict(num_workers=2, num_servers=2), dict(num_joint=2)],
+                         ids=["separate", "joint"])
+def test_python_binding_push_pull(tmp_path, py_handle, layout):
+    from ps_lite_b200.launch.local import LocalJob
+    script = tmp_path / "node.py"
+    script.write_text(WORKER_SCRIPT)
+    job = LocalJob([sys.executable, str(script)], env={"PSB_ROOT": ROOT, "PSB_PY_HANDLE": py_handle},
+                   capture=True, **layout)
+    job.start()
+    rc = job.wait(120)
+    out = job.output()
+    assert rc == 0 and out.count("PY_WORKER_OK") == 2, out[-3000:]
+
+
+def test_launcher_command_lines(tmp_path):
+    from ps_lite_b200.launch import mpi, ssh, tracker
+    hf = tmp_path / "hosts"
+    hf.write_text("nodeA\nnodeB:2222\n")
+    hosts = ssh.read_hosts(str(hf))
+    assert hosts == [("nodeA", "22"), ("nodeB", "2222")]
+    envs = {"DMLC_NUM_WORKER": "2", "DMLC_NUM_SERVER": "1", "DMLC_PS_ROOT_URI": "10.0.0.1",
+            "DMLC_PS_ROOT_PORT": "9100"}
+    cmds = ssh.build_commands(hosts, 2, 1, envs, ["./prog", "a b"], "/work")
+    assert len(cmds) == 3 and "export DMLC_ROLE=server;" in cmds[0][-1]
+    assert "export DMLC_ROLE=worker;" in cmds[2][-1] and cmds[1][3] == "nodeB"
+    m = mpi.mpirun_commands(2, 1, envs, ["./prog"], flavor="mpich")
+    assert m[0][:3] == ["mpirun", "-n", "1"] and "-env" in m[0]
+    port = tracker.free_port()
+    assert 1024 < port < 65536
+
+
+def test_keepalive_restarts_on_exit_code_254(tmp_path):
+    """A process that exits with 254 is started again with DMLC_NUM_ATTEMPT incremented."""
+    from ps_lite_b200.launch.local import LocalJob
+    marker = tmp_path / "attempts"
+    script = tmp_path / "flaky.py"
+    script.write_text(
+        "import os, sys\n"
+        f"open(r'{marker}', 'a').write(os.environ['DMLC_ROLE'] + os.environ['DMLC_NUM_ATTEMPT'] + '\\n')\n"
+        "sys.exit(254 if os.environ['DMLC_ROLE'] == 'worker' and os.environ['DMLC_NUM_ATTEMPT'] == '0' else 0)\n")
+    job = LocalJob([sys.executable, str(script)], num_workers=1, num_servers=1)
+    job.start()
+    assert job.wait(30) == 0
+    lines = marker.read_text().split()
+    assert "worker0" in lines and "worker1" in lines and "server1" not in lines

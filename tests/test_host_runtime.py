@@ -1,0 +1,161 @@
+"""Host runtime (C++): unit tests and multi-process integration tests on CPU.
+
+The integration programs are the same kind the reference ships (tests/test_*.cc run under
+tests/local.sh: one process per role on one host); here they are built with g++ against
+``include/`` and ``libpsb200_core.so`` and started by the package's local launcher.
+"""
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BIN = os.path.join(ROOT, "build", "tests")
+REF_TESTS = "/root/reference/tests"
+
+
+@pytest.fixture(scope="session")
+def core_lib():
+    from ps_lite_b200 import _build
+    path = _build.build_core()
+    assert path is not None
+    return str(path)
+
+
+def _compile(src, core_lib, out_name=None):
+    os.makedirs(BIN, exist_ok=True)
+    out = os.path.join(BIN, out_name or os.path.splitext(os.path.basename(src))[0])
+    libdir = os.path.dirname(core_lib)
+    deps = [src, core_lib]
+    if os.path.exists(out) and all(os.path.getmtime(out) >= os.path.getmtime(d) for d in deps):
+        return out
+    cmd = ["g++", "-std=c++17", "-O1", "-g", "-I", os.path.join(ROOT, "include"), src, "-o", out,
+           "-L", libdir, "-lpsb200_core", f"-Wl,-rpath,{libdir}", "-pthread"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-4000:]
+    return out
+
+
+def _prog(name, core_lib):
+    return _compile(os.path.join(ROOT, "tests", "cpp", name + ".cc"), core_lib)
+
+
+def _job(cmd, **kw):
+    from ps_lite_b200.launch.local import LocalJob
+    timeout = kw.pop("timeout", 90)
+    job = LocalJob(cmd, capture=True, **kw)
+    job.start()
+    rc = job.wait(timeout)
+    return rc, job.output()
+
+
+def test_unit_core(core_lib):
+    r = subprocess.run([_prog("unit_core", core_lib)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "UNIT_OK" in r.stdout, r.stderr[-3000:]
+
+
+def test_loop_van_single_process(core_lib):
+    r = subprocess.run([_prog("loop_kv", core_lib)], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "LOOP_OK" in r.stderr, r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("env", [{}, {"DMLC_LOCAL": "1"}, {"DMLC_PS_VAN_TYPE": "p3"},
+                                 {"DMLC_PS_VAN_TYPE": "zmq"}],
+                         ids=["tcp", "ipc", "p3", "zmq-alias"])
+def test_config1_separate_roles(core_lib, env):
+    rc, out = _job([_prog("kv_config1", core_lib)], num_workers=2, num_servers=2, env=env)
+    assert rc == 0 and out.count("CONFIG1_OK") == 2, out[-3000:]
+
+
+@pytest.mark.parametrize("n", [1, 2, 4])
+def test_config1_joint_processes(core_lib, n):
+    """Every process is worker and server at once (the layout used with one process per GPU)."""
+    rc, out = _job([_prog("kv_config1", core_lib)], num_joint=n)
+    assert rc == 0 and out.count("CONFIG1_OK") == n, out[-3000:]
+
+
+@pytest.mark.parametrize("layout", [dict(num_workers=3, num_servers=2), dict(num_joint=3)],
+                         ids=["separate", "joint"])
+def test_kv_features(core_lib, layout):
+    rc, out = _job([_prog("kv_features", core_lib)], **layout)
+    assert rc == 0 and out.count("FEATURES_OK") == 3, out[-3000:]
+
+
+def test_two_customers_in_one_worker_process(core_lib):
+    from ps_lite_b200.launch.local import LocalJob
+    job = LocalJob([_prog("multi_customer", core_lib)], num_workers=2, num_servers=2, capture=True)
+    job._spawn("scheduler", 0)
+    job._spawn("server", 0)
+    job._spawn("server", 1)
+    job._spawn("worker", 0)  # one process, two customer threads
+    rc = job.wait(90)
+    out = job.output()
+    assert rc == 0 and "CUSTOMER_OK 0" in out and "CUSTOMER_OK 1" in out, out[-3000:]
+
+
+@pytest.mark.parametrize("repeat", range(3))
+def test_message_loss_with_resend(core_lib, repeat):
+    """10 % of received messages are dropped; ACK/resend/de-duplication must hide it."""
+    env = {"PS_RESEND": "1", "PS_RESEND_TIMEOUT": "100", "PS_DROP_MSG": "10"}
+    rc, out = _job([_prog("kv_config1", core_lib)], num_workers=2, num_servers=2, env=env)
+    assert rc == 0 and out.count("CONFIG1_OK") == 2, out[-3000:]
+    assert "drop message" in out
+
+
+def test_dead_node_detection_and_recovery(core_lib):
+    from ps_lite_b200.launch.local import LocalJob
+    env = {"PS_HEARTBEAT_INTERVAL": "1", "PS_HEARTBEAT_TIMEOUT": "2"}
+    job = LocalJob([_prog("recovery", core_lib)], num_workers=2, num_servers=1, env=env,
+                   capture=True)
+    job._spawn("scheduler", 0)
+    job._spawn("server", 0)
+    job._spawn("worker", 0)
+    victim = job._spawn("worker", 1, extra_env={"PSB_TEST_DIE": "1"})
+    victim["expected_dead"] = True
+    sched = job.procs[0]["proc"]
+    # wait until the scheduler reports the dead worker
+    import selectors
+    sel = selectors.DefaultSelector()
+    sel.register(sched.stdout, selectors.EVENT_READ)
+    dead_id, deadline, buf = None, time.time() + 40, ""
+    os.set_blocking(sched.stdout.fileno(), False)
+    while dead_id is None and time.time() < deadline:
+        if sel.select(timeout=0.2):
+            chunk = sched.stdout.read() or ""
+            buf += chunk
+            for line in buf.splitlines():
+                if line.startswith("DEAD "):
+                    dead_id = int(line.split()[1])
+    job.procs[0]["output"] += buf
+    assert dead_id is not None, "scheduler never reported a dead node\n" + buf[-2000:]
+    os.set_blocking(sched.stdout.fileno(), True)
+    job.spawn_replacement("worker", 1, extra_env={"PSB_TEST_REPLACEMENT": "1"})
+    rc = job.wait(60)
+    out = job.output()
+    assert rc == 0, out[-4000:]
+    assert f"RECOVERED {dead_id}" in out, out[-4000:]
+    assert f"WORKER_DONE {dead_id}" in out
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_TESTS), reason="reference sources not mounted")
+@pytest.mark.parametrize("name", ["test_connection", "test_simple_app", "test_kv_app"])
+def test_reference_programs_build_and_pass_unchanged(core_lib, name):
+    """The reference's own test programs compile against these headers without edits."""
+    exe = _compile(os.path.join(REF_TESTS, name + ".cc"), core_lib, out_name="ref_" + name)
+    rc, out = _job([exe], num_workers=2, num_servers=2)
+    assert rc == 0, out[-3000:]
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_TESTS), reason="reference sources not mounted")
+def test_reference_multi_worker_program(core_lib):
+    from ps_lite_b200.launch.local import LocalJob
+    exe = _compile(os.path.join(REF_TESTS, "test_kv_app_multi_workers.cc"), core_lib,
+                   out_name="ref_multi_workers")
+    job = LocalJob([exe], num_workers=2, num_servers=2, capture=True, role_as_arg=True)
+    job._spawn("scheduler", 0)
+    job._spawn("server", 0)
+    job._spawn("server", 1)
+    job._spawn("worker", 0)
+    assert job.wait(90) == 0, job.output()[-3000:]
