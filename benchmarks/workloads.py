@@ -1,0 +1,110 @@
+"""Model workloads of bench.py: data-parallel ResNet-50 and BERT-large through the
+server-side optimizer (synthetic data, random-init weights)."""
+from __future__ import annotations
+
+import json
+import os
+import time
+
+import torch
+import torch.nn.functional as F
+
+
+def _setup(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    return rank, world, dev
+
+
+def run(args):
+    from ps_lite_b200 import _lib, kvstore
+    from ps_lite_b200.parallel import ServerOptimizer
+    from ps_lite_b200.parallel.optimizer import DistributedOptimizer
+    from ps_lite_b200.utils.timing import ClockSampler, max_over_ranks
+    rank, world, dev = _setup(args)
+    torch.manual_seed(0)
+    torch.backends.cudnn.benchmark = True
+    if args.workload == "resnet50":
+        from ps_lite_b200.models.resnet import ResNet50
+        batch = args.batch or 256
+        model = ResNet50().to(dev).to(memory_format=torch.channels_last)
+        sopt = ServerOptimizer("momentum", lr=0.1, momentum=0.9, scale=1.0 / world)
+        make = lambda: (torch.randn(batch, 3, 224, 224).pin_memory(),
+                        torch.randint(0, 1000, (batch,)).pin_memory())
+        unit, per_step = "img/s", batch
+        metric = "resnet50_train_img_per_s"
+
+        def fwd(x, y):
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                out = model(x.contiguous(memory_format=torch.channels_last))
+            return F.cross_entropy(out.float(), y)
+    else:
+        from ps_lite_b200.models.bert import BertLarge
+        batch, seq = args.batch or 32, 512
+        model = BertLarge().to(dev).to(torch.bfloat16)
+        sopt = ServerOptimizer("adam", lr=1e-4, eps=1e-6, scale=1.0 / world)
+        make = lambda: (torch.randint(0, 30522, (batch, seq)).pin_memory(),
+                        torch.randint(0, 30522, (batch, seq)).pin_memory())
+        unit, per_step = "seq/s", batch
+        metric = "bert_large_train_seq_per_s"
+
+        def fwd(x, y):
+            return model(x, y)
+    nparam = sum(p.numel() for p in model.parameters())
+    ctx = kvstore.init(heap_bytes=nparam * 8 + (256 << 20), device=dev)
+    dopt = DistributedOptimizer(model.parameters(), ctx.heap, sopt, grad_dtype=torch.bfloat16,
+                                num_ctas=args.ctas or 32)
+    hx, hy = make()
+    lib = _lib.device_lib()
+
+    def step():
+        x = hx.to(dev, non_blocking=True)   # host -> device copy of this step's inputs
+        y = hy.to(dev, non_blocking=True)
+        dopt.zero_grad()
+        loss = fwd(x, y)
+        loss.backward()
+        dopt.step()
+        return loss
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    ctx.host_barrier()
+    sampler = ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()
+    l0 = lib.psdev_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    losses = []
+    for _ in range(args.steps):
+        losses.append(float(step().item()))   # device -> host read of the step's loss
+    e1.record()
+    torch.cuda.synchronize()
+    ms = max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    dopt.check()
+    value = world * per_step / (ms * 1e-3)
+    if rank == 0:
+        print(json.dumps({
+            "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "impl": "ours",
+            "config": {"model": args.workload, "global_batch": per_step * world,
+                       "parameters": nparam, "parallelism": f"dp{world}, server-side optimizer",
+                       "slices_per_step": dopt.launched_slices // max(1, dopt.steps),
+                       "timing": "end to end: pinned-host inputs copied in and loss read back "
+                                 "every step"},
+            "loss_first_last": [losses[0], losses[-1]], "clocks": clocks,
+            "gpu_launches": int(lib.psdev_launch_count() - l0)}), flush=True)
+    kvstore.finalize()
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()

@@ -72,6 +72,39 @@ __device__ __forceinline__ void st_v2(void* p, uint2 v) {
   asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
 
+// ---- NVLS (NVSwitch multicast) accesses ------------------------------------------------------
+// `mc` is an address inside the multicast alias of the symmetric heap: a load-reduce returns
+// the element-wise sum over every rank's copy, computed in the switch; a store is replicated
+// into every rank's copy.
+__device__ __forceinline__ uint4 multimem_ld_reduce_f32x4(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+// Eight bf16 values per rank, summed with fp32 accumulation, returned rounded to bf16.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile(
+      "multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+      : "l"(mc)
+      : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_v4(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc),
+               "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void multimem_st_v2(void* mc, uint2 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1,%2};" ::"l"(mc), "r"(v.x),
+               "r"(v.y)
+               : "memory");
+}
+
 // Spin until *flag >= want or the deadline passes.  Returns true on success.
 __device__ __forceinline__ bool wait_flag_ge(const unsigned long long* flag,
                                              unsigned long long want,

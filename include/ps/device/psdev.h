@@ -47,7 +47,10 @@ enum {
 };
 
 /* which halves of the round trip a launch performs */
-enum { PSDEV_OP_PUSH = 1, PSDEV_OP_PULL = 2, PSDEV_OP_PUSHPULL = 3 };
+enum { PSDEV_OP_PUSH = 1, PSDEV_OP_PULL = 2, PSDEV_OP_PUSHPULL = 3,
+       /* PUSH | PUBLISH: push, and write the owned blocks' new values into the owner's own
+        * weight buffer only, for a later pull fused with a GEMM */
+       PSDEV_OP_PUBLISH = 4 };
 
 /* error codes (negative); also stored in the per-channel device status word */
 enum {
@@ -129,8 +132,10 @@ int psdev_channel_clear(void* local_base, int channel);
  *   PULL     : each owner casts its master blocks and stores them into every
  *              worker's weight buffer.
  *   PUSHPULL : both in one pass; the summed gradient never touches memory.
- * `sync` != 0: ranks rendezvous through epoch flags in the heap on `channel`
- * (every rank must issue the same sequence of calls per channel).  `sync` == 0:
+ * `sync` is a bit set.  Bit 1 (value 2): reduce and broadcast through the NVSwitch multicast
+ * alias `w->mc_base` (multimem.ld_reduce / multimem.st) instead of per-peer loads and stores;
+ * ignored when mc_base is NULL.  Bit 0 (value 1) set: ranks rendezvous through epoch flags in the heap on `channel`
+ * (every rank must issue the same sequence of calls per channel).  Bit 0 clear:
  * no flags are touched (used when the caller has already ordered the ranks, and
  * to run all ranks' roles back to back on one GPU).
  * `timeout_ns` bounds every flag wait; on expiry the kernel records an error in
@@ -147,6 +152,21 @@ uint64_t psdev_launch_count(void);
 /* Flag-only rendezvous of all ranks on a channel (device barrier). */
 int psdev_device_barrier(const psdev_world_t* w, int channel, uint64_t timeout_ns,
                          void* stream);
+
+/* ---- bf16 GEMM on tcgen05, alone or fused with the pull of its weights ----------------- */
+/* c[M,N] = x[M,K] * w[N,K]^T; all row-major bf16, 16-byte aligned, N and K multiples of 8. */
+int psdev_gemm_bf16(const void* x, const void* w, void* c, int64_t M, int64_t N, int64_t K,
+                    int num_ctas, uint64_t timeout_ns, void* stream);
+/* Same product where w = elements [w_elem_off, w_elem_off + N*K) of table `t`'s bf16 weight
+ * buffer: copy CTAs fetch the blocks owned by other ranks over NVLink panel by panel while
+ * the tensor cores work on the panels that have landed.  Must follow, on `stream`, a
+ * PUSH|PUBLISH of that range by every rank.  Uses a small per-device scratch block that the
+ * library allocates on first use. */
+int psdev_pull_gemm_bf16(const psdev_world_t* w, const psdev_table_t* t, int64_t w_elem_off,
+                         const void* x, void* c, int64_t M, int64_t N, int64_t K,
+                         int num_copy_ctas, int num_ctas, uint64_t timeout_ns, void* stream);
+/* Reads and clears the error word of the GEMM kernels on the current device (synchronous). */
+int psdev_gemm_status(int32_t* status);
 
 /* Peer bandwidth probe: copies `bytes` from `src` to `dst` with 16 B accesses. */
 int psdev_copy_probe(void* dst, const void* src, size_t bytes, int num_ctas, void* stream);

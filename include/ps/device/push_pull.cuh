@@ -25,6 +25,7 @@ constexpr int kDenseThreads = 512;
 
 struct DenseArgs {
   void* base[PSDEV_MAX_RANKS];
+  void* mc_base;  // multicast alias of the heap (used by the MC kernel variant only)
   int rank, world;
   unsigned long long grad_off, weight_off;
   long long blk, begin, end;
@@ -36,6 +37,7 @@ struct DenseArgs {
   float* s2;
   psdev_opt_t opt;
   int channel, sync;
+  int self_only;  // broadcast stores go to this rank's own weight buffer only (publish)
   unsigned long long timeout_ns;
 };
 
@@ -112,23 +114,25 @@ struct VecOf<__nv_bfloat16> {
   }
 };
 
-template <typename OT, int VEC>
+// Stores VEC weights as OT at dst.  MC: dst is a multicast address (one store reaches every
+// rank's buffer); otherwise an ordinary (local or peer) address.
+template <typename OT, int VEC, bool MC = false>
 __device__ __forceinline__ void store_out(OT* dst, const float* w) {
   if constexpr (sizeof(OT) == 4) {
 #pragma unroll
     for (int q = 0; q < VEC / 4; ++q) {
       uint4 u = make_uint4(__float_as_uint(w[4 * q]), __float_as_uint(w[4 * q + 1]),
                            __float_as_uint(w[4 * q + 2]), __float_as_uint(w[4 * q + 3]));
-      st_v4(dst + 4 * q, u);
+      if constexpr (MC) multimem_st_v4(dst + 4 * q, u); else st_v4(dst + 4 * q, u);
     }
   } else {
     if constexpr (VEC == 8) {
       uint4 u = make_uint4(f2_to_bf16x2(w[0], w[1]), f2_to_bf16x2(w[2], w[3]),
                            f2_to_bf16x2(w[4], w[5]), f2_to_bf16x2(w[6], w[7]));
-      st_v4(dst, u);
+      if constexpr (MC) multimem_st_v4(dst, u); else st_v4(dst, u);
     } else {
       uint2 u = make_uint2(f2_to_bf16x2(w[0], w[1]), f2_to_bf16x2(w[2], w[3]));
-      st_v2(dst, u);
+      if constexpr (MC) multimem_st_v2(dst, u); else st_v2(dst, u);
     }
   }
 }
@@ -234,7 +238,10 @@ struct DenseTile {
   static constexpr int kElems = kDenseThreads * kVec * kUnroll;
 };
 
-template <typename GT, typename OT, class Opt, bool REDUCE, bool BCAST, int WMAX>
+// MC: reduce with one multimem.ld_reduce and broadcast with one multimem.st per vector (the
+// NVSwitch does the fan-in and fan-out); instantiate with WMAX = 1 so that four vectors per
+// thread are in flight.  Otherwise plain loads from and stores to each peer.
+template <typename GT, typename OT, class Opt, bool REDUCE, bool BCAST, int WMAX, bool MC = false>
 __global__ void __launch_bounds__(kDenseThreads)
     dense_kernel(const __grid_constant__ DenseArgs a) {
   constexpr int VEC = DenseVec<GT, OT, REDUCE>::kVec;
@@ -274,12 +281,21 @@ __global__ void __launch_bounds__(kDenseThreads)
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const long long i = i0 + (long long)u * kDenseThreads * VEC;
-#pragma unroll
-          for (int p = 0; p < WMAX; ++p) {
-            if (p < W && live[u]) {
+          if constexpr (MC) {
+            if (live[u]) {
               const GT* src = reinterpret_cast<const GT*>(
-                                  reinterpret_cast<const char*>(a.base[p]) + a.grad_off) + i;
-              gv[u][p] = ld_sys_v4(src);
+                                  reinterpret_cast<const char*>(a.mc_base) + a.grad_off) + i;
+              if constexpr (sizeof(GT) == 4) gv[u][0] = multimem_ld_reduce_f32x4(src);
+              else gv[u][0] = multimem_ld_reduce_bf16x8(src);
+            }
+          } else {
+#pragma unroll
+            for (int p = 0; p < WMAX; ++p) {
+              if (p < W && live[u]) {
+                const GT* src = reinterpret_cast<const GT*>(
+                                    reinterpret_cast<const char*>(a.base[p]) + a.grad_off) + i;
+                gv[u][p] = ld_sys_v4(src);
+              }
             }
           }
         }
@@ -301,7 +317,7 @@ __global__ void __launch_bounds__(kDenseThreads)
           for (int q = 0; q < VEC; ++q) g[q] = 0.f;
 #pragma unroll
           for (int p = 0; p < WMAX; ++p) {
-            if (p < W) {
+            if (MC || p < W) {
               float f[VEC];
               VecOf<GT>::unpack(gv[u][p], f);
 #pragma unroll
@@ -327,10 +343,17 @@ __global__ void __launch_bounds__(kDenseThreads)
           if (live[u]) load_f32<VEC>(a.master + si, w[u]);
         }
       }
-      if constexpr (BCAST) {
+      if constexpr (BCAST && MC) {
+        OT* dst0 = reinterpret_cast<OT*>(reinterpret_cast<char*>(a.mc_base) + a.weight_off);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + (long long)u * kDenseThreads * VEC;
+          if (live[u]) store_out<OT, VEC, true>(dst0 + i, w[u]);
+        }
+      } else if constexpr (BCAST) {
 #pragma unroll
         for (int pp = 0; pp < WMAX; ++pp) {
-          if (pp < W) {
+          if (pp < W && (pp == 0 || !a.self_only)) {
             int p = R + pp;
             if (p >= W) p -= W;
             OT* dst0 = reinterpret_cast<OT*>(reinterpret_cast<char*>(a.base[p]) + a.weight_off);

@@ -79,8 +79,11 @@ class KVWorker : public SimpleApp {
                std::vector<Val>* outs, std::vector<int>* lens = nullptr, int cmd = 0,
                const Callback& cb = nullptr, int priority = 0) {
     CHECK_NOTNULL(outs);
-    if (outs->empty()) outs->resize(vals.size());
-    else CHECK_EQ(vals.size(), outs->size());
+    if (outs->empty()) {
+      outs->resize(vals.size());
+    } else {
+      CHECK_EQ(vals.size(), outs->size());
+    }
     SArray<Key> skeys(keys);
     SArray<Val> svals(vals);
     // zero-copy views of the caller's output storage
@@ -173,19 +176,25 @@ class KVWorker : public SimpleApp {
         // slices must tile the requested keys in order
         CHECK_EQ(s.kvs.keys.front(), keys[static_cast<int>(nkeys)])
             << "pulled slice does not start at the expected key";
-        if (have_prev) CHECK_GT(s.kvs.keys.front(), prev_last);
+        if (have_prev) { CHECK_GT(s.kvs.keys.front(), prev_last); }
         prev_last = s.kvs.keys.back();
         have_prev = true;
         nkeys += s.kvs.keys.size();
         nvals += s.kvs.vals.size();
-        if (lens) CHECK_EQ(s.kvs.lens.size(), s.kvs.keys.size());
+        if (lens) { CHECK_EQ(s.kvs.lens.size(), s.kvs.keys.size()); }
       }
       CHECK_EQ(nkeys, keys.size()) << "lost some servers?";
-      if (vals->empty()) vals->resize(nvals);
-      else CHECK_EQ(vals->size(), nvals);
+      if (vals->empty()) {
+        vals->resize(nvals);
+      } else {
+        CHECK_EQ(vals->size(), nvals);
+      }
       if (lens) {
-        if (lens->empty()) lens->resize(nkeys);
-        else CHECK_EQ(lens->size(), nkeys);
+        if (lens->empty()) {
+          lens->resize(nkeys);
+        } else {
+          CHECK_EQ(lens->size(), nkeys);
+        }
       }
       Val* vdst = vals->data();
       int* ldst = lens ? lens->data() : nullptr;
@@ -313,7 +322,7 @@ class KVWorker : public SimpleApp {
         for (; c < cut[i]; ++c) acc += static_cast<size_t>(send.lens[static_cast<int>(c)]);
         voff[i] = acc;
       }
-      if (!send.vals.empty()) CHECK_EQ(acc, send.vals.size());
+      if (!send.vals.empty()) { CHECK_EQ(acc, send.vals.size()); }
     }
     for (size_t i = 0; i < S; ++i) {
       if (cut[i + 1] == cut[i]) continue;

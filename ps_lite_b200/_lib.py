@@ -18,7 +18,7 @@ IPC_HANDLE_BYTES = 64
 
 F32, BF16 = 0, 1
 OPT_SUM, OPT_SGD, OPT_MOMENTUM, OPT_ADAM, OPT_ASSIGN = 0, 1, 2, 3, 4
-OP_PUSH, OP_PULL, OP_PUSHPULL = 1, 2, 3
+OP_PUSH, OP_PULL, OP_PUSHPULL, OP_PUBLISH = 1, 2, 3, 4
 
 ERR_NAMES = {
     0: "ok", -1: "bad argument", -2: "timeout waiting for peers to enter",
@@ -44,6 +44,14 @@ class Table(C.Structure):
                 ("n", C.c_int64), ("blk", C.c_int64),
                 ("master", C.c_void_p), ("state1", C.c_void_p), ("state2", C.c_void_p),
                 ("grad_dtype", C.c_int32), ("out_dtype", C.c_int32)]
+
+
+class Sparse(C.Structure):
+    _fields_ = [("range", C.c_uint64), ("keys_off", C.c_uint64), ("grads_off", C.c_uint64),
+                ("out_off", C.c_uint64), ("pos_off", C.c_uint64), ("acc_off", C.c_uint64),
+                ("w", C.c_void_p), ("z", C.c_void_p), ("n", C.c_void_p),
+                ("kind", C.c_int32), ("lr", C.c_float), ("alpha", C.c_float),
+                ("beta", C.c_float), ("l1", C.c_float), ("l2", C.c_float)]
 
 
 class PsdevError(RuntimeError):
@@ -80,6 +88,14 @@ def _declare(lib: C.CDLL) -> None:
         "psdev_launch_count": (u64, []),
         "psdev_device_barrier": (i32, [C.POINTER(World), i32, u64, vp]),
         "psdev_copy_probe": (i32, [vp, vp, sz, i32, vp]),
+        "psdev_gemm_bf16": (i32, [vp, vp, vp, i64, i64, i64, i32, u64, vp]),
+        "psdev_pull_gemm_bf16": (i32, [C.POINTER(World), C.POINTER(Table), i64, vp, vp, i64, i64,
+                                       i64, i32, i32, u64, vp]),
+        "psdev_gemm_status": (i32, [C.POINTER(C.c_int32)]),
+        "psdev_key_shard_lookup": (i32, [vp, i64, u64, i32, vp, vp]),
+        "psdev_sparse_scatter": (i32, [C.POINTER(World), C.POINTER(Sparse), i64, i32, vp]),
+        "psdev_sparse_apply": (i32, [C.POINTER(World), C.POINTER(Sparse), i32, vp]),
+        "psdev_sparse_respond": (i32, [C.POINTER(World), C.POINTER(Sparse), i32, vp]),
     }
     for name, (res, args) in sig.items():
         if hasattr(lib, name):

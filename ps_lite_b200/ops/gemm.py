@@ -1,0 +1,58 @@
+"""bf16 GEMM on the tcgen05 tensor cores, alone or fused with the pull of its weights."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from .. import _lib
+
+
+def _stream(dev):
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def gemm_status(device) -> int:
+    """Error word of the last GEMM launches on ``device`` (0 = none); synchronises."""
+    st = C.c_int32()
+    with torch.cuda.device(device):
+        _lib.check(_lib.device_lib().psdev_gemm_status(C.byref(st)), "psdev_gemm_status")
+    return st.value
+
+
+def linear_bf16(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+                num_ctas: int = 0, timeout_s: float = 2.0) -> torch.Tensor:
+    """``out[M,N] = x[M,K] @ w[N,K]^T`` (bf16 in, fp32 accumulate, bf16 out)."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.is_contiguous() and w.is_contiguous() and x.shape[-1] == w.shape[-1]
+    M, K = x.numel() // x.shape[-1], x.shape[-1]
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(*x.shape[:-1], N, dtype=torch.bfloat16, device=x.device)
+    rc = _lib.device_lib().psdev_gemm_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), M, N, K,
+                                           num_ctas, int(timeout_s * 1e9), _stream(x.device))
+    _lib.check(rc, "psdev_gemm_bf16")
+    return out
+
+
+def pull_linear_bf16(table, w_offset: int, n_out: int, x: torch.Tensor,
+                     out: Optional[torch.Tensor] = None, num_copy_ctas: int = 0,
+                     num_ctas: int = 0, timeout_s: float = 2.0) -> torch.Tensor:
+    """Pull ``W = table.weight[w_offset : w_offset + n_out*K]`` (viewed ``[n_out, K]``) from its
+    owners and compute ``x @ W^T`` in the same kernel.
+
+    Must follow, on the same stream, a ``table.push(..., publish=True)`` covering that range.
+    Afterwards ``table.weight`` holds the complete W locally (for the backward pass).
+    """
+    assert x.dtype == torch.bfloat16 and x.is_contiguous()
+    assert table.out_dtype == torch.bfloat16
+    K = x.shape[-1]
+    M = x.numel() // K
+    if out is None:
+        out = torch.empty(*x.shape[:-1], n_out, dtype=torch.bfloat16, device=x.device)
+    rc = _lib.device_lib().psdev_pull_gemm_bf16(
+        C.byref(table._world), C.byref(table._table), int(w_offset), x.data_ptr(), out.data_ptr(),
+        M, n_out, K, num_copy_ctas, num_ctas, int(timeout_s * 1e9), _stream(x.device))
+    _lib.check(rc, "psdev_pull_gemm_bf16")
+    return out

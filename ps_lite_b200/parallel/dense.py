@@ -73,7 +73,7 @@ class DenseTable:
     def __init__(self, heap: SymmetricHeap, n: int, grad_dtype=torch.float32,
                  out_dtype=torch.float32, blk: Optional[int] = None,
                  optimizer: Optional[ServerOptimizer] = None, channel: int = 0,
-                 num_ctas: int = 0):
+                 num_ctas: int = 0, nvls: Optional[bool] = None):
         self.heap = heap
         W = heap.world
         self.n_user = int(n)
@@ -88,6 +88,13 @@ class DenseTable:
         self.optimizer = optimizer or ServerOptimizer("sum")
         self.channel, self.num_ctas = int(channel), int(num_ctas)
         self.step = 0
+        # NVSwitch multicast path: on by default from four ranks up when the heap has a
+        # multicast alias (with two ranks plain peer accesses move fewer bytes per link)
+        if nvls is None:
+            import os
+            env = os.environ.get("PSB200_NVLS")
+            nvls = (W >= 4) if env is None else (env == "1")
+        self.nvls = bool(nvls and heap.mc_base and W > 1)
         gsz = torch.empty((), dtype=grad_dtype).element_size()
         osz = torch.empty((), dtype=out_dtype).element_size()
         self.grad_off = heap.alloc(self.n * gsz)
@@ -146,13 +153,20 @@ class DenseTable:
         tmo = int((timeout_s if timeout_s is not None else default_timeout_s()) * 1e9)
         rc = self.heap.lib.psdev_dense_op(C.byref(self._world), C.byref(self._table), op,
                                           int(begin), int(end), C.byref(o), self.channel,
-                                          self.num_ctas, tmo, 1 if sync else 0, s.cuda_stream)
+                                          self.num_ctas, tmo,
+                                          (1 if sync else 0) | (2 if self.nvls else 0),
+                                          s.cuda_stream)
         _lib.check(rc, "psdev_dense_op")
 
     def push(self, begin: int = 0, end: Optional[int] = None, *, sync: bool = True, stream=None,
-             timeout_s=None, opt_step: bool = True) -> None:
-        """Reduce every worker's ``grad[begin:end]`` into the owners and apply the handle."""
-        self._run(_lib.OP_PUSH, begin, end, sync, stream, timeout_s, opt_step)
+             timeout_s=None, opt_step: bool = True, publish: bool = False) -> None:
+        """Reduce every worker's ``grad[begin:end]`` into the owners and apply the handle.
+
+        ``publish``: owners also store the new values of their blocks into their own
+        ``weight`` buffer, from where a pull fused with a GEMM fetches them.
+        """
+        op = _lib.OP_PUSH | (_lib.OP_PUBLISH if publish else 0)
+        self._run(op, begin, end, sync, stream, timeout_s, opt_step)
 
     def pull(self, begin: int = 0, end: Optional[int] = None, *, sync: bool = True, stream=None,
              timeout_s=None) -> None:

@@ -42,6 +42,7 @@ class SymmetricHeap:
     def __init__(self, nbytes: int, rank: int = 0, world: int = 1, group=None,
                  device: Optional[torch.device] = None,
                  exchange: Optional[Callable[[bytes], Sequence[bytes]]] = None,
+                 backend: str = "auto",
                  _bases: Optional[Sequence[int]] = None, _owner: bool = True):
         if world < 1 or world > _lib.MAX_RANKS:
             raise ValueError(f"world must be in [1, {_lib.MAX_RANKS}]")
@@ -54,10 +55,24 @@ class SymmetricHeap:
         self._opened: list[int] = []
         self._sub = self.lib.psdev_suballoc_new(self.nbytes)
         self._siblings: list["SymmetricHeap"] = []
+        self.mc_base = 0        # NVSwitch multicast alias of the arena (0: none)
+        self._symm = None       # torch symmetric-memory tensor and handle, when used
+        self.backend = "ipc"
         if _bases is not None:  # view created by `emulated`
             self.bases = list(_bases)
             self._base = self.bases[self.rank]
             return
+        if backend == "auto":
+            import os
+            backend = os.environ.get("PSB200_HEAP", "symm" if world > 1 and exchange is None
+                                     else "ipc")
+        if backend == "symm" and world > 1:
+            try:
+                self._init_symm(group)
+                return
+            except Exception as exc:  # fall back to CUDA IPC (no multicast alias then)
+                import warnings
+                warnings.warn(f"symmetric-memory heap unavailable ({exc}); using CUDA IPC")
         with torch.cuda.device(self.device):
             base = C.c_void_p()
             handle = C.create_string_buffer(_lib.IPC_HANDLE_BYTES)
@@ -81,6 +96,28 @@ class SymmetricHeap:
                     _lib.check(self.lib.psdev_heap_open(h, C.byref(ptr)), f"psdev_heap_open({p})")
                     self.bases[p] = ptr.value
                     self._opened.append(ptr.value)
+
+    def _init_symm(self, group) -> None:
+        """Arena from torch's symmetric memory: cuMem allocations exchanged among the ranks
+        and, where the fabric supports it, bound to an NVSwitch multicast object."""
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        grp = group if group is not None else dist.group.WORLD
+        with torch.cuda.device(self.device):
+            t = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+            hdl = symm_mem.rendezvous(t, group=grp)
+            t[: _lib.CTRL_BYTES].zero_()
+            torch.cuda.synchronize()
+        self._symm = (t, hdl)
+        self.bases = [int(p) for p in hdl.buffer_ptrs]
+        self._base = self.bases[self.rank]
+        if self._base != t.data_ptr():
+            raise RuntimeError("symmetric memory handle does not describe the arena")
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        self.mc_base = mc
+        self.backend = "symm"
+        self._owner = False  # torch owns the allocation
+        dist.barrier(group=grp)
 
     # -- single-GPU emulation of a multi-rank job --------------------------------------
     @classmethod
@@ -129,7 +166,7 @@ class SymmetricHeap:
         w.rank, w.world = self.rank, self.world
         for p in range(self.world):
             w.peer_base[p] = self.bases[p]
-        w.mc_base = None
+        w.mc_base = self.mc_base or None
         return w
 
     # -- channel state -----------------------------------------------------------------------

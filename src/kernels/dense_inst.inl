@@ -22,7 +22,20 @@ static int launch_w(DenseArgs a, int num_ctas, cudaStream_t s) {
 }
 
 template <typename GT, typename OT, class Opt, bool RED, bool BC>
+static int launch_mc(DenseArgs a, int num_ctas, cudaStream_t s) {
+  constexpr int tile = DenseTile<GT, OT, RED, 1>::kElems;
+  a.tiles_per_blk = (a.blk + tile - 1) / tile;
+  const long long ntiles = a.n_owned * a.tiles_per_blk;
+  int ctas = num_ctas > 0 ? num_ctas : 2 * 148;
+  if (ntiles < ctas) ctas = ntiles > 0 ? (int)ntiles : 1;
+  dense_kernel<GT, OT, Opt, RED, BC, 1, true><<<ctas, kDenseThreads, 0, s>>>(a);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return (int)cudaGetLastError();
+}
+
+template <typename GT, typename OT, class Opt, bool RED, bool BC>
 static int launch(const DenseArgs& a, int ctas, cudaStream_t s) {
+  if (a.mc_base && a.world > 1) return launch_mc<GT, OT, Opt, RED, BC>(a, ctas, s);
   if (a.world == 1) return launch_w<GT, OT, Opt, RED, BC, 1>(a, ctas, s);
   if (a.world == 2) return launch_w<GT, OT, Opt, RED, BC, 2>(a, ctas, s);
   if (a.world <= 4) return launch_w<GT, OT, Opt, RED, BC, 4>(a, ctas, s);

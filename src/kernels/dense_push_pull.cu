@@ -45,7 +45,15 @@ extern "C" int psdev_dense_op(const psdev_world_t* w, const psdev_table_t* t, in
   a.s2 = t->state2;
   if (opt) a.opt = *opt;
   a.channel = channel;
-  a.sync = sync;
+  a.sync = sync & 1;
+  a.mc_base = (sync & 2) ? w->mc_base : nullptr;  // bit 1: use the NVSwitch multicast alias
+  if (op == (PSDEV_OP_PUSH | PSDEV_OP_PUBLISH)) {
+    // push, and store the new values of the owned blocks into this rank's own weight
+    // buffer, where a later fused pull finds them
+    op = PSDEV_OP_PUSHPULL;
+    a.self_only = 1;
+    a.mc_base = nullptr;
+  }
   a.timeout_ns = timeout_ns;
   // owned blocks meeting [begin, end): indices j in [jb, je] with j % W == R
   a.n_owned = 0;

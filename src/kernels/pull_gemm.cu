@@ -1,0 +1,504 @@
+// C[M,N] = X[M,K] * W[N,K]^T in bf16 with fp32 accumulation on the 5th-generation tensor
+// cores, optionally fused with the pull (all-gather) of W.
+//
+// Structure of one GEMM CTA (256 threads of which six warps have a role; persistent over
+// output tiles):
+//   warp 0      TMA producer: loads 128xBK tiles of X and BNxBK tiles of W into a ring of
+//               shared-memory stages (128-byte swizzle, mbarrier transaction counts);
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x BN x 16 per instruction)
+//               from the stages into one of two fp32 accumulators in tensor memory and
+//               commits stage-free / accumulator-full mbarriers;
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (each warp its 32 lanes),
+//               convert to bf16 and store to C while the next tile is being multiplied.
+//
+// Fusion with pull: W lives in the workers' weight buffer of a dense table; each rank holds
+// the blocks it owns (published by its push).  Extra "copy" CTAs, placed first in the grid so
+// that they never wait behind GEMM CTAs, fetch the remotely owned blocks of W over NVLink
+// with plain peer loads, one BN-row panel at a time, and bump a per-panel counter; the TMA
+// producer of every GEMM CTA waits for the panel of its current tile (and for nothing
+// else), then reads it from local memory with ordinary, non-multicast TMA.  The matrix
+// multiply of panel p therefore overlaps the transfer of panels p+1, p+2, ...
+//
+// The reference has no compute of any kind; the pull it implements (server response plus
+// worker-side reassembly, include/ps/kv_app.h:616-717) is what the copy CTAs replace.
+//
+// Every wait (mbarrier, panel counter) is bounded; on expiry the kernel
+// records an error, lets its in-flight copies land, frees its tensor memory and returns.
+#include <cuda_bf16.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "ps/device/push_pull.cuh"
+#include "ps/device/sm100_ptx.cuh"
+
+namespace psdev {
+extern std::atomic<uint64_t> g_launches;
+
+namespace gemm {
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kThreads = 256;      // warps 0..5 have roles in a GEMM CTA
+constexpr int kCopyThreads = kThreads;
+constexpr int kCopyUnroll = 8;
+constexpr int kMaxPanels = 1024;
+
+// Device scratch of the fused kernel: zero between launches (the last CTA to leave resets it).
+struct Scratch {
+  unsigned int panel_done[kMaxPanels];  // copy CTAs that finished panel p
+  unsigned int ctas_done;
+  int status;  // first error of the last launch that failed (sticky until read)
+};
+
+struct Args {
+  long long M, N, K;
+  __nv_bfloat16* c;
+  Scratch* scratch;
+  unsigned long long timeout_ns;
+  // fused pull
+  int fused, num_copy_ctas;
+  void* base[PSDEV_MAX_RANKS];
+  int rank, world;
+  unsigned long long weight_off;  // heap offset of the table's weight buffer
+  long long w_elem_off;           // first element of W inside the table
+  long long blk;
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void report(Scratch* s, int code) { atomicMin(&s->status, code); }
+
+// ---- copy CTA: all-gather of W, panel by panel ----------------------------------------------
+template <int BN>
+__device__ void copy_role(const Args& a, int copy_idx) {
+  const long long panel_elems = (long long)BN * a.K;
+  const long long total = a.N * a.K;
+  const int npanels = (int)((a.N + BN - 1) / BN);
+  char* mine = reinterpret_cast<char*>(a.base[a.rank]) + a.weight_off;
+  for (int p = 0; p < npanels; ++p) {
+    const long long lo = (long long)p * panel_elems;
+    long long hi = lo + panel_elems;
+    if (hi > total) hi = total;
+    // 16-byte vectors of this panel, interleaved over the copy CTAs
+    const long long nvec = (hi - lo) / 8;
+    const long long stride = (long long)a.num_copy_ctas * kCopyThreads;
+    for (long long v0 = (long long)copy_idx * kCopyThreads + threadIdx.x; v0 < nvec;
+         v0 += stride * kCopyUnroll) {
+      uint4 buf[kCopyUnroll];
+      long long eoff[kCopyUnroll];
+#pragma unroll
+      for (int u = 0; u < kCopyUnroll; ++u) {
+        const long long v = v0 + u * stride;
+        eoff[u] = -1;
+        if (v < nvec) {
+          const long long e = a.w_elem_off + lo + v * 8;  // element index inside the table
+          const int owner = (int)((e / a.blk) % a.world);
+          if (owner != a.rank) {
+            eoff[u] = e * 2;
+            buf[u] = ld_sys_v4(reinterpret_cast<const char*>(a.base[owner]) + a.weight_off + e * 2);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kCopyUnroll; ++u)
+        if (eoff[u] >= 0) st_v4(mine + eoff[u], buf[u]);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      // the panel is read next by TMA (async proxy) from other CTAs
+      fence_proxy_async_global();
+      __threadfence();
+      atomicAdd(&a.scratch->panel_done[p], 1u);
+    }
+  }
+}
+
+__device__ __forceinline__ bool wait_panel(const Args& a, int p, volatile int* abort_flag) {
+  const unsigned int want = (unsigned int)a.num_copy_ctas;
+  const unsigned long long t0 = gtimer_ns();
+  while (ld_acquire_gpu_u32(&a.scratch->panel_done[p]) < want) {
+    if (*abort_flag) return false;
+    if (gtimer_ns() - t0 > a.timeout_ns) {
+      *abort_flag = 1;
+      return false;
+    }
+    __nanosleep(64);
+  }
+  fence_proxy_async_global();
+  return true;
+}
+
+// ---- GEMM CTA ----------------------------------------------------------------------------------
+template <int BN>
+__device__ void gemm_role(const Args& a, const CUtensorMap* tmap_x, const CUtensorMap* tmap_w,
+                          int gemm_idx, int num_gemm_ctas, unsigned char* smem_raw,
+                          volatile int* abort_flag) {
+  using C = Cfg<BN>;
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* full_bar = bars;                     // [kStages]
+  uint64_t* empty_bar = bars + C::kStages;       // [kStages]
+  uint64_t* tmem_full = bars + 2 * C::kStages;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;          // [2]
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long tiles_m = (a.M + BM - 1) / BM;
+  const long long tiles_n = (a.N + BN - 1) / BN;
+  const long long num_tiles = tiles_m * tiles_n;
+  const int num_kb = (int)((a.K + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 128);
+    }
+    fence_barrier_init();
+    prefetch_tmap(tmap_x);
+    prefetch_tmap(tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int armed = 0;  // stages armed in total (for the drain after an abort)
+      int last_panel = -1;
+      bool ok = true;
+      for (long long t = gemm_idx; t < num_tiles && ok; t += num_gemm_ctas) {
+        const int tn = (int)(t / tiles_m), tm = (int)(t % tiles_m);  // panel-major order
+        if (a.fused && tn != last_panel) {
+          ok = wait_panel(a, tn, abort_flag);
+          if (!ok) break;
+          last_panel = tn;
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, a.timeout_ns)) {
+            ok = false;
+            break;
+          }
+          unsigned char* sa = smem + stage * C::kStageBytes;
+          unsigned char* sb = sa + C::kABytes;
+          mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
+          tma_load_2d(sa, tmap_x, kb * BK, tm * BM, &full_bar[stage]);
+          tma_load_2d(sb, tmap_w, kb * BK, tn * BN, &full_bar[stage]);
+          ++armed;
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+        // let the copies that are still in flight land before shared memory is released:
+        // the last min(armed, kStages) stages may still be receiving bytes
+        const int back = armed < C::kStages ? armed : C::kStages;
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < back; ++i) {
+          if (--s < 0) { s = C::kStages - 1; ph ^= 1; }
+          const unsigned long long t0 = gtimer_ns();
+          while (!mbar_try_wait(&full_bar[s], ph) && gtimer_ns() - t0 < 2000000ull) {}
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      long long local = 0;
+      bool ok = true;
+      for (long long t = gemm_idx; t < num_tiles && ok; t += num_gemm_ctas, ++local) {
+        const int acc = (int)(local & 1);
+        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        if (!mbar_wait_bounded(&tmem_empty[acc], acc_phase ^ 1, abort_flag, a.timeout_ns)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, a.timeout_ns)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          unsigned char* sa = smem + stage * C::kStageBytes;
+          const uint64_t da = make_desc_k128(sa);
+          const uint64_t db = make_desc_k128(sa + C::kABytes);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // +2 in the address field = 32 bytes = 16 bf16 along K inside the swizzled row
+            umma_f16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                     (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full[acc]);
+      }
+      if (!ok) report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ================= epilogue (warps 2..5) =================
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+    long long local = 0;
+    bool ok = true;
+    for (long long t = gemm_idx; t < num_tiles && ok; t += num_gemm_ctas, ++local) {
+      const int tn = (int)(t / tiles_m), tm = (int)(t % tiles_m);
+      const int acc = (int)(local & 1);
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag, a.timeout_ns)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const long long row = (long long)tm * BM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + (uint32_t)c0, r);
+        tmem_ld_wait();
+        const long long col = (long long)tn * BN + c0;
+        if (row < a.M) {
+          __nv_bfloat16* dst = a.c + row * a.N + col;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (col + j * 8 + 8 <= a.N) {
+              uint4 u;
+              u.x = f2_to_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+              u.y = f2_to_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              u.z = f2_to_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              u.w = f2_to_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              *reinterpret_cast<uint4*>(dst + j * 8) = u;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tmem_empty[acc]);
+    }
+    if (!ok && lane == 0) report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+  }
+
+  // teardown: everyone is done with tensor memory
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
+}
+
+// Grid: [num_copy_ctas copy CTAs][GEMM CTAs], 256 threads each.  GEMM CTAs use six warps;
+// the last two only take part in the block-wide barriers.
+//
+// No flag is exchanged between ranks here.  The fused form must follow, on the same stream,
+// a push that published the owners' blocks (PSDEV_OP_PUSH | PSDEV_OP_PUBLISH): that kernel
+// returns only after every rank has finished publishing, and the entry rendezvous of the
+// next push on the channel keeps owners from overwriting a shard that a peer still reads.
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+    pull_gemm_kernel(const __grid_constant__ Args a, const __grid_constant__ CUtensorMap tmap_x,
+                     const __grid_constant__ CUtensorMap tmap_w) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ int s_abort;
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  const int ncopy = a.fused ? a.num_copy_ctas : 0;
+  if ((int)blockIdx.x < ncopy) {
+    copy_role<BN>(a, (int)blockIdx.x);
+  } else {
+    gemm_role<BN>(a, &tmap_x, &tmap_w, (int)blockIdx.x - ncopy, (int)gridDim.x - ncopy,
+                  smem_raw, &s_abort);
+  }
+  // the last CTA to leave puts the scratch back to zero for the next launch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = (atomicAdd(&a.scratch->ctas_done, 1u) == gridDim.x - 1);
+    if (s_last) {
+      const int npanels = (int)((a.N + BN - 1) / BN);
+      for (int p = 0; p < npanels; ++p) a.scratch->panel_done[p] = 0;
+      a.scratch->ctas_done = 0;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace gemm
+}  // namespace psdev
+
+// ================================== host side ===================================================
+namespace psdev {
+namespace gemm {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                              const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+            cudaSuccess || q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// Row-major [rows, cols] bf16 tensor, tiles of box_rows x 64 columns, 128-byte swizzle,
+// out-of-bounds elements read as zero.
+static int make_tmap(CUtensorMap* m, const void* ptr, long long rows, long long cols,
+                     int box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return PSDEV_ERR_UNSUPPORTED;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : PSDEV_ERR_ARG;
+}
+
+// One scratch block per device, allocated on first use and kept until the process exits.
+static Scratch* scratch_for_current_device(int* err) {
+  static std::mutex mu;
+  static Scratch* table[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (dev < 0 || dev >= 64) { *err = PSDEV_ERR_ARG; return nullptr; }
+  if (!table[dev]) {
+    Scratch* s = nullptr;
+    cudaError_t e = cudaMalloc(&s, sizeof(Scratch));
+    if (e == cudaSuccess) e = cudaMemset(s, 0, sizeof(Scratch));
+    if (e != cudaSuccess) { *err = (int)e; return nullptr; }
+    table[dev] = s;
+  }
+  return table[dev];
+}
+
+template <int BN>
+static int launch(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, int grid,
+                  cudaStream_t s) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(pull_gemm_kernel<BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg<BN>::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev & 63] = true;
+  }
+  pull_gemm_kernel<BN><<<grid, kThreads, Cfg<BN>::kSmemBytes, s>>>(a, tx, tw);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return (int)cudaGetLastError();
+}
+
+static int run(Args a, const void* x, const void* w, int num_ctas, cudaStream_t s) {
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.N & 7) || (a.K & 7)) return PSDEV_ERR_ARG;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)a.c & 15)) return PSDEV_ERR_ARG;
+  int err = 0;
+  a.scratch = scratch_for_current_device(&err);
+  if (!a.scratch) return err;
+  const int BN = (a.N % 256 == 0 || a.N > 1024) ? 256 : 128;
+  if ((a.N + BN - 1) / BN >= kMaxPanels) return PSDEV_ERR_UNSUPPORTED;
+  CUtensorMap tx, tw;
+  int rc = make_tmap(&tx, x, a.M, a.K, BM);
+  if (rc) return rc;
+  rc = make_tmap(&tw, w, a.N, a.K, BN);
+  if (rc) return rc;
+  int sms = 148;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
+  int gemm_ctas = num_ctas > 0 ? num_ctas : sms;
+  if (a.fused) gemm_ctas = gemm_ctas > a.num_copy_ctas + 1 ? gemm_ctas - a.num_copy_ctas : 1;
+  if (tiles < gemm_ctas) gemm_ctas = (int)tiles;
+  const int grid = gemm_ctas + (a.fused ? a.num_copy_ctas : 0);
+  return BN == 256 ? launch<256>(a, tx, tw, grid, s) : launch<128>(a, tx, tw, grid, s);
+}
+
+}  // namespace gemm
+}  // namespace psdev
+
+using namespace psdev;
+
+extern "C" int psdev_gemm_bf16(const void* x, const void* w, void* c, int64_t M, int64_t N,
+                               int64_t K, int num_ctas, uint64_t timeout_ns, void* stream) {
+  gemm::Args a{};
+  a.M = M; a.N = N; a.K = K;
+  a.c = static_cast<__nv_bfloat16*>(c);
+  a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
+  a.fused = 0;
+  return gemm::run(a, x, w, num_ctas, (cudaStream_t)stream);
+}
+
+extern "C" int psdev_pull_gemm_bf16(const psdev_world_t* w, const psdev_table_t* t,
+                                    int64_t w_elem_off, const void* x, void* c, int64_t M,
+                                    int64_t N, int64_t K, int num_copy_ctas, int num_ctas,
+                                    uint64_t timeout_ns, void* stream) {
+  if (!w || !t || w->world < 1 || w->world > PSDEV_MAX_RANKS) return PSDEV_ERR_ARG;
+  if (t->out_dtype != PSDEV_BF16) return PSDEV_ERR_UNSUPPORTED;
+  if (w_elem_off < 0 || (w_elem_off & 7) || w_elem_off + N * K > t->n) return PSDEV_ERR_ARG;
+  gemm::Args a{};
+  a.M = M; a.N = N; a.K = K;
+  a.c = static_cast<__nv_bfloat16*>(c);
+  a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
+  a.fused = w->world > 1 ? 1 : 0;
+  a.num_copy_ctas = a.fused ? (num_copy_ctas > 0 ? num_copy_ctas : 16) : 0;
+  for (int p = 0; p < w->world; ++p) a.base[p] = w->peer_base[p];
+  a.rank = w->rank;
+  a.world = w->world;
+  a.weight_off = t->weight_off;
+  a.w_elem_off = w_elem_off;
+  a.blk = t->blk;
+  const char* wl = static_cast<const char*>(w->peer_base[w->rank]) + t->weight_off + w_elem_off * 2;
+  return gemm::run(a, x, wl, num_ctas, (cudaStream_t)stream);
+}
+
+// Reads (synchronously) and clears the error word of the GEMM scratch of the current device.
+extern "C" int psdev_gemm_status(int32_t* status) {
+  int err = 0;
+  gemm::Scratch* s = gemm::scratch_for_current_device(&err);
+  if (!s) return err;
+  cudaError_t e = cudaMemcpy(status, &s->status, sizeof(int32_t), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return (int)e;
+  if (*status != 0) e = cudaMemset(&s->status, 0, sizeof(int));
+  return (int)e;
+}

@@ -59,6 +59,9 @@ def main():
             dense_update(ref, grads, kind, lr=0.05, momentum=0.9, eps=1e-6, scale=1.0 / world,
                          step=step, s1=s1, s2=s2)
             tol = dict(rtol=1e-2, atol=1e-2) if odt == torch.bfloat16 else dict(rtol=3e-5, atol=3e-5)
+            if t.nvls and gdt == torch.bfloat16 and odt == torch.float32:
+                # the switch returns the bf16 sum rounded to bf16 (fp32 accumulation inside)
+                tol = dict(rtol=3e-3, atol=3e-3)
             try:
                 torch.testing.assert_close(t.weight[:n].float(), ref[:n].to(odt).float(), **tol)
             except AssertionError as e:
@@ -69,7 +72,8 @@ def main():
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0 and int(flag.item()) == 1:
-        print("MP_DENSE_OK", flush=True)
+        print(f"MP_DENSE_OK heap={ctx.heap.backend} multicast={bool(ctx.heap.mc_base)} "
+              f"nvls_used={kv.tables[0].nvls}", flush=True)
     kvstore.finalize()
     dist.destroy_process_group()
     sys.exit(0 if int(flag.item()) == 1 else 1)

@@ -198,3 +198,16 @@ def test_keepalive_restarts_on_exit_code_254(tmp_path):
     assert job.wait(30) == 0
     lines = marker.read_text().split()
     assert "worker0" in lines and "worker1" in lines and "server1" not in lines
+
+
+def test_p3_scheduler_order():
+    from ps_lite_b200.parallel.optimizer import P3Scheduler
+    s = P3Scheduler(slice_elems=16)
+    assert s.add(0, 40, priority=1) == 3       # [0,16) [16,32) [32,40)
+    assert s.add(100, 116, priority=5) == 1
+    assert s.add(200, 232, priority=1) == 2
+    got = []
+    while len(s):
+        got.append(s.pop())
+    assert got == [(100, 116, 5), (0, 16, 1), (16, 32, 1), (32, 40, 1), (200, 216, 1),
+                   (216, 232, 1)]

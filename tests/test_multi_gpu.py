@@ -25,11 +25,14 @@ def _torchrun(script, nproc, timeout=600, extra_env=None):
     return subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
 
 
-def test_dense_push_pull_across_gpus(cuda_device):
+@pytest.mark.parametrize("nvls", ["0", "1"], ids=["peer-loads", "nvswitch-multicast"])
+def test_dense_push_pull_across_gpus(cuda_device, nvls):
     import torch
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least two GPUs")
     nproc = 8 if n >= 8 else (4 if n >= 4 else 2)
-    r = _torchrun("mp_dense_check.py", nproc)
+    r = _torchrun("mp_dense_check.py", nproc, extra_env={"PSB200_NVLS": nvls})
     assert r.returncode == 0 and "MP_DENSE_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    if nvls == "1" and "multicast=True" in r.stdout:
+        assert "nvls_used=True" in r.stdout

@@ -1,0 +1,79 @@
+"""Sparse push/pull kernels against a plain PyTorch statement of the same update."""
+import pytest
+import torch
+
+from ps_lite_b200.utils.oracle import ftrl_update
+
+pytestmark = pytest.mark.gpu
+
+
+def _zipf_keys(n, key_space, gen, dev):
+    u = torch.rand(4 * n, generator=gen, device=dev, dtype=torch.float64)
+    k = (key_space ** u).to(torch.int64) - 1   # log-uniform: heavy head like a Zipf law
+    k = torch.unique(k.clamp_(0, key_space - 1))
+    k = k[torch.randperm(k.numel(), generator=gen, device=dev)[:n]]
+    return torch.sort(k).values
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("kind", ["sum", "sgd", "ftrl"])
+def test_sparse_push_pull_matches_oracle(cuda_device, world, kind):
+    from ps_lite_b200.parallel import SparseTable, SymmetricHeap
+    key_space, n = 1 << 20, 20000
+    nbytes = 65536 + 20 * n + 4 * ((key_space + world - 1) // world) + (1 << 20)
+    heaps = (SymmetricHeap.emulated(nbytes, world, device=cuda_device) if world > 1
+             else [SymmetricHeap(nbytes, 0, 1, device=cuda_device)])
+    tables = [SparseTable(h, key_space, n, kind=kind, lr=0.1) for h in heaps]
+    gen = torch.Generator(device=cuda_device)
+    gen.manual_seed(11)
+    W = torch.zeros(key_space, device=cuda_device)
+    Z, N = torch.zeros_like(W), torch.zeros_like(W)
+    for step in range(3):
+        reqs = []
+        for t in tables:
+            keys = _zipf_keys(n - 100 * step, key_space, gen, cuda_device)
+            grads = torch.randn(keys.numel(), generator=gen, device=cuda_device) * 0.5
+            t.stage(keys, grads)
+            reqs.append((keys, grads))
+        for t in tables:
+            t.scatter()
+        for t in tables:
+            t.apply()
+        for t in tables:
+            t.respond()
+        torch.cuda.synchronize()
+        # oracle: sum the workers' gradients per key, update the touched keys once
+        G = torch.zeros_like(W)
+        for keys, grads in reqs:
+            G.index_add_(0, keys, grads)
+        touched = torch.zeros(key_space, dtype=torch.bool, device=cuda_device)
+        for keys, _ in reqs:
+            touched[keys] = True
+        idx = touched.nonzero().squeeze(1)
+        if kind == "sum":
+            W[idx] += G[idx]
+        elif kind == "sgd":
+            W[idx] -= 0.1 * G[idx]
+        else:
+            z, nn, w = Z[idx], N[idx], W[idx]
+            ftrl_update(z, nn, w, G[idx])
+            Z[idx], N[idx], W[idx] = z, nn, w
+        for t, (keys, _) in zip(tables, reqs):
+            torch.testing.assert_close(t.out[: keys.numel()], W[keys], rtol=1e-4, atol=1e-5)
+            pos = t.pos[: world + 2].tolist()
+            assert pos[0] == 0 and pos[world] == keys.numel() and pos[world + 1] == keys.numel()
+            assert torch.all(t.acc == 0)  # accumulators are clean for the next step
+
+
+def test_key_shard_lookup(cuda_device):
+    import ctypes as C
+    from ps_lite_b200 import _lib
+    lib = _lib.device_lib()
+    keys = torch.tensor([0, 5, 9, 10, 11, 29, 30, 31, 45], device=cuda_device, dtype=torch.int64)
+    pos = torch.zeros(6, dtype=torch.int64, device=cuda_device)
+    rc = lib.psdev_key_shard_lookup(keys.data_ptr(), keys.numel(), 10, 4, pos.data_ptr(),
+                                    torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    # ranges [0,10) [10,20) [20,30) [30,40); key 45 is beyond the last range
+    assert pos.tolist() == [0, 3, 5, 6, 8, 9]
