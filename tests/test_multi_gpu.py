@@ -36,3 +36,13 @@ def test_dense_push_pull_across_gpus(cuda_device, nvls):
     assert r.returncode == 0 and "MP_DENSE_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
     if nvls == "1" and "multicast=True" in r.stdout:
         assert "nvls_used=True" in r.stdout
+
+
+def test_fused_pull_gemm_sparse_and_training_across_gpus(cuda_device):
+    import torch
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    nproc = 8 if n >= 8 else (4 if n >= 4 else 2)
+    r = _torchrun("mp_fused_check.py", nproc)
+    assert r.returncode == 0 and "MP_FUSED_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
