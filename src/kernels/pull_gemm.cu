@@ -502,3 +502,85 @@ extern "C" int psdev_gemm_status(int32_t* status) {
   if (*status != 0) e = cudaMemset(&s->status, 0, sizeof(int));
   return (int)e;
 }
+
+// ================== variant that allocates nothing (see pull_gemm_noalloc.h) ==================
+#include <cstdio>
+
+#include "kernels/pull_gemm_noalloc.h"
+
+// Scratch of psdev_gemm_bf16_noalloc.  In host code this name is only a handle for
+// cudaGetSymbolAddress: it is not a device address and must never be passed to a kernel.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[PSDEV_NOALLOC_SCRATCH_BYTES];
+static_assert(sizeof(psdev::gemm::Scratch) <= PSDEV_NOALLOC_SCRATCH_BYTES,
+              "static scratch too small for the kernel's counters");
+
+namespace {
+// Device address of g_noalloc_scratch on each device, resolved on the first call there.
+psdev::gemm::Scratch* g_noalloc_ptr[64] = {};
+std::mutex g_noalloc_mu;
+
+int noalloc_scratch(psdev::gemm::Scratch** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return PSDEV_ERR_ARG;
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);  // address on the current device
+    if (e != cudaSuccess) return (int)e;
+    if (!p) return PSDEV_ERR_UNSUPPORTED;
+    g_noalloc_ptr[dev] = static_cast<psdev::gemm::Scratch*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" int psdev_gemm_bf16_noalloc(const void* x, const void* w, void* c, int64_t M,
+                                       int64_t N, int64_t K, int num_ctas, uint64_t timeout_ns,
+                                       int32_t* status_dev, void* stream) {
+  using namespace psdev::gemm;
+  if (M <= 0 || N <= 0 || K <= 0 || (N & 7) || (K & 7)) return PSDEV_ERR_ARG;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)c & 15)) return PSDEV_ERR_ARG;
+  const int BN = (N % 256 == 0 || N > 1024) ? 256 : 128;
+  const int64_t npanels = (N + BN - 1) / BN;
+  if (npanels >= kMaxPanels) {
+    fprintf(stderr,
+            "psdev_gemm_bf16_noalloc: N = %lld needs %lld column panels of %d; the static "
+            "scratch of this entry point holds counters for at most %d panels\n",
+            (long long)N, (long long)npanels, BN, kMaxPanels - 1);
+    return PSDEV_ERR_TOO_LARGE;
+  }
+  Scratch* scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  // the array keeps the previous call's contents: counters and error word start at zero
+  cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(Scratch), s);
+  if (e != cudaSuccess) return (int)e;
+  Args a{};
+  a.M = M; a.N = N; a.K = K;
+  a.c = static_cast<__nv_bfloat16*>(c);
+  a.scratch = scratch;
+  a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
+  a.fused = 0;
+  CUtensorMap tx, tw;
+  rc = make_tmap(&tx, x, M, K, BM);
+  if (rc) return rc;
+  rc = make_tmap(&tw, w, N, K, BN);
+  if (rc) return rc;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long tiles = ((M + BM - 1) / BM) * npanels;
+  int grid = num_ctas > 0 ? num_ctas : sms;
+  if (tiles < grid) grid = (int)tiles;
+  rc = BN == 256 ? launch<256>(a, tx, tw, grid, s) : launch<128>(a, tx, tw, grid, s);
+  if (rc) return rc;
+  if (status_dev) {
+    e = cudaMemcpyAsync(status_dev, &scratch->status, sizeof(int32_t), cudaMemcpyDeviceToDevice, s);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
+}
