@@ -4,6 +4,8 @@
 #include <random>
 #include <thread>
 
+#include "ps/internal/parallel_kv_match.h"
+#include "ps/internal/parallel_sort.h"
 #include "ps/internal/pb_codec.h"
 #include "ps/internal/resender.h"
 #include "ps/internal/threadsafe_pqueue.h"
@@ -291,7 +293,33 @@ static void TestMisc() {
   CHECK_EQ(r.size(), (uint64_t)4);
 }
 
+static void TestSortAndMatch() {
+  std::mt19937_64 rng(3);
+  SArray<Key> a(200000);
+  for (auto& v : a) v = rng();
+  std::vector<Key> ref(a.begin(), a.end());
+  std::sort(ref.begin(), ref.end());
+  ParallelSort(&a, 4);
+  for (size_t i = 0; i < ref.size(); ++i) CHECK_EQ(a[static_cast<int>(i)], ref[i]);
+  SArray<Key> sk, dk;
+  SArray<float> sv;
+  for (Key i = 0; i < 30000; i += 3) { sk.push_back(i); sv.push_back(1.f); sv.push_back(2.f); }
+  for (Key i = 0; i < 30000; i += 2) dk.push_back(i);
+  SArray<float> dv(dk.size() * 2, 10.f);
+  size_t n = ParallelOrderedMatch(sk, sv, dk, &dv, 2, PLUS, 4);
+  CHECK_EQ(n, (size_t)5000);
+  for (size_t j = 0; j < dk.size(); ++j) {
+    const bool hit = dk[static_cast<int>(j)] % 3 == 0;
+    CHECK_EQ(dv[static_cast<int>(2 * j)], hit ? 11.f : 10.f);
+    CHECK_EQ(dv[static_cast<int>(2 * j + 1)], hit ? 12.f : 10.f);
+  }
+  int x = 12;
+  AssignFunc(10, XOR, &x);
+  CHECK_EQ(x, 6);
+}
+
 int main() {
+  TestSortAndMatch();
   TestSArray();
   TestEnv();
   TestQueues();
