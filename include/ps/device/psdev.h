@@ -146,6 +146,16 @@ int psdev_dense_op(const psdev_world_t* w, const psdev_table_t* t, int op,
                    int channel, int num_ctas, uint64_t timeout_ns, int sync,
                    void* stream);
 
+/* Several slices of one table in one launch and one rendezvous.  `segs`: device memory with
+ * `nseg` (<= 1024) triples (begin, end, priority) of int64; a small kernel orders them by
+ * priority (highest first, ties in submission order) and numbers the tiles across slices, so
+ * the CTAs work on the most urgent slice first.  `sched`: device scratch of
+ * psdev_sched_bytes(nseg) bytes. */
+int psdev_dense_op_multi(const psdev_world_t* w, const psdev_table_t* t, int op,
+                         const int64_t* segs, int nseg, void* sched, const psdev_opt_t* opt,
+                         int channel, int num_ctas, uint64_t timeout_ns, int sync, void* stream);
+size_t psdev_sched_bytes(int nseg);
+
 /* Number of kernels this library has launched in this process (for reporting). */
 uint64_t psdev_launch_count(void);
 

@@ -23,6 +23,15 @@ namespace psdev {
 
 constexpr int kDenseThreads = 512;
 
+// One slice of a multi-slice launch, in the order the CTAs consume them (highest priority
+// first).  Entry [nseg] is a sentinel whose tile_begin is the total number of tiles.
+struct SchedEntry {
+  long long begin, end;    // element range of the slice
+  long long first_owned;   // first block of the slice owned by this rank
+  long long n_owned;       // owned blocks that meet the slice
+  long long tile_begin;    // index of the slice's first tile in the launch-wide tile order
+};
+
 struct DenseArgs {
   void* base[PSDEV_MAX_RANKS];
   void* mc_base;  // multicast alias of the heap (used by the MC kernel variant only)
@@ -38,6 +47,9 @@ struct DenseArgs {
   psdev_opt_t opt;
   int channel, sync;
   int self_only;  // broadcast stores go to this rank's own weight buffer only (publish)
+  const SchedEntry* sched;  // multi-slice launch: nseg+1 entries written by the schedule kernel
+  int nseg;                 // 0: single range [begin, end)
+  const long long* segs_in; // multi-slice launch: nseg x (begin, end, priority), device memory
   unsigned long long timeout_ns;
 };
 
@@ -254,18 +266,32 @@ __global__ void __launch_bounds__(kDenseThreads)
   if (a.sync) {
     e = channel_enter(a.base, R, W, a.channel, a.timeout_ns, &s_epoch, &s_err);
   }
-  if (e != 0ull && a.n_owned > 0) {
-    const long long ntiles = a.n_owned * a.tiles_per_blk;
+  const long long ntiles_all =
+      a.nseg > 0 ? a.sched[a.nseg].tile_begin : a.n_owned * a.tiles_per_blk;
+  if (e != 0ull && ntiles_all > 0) {
+    const long long ntiles = ntiles_all;
     for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
-      const long long k = t / a.tiles_per_blk;
-      const long long sub = t - k * a.tiles_per_blk;
-      const long long j = a.first_owned + k * W;  // global block index
+      long long seg_begin = a.begin, seg_end = a.end, first_owned = a.first_owned, tl = t;
+      if (a.nseg > 0) {
+        // tiles are numbered slice after slice in priority order: find this tile's slice
+        int slo = 0, shi = a.nseg - 1;
+        while (slo < shi) {
+          const int mid = (slo + shi + 1) >> 1;
+          if (a.sched[mid].tile_begin <= t) slo = mid; else shi = mid - 1;
+        }
+        const SchedEntry se = a.sched[slo];
+        seg_begin = se.begin; seg_end = se.end; first_owned = se.first_owned;
+        tl = t - se.tile_begin;
+      }
+      const long long k = tl / a.tiles_per_blk;
+      const long long sub = tl - k * a.tiles_per_blk;
+      const long long j = first_owned + k * W;  // global block index
       const long long blk_lo = j * a.blk;
       long long lo = blk_lo + sub * TILE;
       long long hi = lo + TILE;
       const long long blk_hi = blk_lo + a.blk;
       if (hi > blk_hi) hi = blk_hi;
-      if (hi > a.end) hi = a.end;
+      if (hi > seg_end) hi = seg_end;
       // `lo` is not clamped to a.begin: lanes keep their alignment and skip i < begin
       const long long st_base = (j / W) * a.blk - blk_lo;  // state index = st_base + i
       const long long i0 = lo + (long long)threadIdx.x * VEC;
@@ -273,7 +299,7 @@ __global__ void __launch_bounds__(kDenseThreads)
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const long long i = i0 + (long long)u * kDenseThreads * VEC;
-        live[u] = (i < hi) && (i >= a.begin);
+        live[u] = (i < hi) && (i >= seg_begin);
       }
       float w[U][VEC], m[U][VEC], v[U][VEC];
       if constexpr (REDUCE) {

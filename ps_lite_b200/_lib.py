@@ -85,6 +85,9 @@ def _declare(lib: C.CDLL) -> None:
         "psdev_channel_clear": (i32, [vp, i32]),
         "psdev_dense_op": (i32, [C.POINTER(World), C.POINTER(Table), i32, i64, i64,
                                  C.POINTER(Opt), i32, i32, u64, i32, vp]),
+        "psdev_dense_op_multi": (i32, [C.POINTER(World), C.POINTER(Table), i32, vp, i32, vp,
+                                       C.POINTER(Opt), i32, i32, u64, i32, vp]),
+        "psdev_sched_bytes": (sz, [i32]),
         "psdev_launch_count": (u64, []),
         "psdev_device_barrier": (i32, [C.POINTER(World), i32, u64, vp]),
         "psdev_copy_probe": (i32, [vp, vp, sz, i32, vp]),

@@ -178,6 +178,38 @@ class DenseTable:
         """Push and pull in one kernel pass (``ZPushPull``, include/ps/kv_app.h:290-306)."""
         self._run(_lib.OP_PUSHPULL, begin, end, sync, stream, timeout_s, opt_step)
 
+    MAX_SEGS = 1024
+
+    def run_multi(self, op: int, segments, *, sync: bool = True, stream=None, timeout_s=None) -> None:
+        """Run ``op`` on several slices ``(begin, end, priority)`` in one launch and one
+        rendezvous; the kernel's CTAs take the slices in priority order (device-side P3
+        schedule).  At most ``MAX_SEGS`` slices per call."""
+        if not segments:
+            return
+        if len(segments) > self.MAX_SEGS:
+            raise ValueError("too many slices for one launch")
+        s = stream or torch.cuda.current_stream(self.heap.device)
+        if not hasattr(self, "_seg_host"):
+            self._seg_host = torch.empty(self.MAX_SEGS * 3, dtype=torch.int64).pin_memory()
+            self._seg_dev = torch.empty(self.MAX_SEGS * 3, dtype=torch.int64, device=self.heap.device)
+            nb = self.heap.lib.psdev_sched_bytes(self.MAX_SEGS)
+            self._sched_dev = torch.empty(nb, dtype=torch.uint8, device=self.heap.device)
+            self._seg_free = torch.cuda.Event()
+            self._seg_free.record(s)
+        self._seg_free.synchronize()   # the previous launch has read the staging buffer
+        flat = [int(v) for seg in segments for v in seg]
+        self._seg_host[: len(flat)] = torch.tensor(flat, dtype=torch.int64)
+        with torch.cuda.stream(s):
+            self._seg_dev[: len(flat)].copy_(self._seg_host[: len(flat)], non_blocking=True)
+        self._seg_free.record(s)
+        o = self.optimizer.to_struct(max(self.step, 1))
+        tmo = int((timeout_s if timeout_s is not None else default_timeout_s()) * 1e9)
+        rc = self.heap.lib.psdev_dense_op_multi(
+            C.byref(self._world), C.byref(self._table), op, self._seg_dev.data_ptr(),
+            len(segments), self._sched_dev.data_ptr(), C.byref(o), self.channel, self.num_ctas,
+            tmo, (1 if sync else 0) | (2 if self.nvls else 0), s.cuda_stream)
+        _lib.check(rc, "psdev_dense_op_multi")
+
     def check(self) -> None:
         """Raise if a device wait on this table's channel ran out."""
         self.heap.check_channel(self.channel)

@@ -146,10 +146,32 @@ class DistributedOptimizer:
                 self.table.push_pull(b, e, stream=stream, opt_step=False)
             self.launched_slices += 1
 
+    def _drain(self) -> None:
+        """Everything still queued goes out in one launch per kind of operation; the kernel
+        itself takes the slices in priority order (device-side schedule)."""
+        if not len(self.sched):
+            return
+        cur = torch.cuda.current_stream(self.heap.device)
+        stream = self.comm or cur
+        if self.comm is not None:
+            self.comm.wait_stream(cur)
+        both, publish = [], []
+        while True:
+            item = self.sched.pop()
+            if item is None:
+                break
+            (publish if item[2] < 0 else both).append(item)
+        cap = self.table.MAX_SEGS
+        for i in range(0, len(both), cap):
+            self.table.run_multi(_lib.OP_PUSHPULL, both[i:i + cap], stream=stream)
+        for i in range(0, len(publish), cap):
+            self.table.run_multi(_lib.OP_PUSH | _lib.OP_PUBLISH, publish[i:i + cap], stream=stream)
+        self.launched_slices += len(both) + len(publish)
+
     def step(self) -> None:
         """Finish the exchange of this step's gradients; afterwards the parameters hold the
         weights for the next forward pass (except published ones, which their GEMM pulls)."""
-        self._launch(len(self.sched))
+        self._drain()
         if self.comm is not None:
             torch.cuda.current_stream(self.heap.device).wait_stream(self.comm)
         self.steps += 1

@@ -8,6 +8,8 @@
 
 namespace psdev {
 extern std::atomic<uint64_t> g_launches;
+void launch_p3_schedule(const long long* segs, int nseg, long long blk, int world, int rank,
+                        long long tiles_per_blk, SchedEntry* out, cudaStream_t s);
 
 template <typename GT, typename OT, class Opt, bool RED, bool BC, int WMAX>
 static int launch_w(DenseArgs a, int num_ctas, cudaStream_t s) {
@@ -15,7 +17,13 @@ static int launch_w(DenseArgs a, int num_ctas, cudaStream_t s) {
   a.tiles_per_blk = (a.blk + tile - 1) / tile;
   const long long ntiles = a.n_owned * a.tiles_per_blk;
   int ctas = num_ctas > 0 ? num_ctas : 2 * 148;
-  if (ntiles < ctas) ctas = ntiles > 0 ? (int)ntiles : 1;
+  if (a.nseg > 0) {
+    // device-side schedule: slices ordered by priority, tiles numbered across slices
+    launch_p3_schedule(a.segs_in, a.nseg, a.blk, a.world, a.rank, a.tiles_per_blk,
+                       const_cast<SchedEntry*>(a.sched), s);
+  } else if (ntiles < ctas) {
+    ctas = ntiles > 0 ? (int)ntiles : 1;
+  }
   dense_kernel<GT, OT, Opt, RED, BC, WMAX><<<ctas, kDenseThreads, 0, s>>>(a);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return (int)cudaGetLastError();
@@ -27,7 +35,12 @@ static int launch_mc(DenseArgs a, int num_ctas, cudaStream_t s) {
   a.tiles_per_blk = (a.blk + tile - 1) / tile;
   const long long ntiles = a.n_owned * a.tiles_per_blk;
   int ctas = num_ctas > 0 ? num_ctas : 2 * 148;
-  if (ntiles < ctas) ctas = ntiles > 0 ? (int)ntiles : 1;
+  if (a.nseg > 0) {
+    launch_p3_schedule(a.segs_in, a.nseg, a.blk, a.world, a.rank, a.tiles_per_blk,
+                       const_cast<SchedEntry*>(a.sched), s);
+  } else if (ntiles < ctas) {
+    ctas = ntiles > 0 ? (int)ntiles : 1;
+  }
   dense_kernel<GT, OT, Opt, RED, BC, 1, true><<<ctas, kDenseThreads, 0, s>>>(a);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return (int)cudaGetLastError();

@@ -13,11 +13,103 @@ int dense_dispatch_bf16_f32(int op, const DenseArgs& a, int ctas, cudaStream_t s
 int dense_dispatch_f32_bf16(int op, const DenseArgs& a, int ctas, cudaStream_t s);
 }  // namespace psdev
 
+// ---- P3 slice schedule (device side) ----------------------------------------------------------
+// Orders the slices of one launch by priority (highest first, ties in submission order -- the
+// order of the reference's priority send queue, src/p3_van.h:40-50, with FIFO ties) and
+// numbers this rank's tiles across the ordered slices, so that the CTAs of the push/pull
+// kernel, which take tiles in increasing number, work on the most urgent slice first.
+namespace psdev {
+constexpr int kMaxSegs = 1024;
+
+__global__ void p3_slice_schedule_kernel(const long long* segs, int nseg, long long blk, int W,
+                                         int R, long long tiles_per_blk, SchedEntry* out) {
+  __shared__ int order[kMaxSegs];
+  __shared__ long long scan[kMaxSegs];
+  const int i = threadIdx.x;
+  if (i < nseg) {
+    const long long pri = segs[3 * i + 2];
+    int rank = 0;
+    for (int j = 0; j < nseg; ++j) {
+      const long long pj = segs[3 * j + 2];
+      rank += (pj > pri) || (pj == pri && j < i);
+    }
+    order[rank] = i;
+  }
+  __syncthreads();
+  SchedEntry e{};
+  long long tiles = 0;
+  if (i < nseg) {
+    const int s = order[i];
+    e.begin = segs[3 * s];
+    e.end = segs[3 * s + 1];
+    if (e.end > e.begin) {
+      const long long jb = e.begin / blk, je = (e.end - 1) / blk;
+      const long long first = jb + ((R - jb % W) + W) % W;
+      if (first <= je) {
+        e.first_owned = first;
+        e.n_owned = (je - first) / W + 1;
+      }
+    }
+    tiles = e.n_owned * tiles_per_blk;
+  }
+  scan[i] = tiles;
+  __syncthreads();
+  for (int off = 1; off < kMaxSegs; off <<= 1) {
+    const long long t = i >= off ? scan[i - off] : 0;
+    __syncthreads();
+    scan[i] += t;
+    __syncthreads();
+  }
+  if (i < nseg) {
+    e.tile_begin = scan[i] - tiles;
+    out[i] = e;
+  }
+  if (i == nseg - 1) {
+    SchedEntry last{};
+    last.tile_begin = scan[i];
+    out[nseg] = last;
+  }
+}
+
+void launch_p3_schedule(const long long* segs, int nseg, long long blk, int world, int rank,
+                        long long tiles_per_blk, SchedEntry* out, cudaStream_t s) {
+  p3_slice_schedule_kernel<<<1, kMaxSegs, 0, s>>>(segs, nseg, blk, world, rank, tiles_per_blk, out);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+}  // namespace psdev
+
 using namespace psdev;
+
+static int dense_op_impl(const psdev_world_t* w, const psdev_table_t* t, int op, int64_t begin,
+                         int64_t end, const psdev_opt_t* opt, int channel, int num_ctas,
+                         uint64_t timeout_ns, int sync, void* stream, const int64_t* segs,
+                         int nseg, void* sched);
 
 extern "C" int psdev_dense_op(const psdev_world_t* w, const psdev_table_t* t, int op,
                               int64_t begin, int64_t end, const psdev_opt_t* opt, int channel,
                               int num_ctas, uint64_t timeout_ns, int sync, void* stream) {
+  return dense_op_impl(w, t, op, begin, end, opt, channel, num_ctas, timeout_ns, sync, stream,
+                       nullptr, 0, nullptr);
+}
+
+// Several slices in one launch and one rendezvous.  `segs` is device memory holding nseg
+// triples (begin, end, priority), begin/end multiples of 8 inside the table; `sched` is device
+// scratch of psdev_sched_bytes(nseg) bytes.  The slices are consumed in priority order.
+extern "C" int psdev_dense_op_multi(const psdev_world_t* w, const psdev_table_t* t, int op,
+                                    const int64_t* segs, int nseg, void* sched,
+                                    const psdev_opt_t* opt, int channel, int num_ctas,
+                                    uint64_t timeout_ns, int sync, void* stream) {
+  if (!segs || !sched || nseg < 1 || nseg > kMaxSegs) return PSDEV_ERR_ARG;
+  return dense_op_impl(w, t, op, 0, t ? t->n : 0, opt, channel, num_ctas, timeout_ns, sync,
+                       stream, segs, nseg, sched);
+}
+
+extern "C" size_t psdev_sched_bytes(int nseg) { return sizeof(SchedEntry) * (size_t)(nseg + 1); }
+
+static int dense_op_impl(const psdev_world_t* w, const psdev_table_t* t, int op, int64_t begin,
+                         int64_t end, const psdev_opt_t* opt, int channel, int num_ctas,
+                         uint64_t timeout_ns, int sync, void* stream, const int64_t* segs,
+                         int nseg, void* sched) {
   if (!w || !t || w->world < 1 || w->world > PSDEV_MAX_RANKS || w->rank < 0 ||
       w->rank >= w->world)
     return PSDEV_ERR_ARG;
@@ -55,6 +147,9 @@ extern "C" int psdev_dense_op(const psdev_world_t* w, const psdev_table_t* t, in
     a.mc_base = nullptr;
   }
   a.timeout_ns = timeout_ns;
+  a.segs_in = reinterpret_cast<const long long*>(segs);
+  a.nseg = nseg;
+  a.sched = static_cast<const SchedEntry*>(sched);
   // owned blocks meeting [begin, end): indices j in [jb, je] with j % W == R
   a.n_owned = 0;
   a.first_owned = 0;

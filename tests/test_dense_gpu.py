@@ -141,3 +141,35 @@ def test_world1_sync_flags_advance_epoch(cuda_device):
     assert heap.channel_status(1) == (0, 5)
     assert torch.all(t.weight[:100_000] == 5.0)
     heap.close()
+
+
+@pytest.mark.parametrize("world", [1, 8])
+def test_multi_slice_launch_with_device_schedule(cuda_device, world):
+    """Many slices with priorities in one launch equal one whole-table push+pull."""
+    from ps_lite_b200 import _lib
+    from ps_lite_b200.parallel import ServerOptimizer
+    torch.manual_seed(21)
+    n = 300_000
+    opt = ServerOptimizer("adam", lr=0.01, eps=1e-6)
+    heaps, tables = _mk_tables(world, n, torch.bfloat16, torch.float32, 1024, opt, cuda_device)
+    npad = tables[0].n
+    w0 = torch.randn(npad, device=cuda_device)
+    grads = []
+    for t in tables:
+        t.load_master(w0)
+        g = torch.randn(npad, device=cuda_device).to(torch.bfloat16)
+        t.grad.copy_(g)
+        grads.append(g)
+    # uneven slices, some empty of owned blocks for some ranks, shuffled priorities
+    cuts = sorted(set([0, npad] + [int(x) & ~7 for x in torch.randint(0, npad, (60,)).tolist()]))
+    segs = [(b, e, (i * 7) % 13) for i, (b, e) in enumerate(zip(cuts[:-1], cuts[1:]))]
+    for t in tables:
+        t.step = 1
+        t.run_multi(_lib.OP_PUSHPULL, segs, sync=False)
+    torch.cuda.synchronize()
+    ref = dense_update(w0.clone(), grads, "adam", lr=0.01, eps=1e-6, step=1,
+                       s1=torch.zeros_like(w0), s2=torch.zeros_like(w0))
+    for t in tables:
+        torch.testing.assert_close(t.weight[:n], ref[:n], rtol=2e-5, atol=2e-5)
+    for h in heaps:
+        h.close()
