@@ -87,14 +87,29 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.rounds):
-            step()
-        e1.record()
+        if args.graph:
+            # the rounds are captured once and replayed: launch cost leaves the measurement
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(args.rounds):
+                    step()
+            graph.replay()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            graph.replay()
+            e1.record()
+        else:
+            e0.record()
+            for _ in range(args.rounds):
+                step()
+            e1.record()
         torch.cuda.synchronize()
         ms = max_over_ranks(e0.elapsed_time(e1), dev) / args.rounds
         if rank == 0:
-            print(json.dumps({"impl": args.impl, "dtype": args.dtype, "n_gpus": world,
+            print(json.dumps({"impl": args.impl, "dtype": args.dtype, "n_gpus": world, "graph": bool(args.graph),
                               "bytes": n * isz, "us_per_round": round(ms * 1e3, 2),
                               "goodput_GBps_per_gpu": round(2 * n * isz / (ms * 1e-3) / 1e9, 2)}),
                   flush=True)

@@ -48,3 +48,21 @@ def test_sort_unique_sum_and_ordered_match(cuda_device):
     si = torch.full((src_keys.numel(),), 0b1010, device=cuda_device, dtype=torch.int32)
     assert K.ordered_match(src_keys, si, dst_keys, di, op=K.XOR) == 1000
     assert torch.all(di[hit] == 0b0110) and torch.all(di[~hit] == 0b1100)
+
+
+def test_filters(cuda_device):
+    from ps_lite_b200.ops import filters as F
+    torch.manual_seed(0)
+    x = torch.randn(100_003, device=cuda_device) * 3
+    b = F.cast_scale(x, torch.bfloat16, 0.5)
+    torch.testing.assert_close(b.float(), (x * 0.5).to(torch.bfloat16).float())
+    torch.testing.assert_close(F.cast_scale(b, torch.float32, 2.0), b.float() * 2.0)
+    q, sc = F.int8_pack(x)
+    pad = torch.zeros(sc.numel() * 256, device=cuda_device)
+    pad[: x.numel()] = x
+    ref_scale = pad.view(-1, 256).abs().amax(dim=1) / 127
+    torch.testing.assert_close(sc, ref_scale)
+    y = F.int8_unpack(q, sc)
+    assert (y - x).abs().max() <= ref_scale.max() * 0.5 + 1e-6
+    z = F.int8_unpack(q, sc, out=y.clone(), accumulate=True)
+    torch.testing.assert_close(z, 2 * y)
