@@ -178,6 +178,34 @@ class DenseTable:
         """Push and pull in one kernel pass (``ZPushPull``, include/ps/kv_app.h:290-306)."""
         self._run(_lib.OP_PUSHPULL, begin, end, sync, stream, timeout_s, opt_step)
 
+    # -- checkpoint of the server shard ----------------------------------------------------
+    def save(self, path: str) -> None:
+        """Write this rank's shard (master weights, optimizer state, step) to ``path``.
+
+        The reference keeps server state inside the user's request handle and has no
+        checkpoint facility (its users send a "save model" ``cmd``); here each server shard
+        is one file whose header records the key layout it belongs to."""
+        torch.cuda.synchronize(self.heap.device)
+        torch.save({"n": self.n_user, "blk": self.blk, "world": self.heap.world,
+                    "rank": self.heap.rank, "step": self.step, "kind": self.optimizer.kind,
+                    "master": self.master.cpu(),
+                    "state1": None if self.state1 is None else self.state1.cpu(),
+                    "state2": None if self.state2 is None else self.state2.cpu()}, path)
+
+    def load(self, path: str) -> None:
+        """Restore a shard written by :meth:`save` for the same layout (a recovered node calls
+        this, then every rank pulls)."""
+        ck = torch.load(path, map_location="cpu")
+        if (ck["n"], ck["blk"], ck["world"], ck["rank"]) != (self.n_user, self.blk,
+                                                             self.heap.world, self.heap.rank):
+            raise ValueError("checkpoint belongs to a different table layout or rank")
+        self.master.copy_(ck["master"])
+        if self.state1 is not None and ck["state1"] is not None:
+            self.state1.copy_(ck["state1"])
+        if self.state2 is not None and ck["state2"] is not None:
+            self.state2.copy_(ck["state2"])
+        self.step = int(ck["step"])
+
     MAX_SEGS = 1024
 
     def run_multi(self, op: int, segments, *, sync: bool = True, stream=None, timeout_s=None) -> None:

@@ -98,3 +98,21 @@ class SparseTable:
 
     def check(self) -> None:
         self.heap.check_channel(self.barrier_channel)
+
+    def save(self, path: str) -> None:
+        """Write this rank's key range (values and FTRL state) to ``path``."""
+        torch.cuda.synchronize(self.heap.device)
+        torch.save({"key_space": self.key_space, "world": self.heap.world, "rank": self.heap.rank,
+                    "kind": self.kind, "w": self.w.cpu(),
+                    "z": None if self.z is None else self.z.cpu(),
+                    "n": None if self.n is None else self.n.cpu()}, path)
+
+    def load(self, path: str) -> None:
+        ck = torch.load(path, map_location="cpu")
+        if (ck["key_space"], ck["world"], ck["rank"]) != (self.key_space, self.heap.world,
+                                                          self.heap.rank):
+            raise ValueError("checkpoint belongs to a different key layout or rank")
+        self.w.copy_(ck["w"])
+        if self.z is not None and ck["z"] is not None:
+            self.z.copy_(ck["z"])
+            self.n.copy_(ck["n"])

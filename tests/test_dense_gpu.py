@@ -173,3 +173,26 @@ def test_multi_slice_launch_with_device_schedule(cuda_device, world):
         torch.testing.assert_close(t.weight[:n], ref[:n], rtol=2e-5, atol=2e-5)
     for h in heaps:
         h.close()
+
+
+def test_shard_checkpoint_round_trip(cuda_device, tmp_path):
+    """Saving a shard, training on, then loading puts the server back to the saved state."""
+    from ps_lite_b200.parallel import DenseTable, ServerOptimizer, SymmetricHeap
+    heap = SymmetricHeap(8 << 20, 0, 1, device=cuda_device)
+    t = DenseTable(heap, 50_000, optimizer=ServerOptimizer("adam", lr=0.1), blk=1024)
+    t.load_master(torch.randn(50_000, device=cuda_device))
+    t.grad.copy_(torch.randn(t.n, device=cuda_device))
+    t.push_pull()
+    path = str(tmp_path / "shard0.pt")
+    t.save(path)
+    saved = (t.master.clone(), t.state1.clone(), t.state2.clone(), t.step)
+    t.push_pull()
+    t.push_pull()
+    t.load(path)
+    assert t.step == saved[3]
+    for a, b in zip((t.master, t.state1, t.state2), saved[:3]):
+        assert torch.equal(a, b)
+    t.pull()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(t.weight[:50_000], saved[0][:50_000])
+    heap.close()
