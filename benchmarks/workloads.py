@@ -34,7 +34,7 @@ def run(args):
         from ps_lite_b200.models.resnet import ResNet50
         batch = args.batch or 256
         model = ResNet50().to(dev).to(memory_format=torch.channels_last)
-        sopt = ServerOptimizer("momentum", lr=0.1, momentum=0.9, scale=1.0 / world)
+        sopt = ServerOptimizer("momentum", lr=0.01, momentum=0.9, scale=1.0 / world)
         make = lambda: (torch.randn(batch, 3, 224, 224).pin_memory(),
                         torch.randint(0, 1000, (batch,)).pin_memory())
         unit, per_step = "img/s", batch

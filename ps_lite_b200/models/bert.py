@@ -51,6 +51,11 @@ class BertLarge(nn.Module):
         self.head = nn.Linear(hidden, hidden)
         self.head_ln = nn.LayerNorm(hidden)
         self.decoder_bias = nn.Parameter(torch.zeros(vocab))
+        for m in self.modules():
+            if isinstance(m, (nn.Linear, nn.Embedding)):
+                nn.init.normal_(m.weight, std=0.02)
+            if isinstance(m, nn.Linear) and m.bias is not None:
+                nn.init.zeros_(m.bias)
 
     def forward(self, ids, labels=None):
         B, S = ids.shape
