@@ -38,9 +38,12 @@ def main():
     ap.add_argument("--shapes", default="16384x3072x1024,16384x1024x1024,16384x4096x1024,8192x8192x8192,2048x3072x1024")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--ctas", type=int, default=0)
+    ap.add_argument("--tile", type=int, default=0, help="output tile height: 128, 256, 0 = auto")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
+    from ps_lite_b200 import _lib
+    _lib.check(_lib.device_lib().psdev_gemm_config(args.tile), "psdev_gemm_config")
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(os.path.dirname(__file__), "..", "MEASURED_PEAKS.json")))
@@ -58,7 +61,7 @@ def main():
         lib = timed(lambda: torch.matmul(x, w.t(), out=ref_out), args.iters, dev)
         err = (out.float() - ref_out.float()).abs().max().item()
         fl = 2.0 * M * N * K
-        print(json.dumps({"shape": [M, N, K], "ours_us": round(ours * 1e3, 1),
+        print(json.dumps({"shape": [M, N, K], "tile": args.tile, "ours_us": round(ours * 1e3, 1),
                           "cublas_us": round(lib * 1e3, 1),
                           "ours_tflops": round(fl / ours / 1e9, 1),
                           "cublas_tflops": round(fl / lib / 1e9, 1),

@@ -58,8 +58,16 @@ def run(args):
             return model(x, y)
     nparam = sum(p.numel() for p in model.parameters())
     ctx = kvstore.init(heap_bytes=nparam * 8 + (256 << 20), device=dev)
+    fused = args.workload == "bert"
     dopt = DistributedOptimizer(model.parameters(), ctx.heap, sopt, grad_dtype=torch.bfloat16,
-                                num_ctas=args.ctas or 32)
+                                num_ctas=args.ctas or 32, publish_first=1 if fused else 0)
+    if fused:
+        # the first GEMM that consumes pulled weights (layer-0 QKV) pulls them itself
+        from ps_lite_b200.ops.gemm import pull_linear
+        qkv_w = model.layers[0].qkv.weight
+        assert dopt.params[0] is qkv_w
+        off = dopt.offset_of(qkv_w)
+        model.layers[0].qkv_fn = lambda x: pull_linear(x, qkv_w, dopt.table, off)
     hx, hy = make()
     lib = _lib.device_lib()
 
@@ -100,6 +108,7 @@ def run(args):
             "config": {"model": args.workload, "global_batch": per_step * world,
                        "parameters": nparam, "parallelism": f"dp{world}, server-side optimizer",
                        "slices_per_step": dopt.launched_slices // max(1, dopt.steps),
+                       "pull_fused_with_first_gemm": bool(fused),
                        "timing": "end to end: pinned-host inputs copied in and loss read back "
                                  "every step"},
             "loss_first_last": [losses[0], losses[-1]], "clocks": clocks,

@@ -56,3 +56,32 @@ def pull_linear_bf16(table, w_offset: int, n_out: int, x: torch.Tensor,
         M, n_out, K, num_copy_ctas, num_ctas, int(timeout_s * 1e9), _stream(x.device))
     _lib.check(rc, "psdev_pull_gemm_bf16")
     return out
+
+
+class _PullLinearFn(torch.autograd.Function):
+    """``x @ W^T`` where W is pulled from its owners inside the GEMM kernel.
+
+    ``weight`` is the parameter whose storage is the table's weight slice: the kernel fills
+    it while multiplying, so the backward pass can use it as an ordinary local tensor."""
+
+    @staticmethod
+    def forward(ctx, x, weight, table, w_offset):
+        n_out, k = weight.shape
+        x2 = x.reshape(-1, k).contiguous()
+        out = pull_linear_bf16(table, w_offset, n_out, x2)
+        ctx.save_for_backward(x2, weight)
+        ctx.x_shape = x.shape
+        return out.view(*x.shape[:-1], n_out)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, weight.shape[0])
+        dx = (dy2 @ weight).view(ctx.x_shape)
+        dw = dy2.t() @ x2
+        return dx, dw, None, None
+
+
+def pull_linear(x: torch.Tensor, weight: torch.nn.Parameter, table, w_offset: int) -> torch.Tensor:
+    """Differentiable form of :func:`pull_linear_bf16` for a parameter stored in ``table``."""
+    return _PullLinearFn.apply(x, weight, table, w_offset)

@@ -27,6 +27,7 @@
 #include <cuda_bf16.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 #include "ps/device/push_pull.cuh"
@@ -92,8 +93,8 @@ __device__ void copy_role(const Args& a, int copy_idx) {
     if (hi > total) hi = total;
     // 16-byte vectors of this panel, interleaved over the copy CTAs
     const long long nvec = (hi - lo) / 8;
-    const long long stride = (long long)a.num_copy_ctas * kCopyThreads;
-    for (long long v0 = (long long)copy_idx * kCopyThreads + threadIdx.x; v0 < nvec;
+    const long long stride = (long long)a.num_copy_ctas * blockDim.x;
+    for (long long v0 = (long long)copy_idx * blockDim.x + threadIdx.x; v0 < nvec;
          v0 += stride * kCopyUnroll) {
       uint4 buf[kCopyUnroll];
       long long eoff[kCopyUnroll];
@@ -316,6 +317,236 @@ __device__ void gemm_role(const Args& a, const CUtensorMap* tmap_x, const CUtens
   if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
 }
 
+// ---- GEMM CTA, 256 x 256 output tile ------------------------------------------------------------
+// Same roles as gemm_role, but the CTA owns a 256 x 256 tile: per k-block it loads 256 rows of
+// X and 256 rows of W (64 KB) and issues two M=128 MMAs per K step, one per half of the rows,
+// into two 256-column accumulators that fill all 512 tensor-memory columns.  An SM can read
+// 64 bytes per clock from L2; a 128 x 256 tile needs 96 bytes per tensor-pipe clock and is
+// therefore capped near two thirds of the tensor peak, while this shape needs exactly 64.
+// The price is that the accumulators are not double buffered: the epilogue of a tile is only
+// overlapped with the next tile's first k-blocks half by half, so eight warps drain it.
+constexpr int kThreads256 = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+
+struct Cfg256 {
+  static constexpr int BN = 256, BM2 = 256;
+  static constexpr int kABytes = BM2 * BK * 2;   // 32 KB
+  static constexpr int kBBytes = BN * BK * 2;    // 32 KB
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = 3;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+__device__ void gemm_role_256(const Args& a, const CUtensorMap* tmap_x, const CUtensorMap* tmap_w,
+                              int gemm_idx, int num_gemm_ctas, unsigned char* smem_raw,
+                              volatile int* abort_flag) {
+  using C = Cfg256;
+  constexpr int BN = C::BN, BM2 = C::BM2;
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* full_bar = bars;                    // [kStages]
+  uint64_t* empty_bar = bars + C::kStages;      // [kStages]
+  uint64_t* tmem_full = bars + 2 * C::kStages;  // [1]: both halves of the tile are complete
+  uint64_t* tmem_empty = tmem_full + 1;         // [2]: half h has been drained
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long tiles_m = (a.M + BM2 - 1) / BM2;
+  const long long tiles_n = (a.N + BN - 1) / BN;
+  const long long num_tiles = tiles_m * tiles_n;
+  const int num_kb = (int)((a.K + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tmem_full[0], 1);
+    mbar_init(&tmem_empty[0], 256);  // all eight epilogue warps arrive once per half
+    mbar_init(&tmem_empty[1], 256);
+    fence_barrier_init();
+    prefetch_tmap(tmap_x);
+    prefetch_tmap(tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int armed = 0, last_panel = -1;
+      bool ok = true;
+      for (long long t = gemm_idx; t < num_tiles && ok; t += num_gemm_ctas) {
+        const int tn = (int)(t / tiles_m), tm = (int)(t % tiles_m);
+        if (a.fused && tn != last_panel) {
+          ok = wait_panel(a, tn, abort_flag);
+          if (!ok) break;
+          last_panel = tn;
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, a.timeout_ns)) {
+            ok = false;
+            break;
+          }
+          unsigned char* sa = smem + stage * C::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[stage], C::kStageBytes);
+          tma_load_2d(sa, tmap_x, kb * BK, tm * BM2, &full_bar[stage]);
+          tma_load_2d(sa + C::kABytes, tmap_w, kb * BK, tn * BN, &full_bar[stage]);
+          ++armed;
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+        const int back = armed < C::kStages ? armed : C::kStages;
+        int s = stage;
+        uint32_t ph = phase;
+        for (int i = 0; i < back; ++i) {
+          if (--s < 0) { s = C::kStages - 1; ph ^= 1; }
+          const unsigned long long t0 = gtimer_ns();
+          while (!mbar_try_wait(&full_bar[s], ph) && gtimer_ns() - t0 < 2000000ull) {}
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      long long local = 0;
+      bool ok = true;
+      for (long long t = gemm_idx; t < num_tiles && ok; t += num_gemm_ctas, ++local) {
+        const uint32_t drained = (uint32_t)(local & 1) ^ 1;  // parity of the previous drain
+        if (!mbar_wait_bounded(&tmem_empty[0], drained, abort_flag, a.timeout_ns)) {
+          ok = false;
+          break;
+        }
+        bool half1_free = false;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, a.timeout_ns)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          unsigned char* sa = smem + stage * C::kStageBytes;
+          const uint64_t da0 = make_desc_k128(sa);
+          const uint64_t da1 = make_desc_k128(sa + 128 * BK * 2);
+          const uint64_t db = make_desc_k128(sa + C::kABytes);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_f16(tmem_base, da0 + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                     (kb | k) != 0 ? 1u : 0u);
+          if (!half1_free) {
+            // the second half may still be draining from the previous tile
+            if (!mbar_wait_bounded(&tmem_empty[1], drained, abort_flag, a.timeout_ns)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            half1_free = true;
+          }
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_f16(tmem_base + (uint32_t)BN, da1 + (uint64_t)(2 * k), db + (uint64_t)(2 * k),
+                     idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(&empty_bar[stage]);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(&tmem_full[0]);
+      }
+      if (!ok) report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+    }
+    __syncwarp();
+  } else {
+    // epilogue: warp w reads lane quarter (w & 3); warps 2..5 take columns [0,128) of each
+    // half, warps 6..9 columns [128,256)
+    const int q = warp & 3;
+    const int col_half = (warp - 2) >> 2;
+    long long local = 0;
+    bool ok = true;
+    for (long long t = gemm_idx; t < num_tiles && ok; t += num_gemm_ctas, ++local) {
+      const int tn = (int)(t / tiles_m), tm = (int)(t % tiles_m);
+      if (!mbar_wait_bounded(&tmem_full[0], (uint32_t)(local & 1), abort_flag, a.timeout_ns)) {
+        ok = false;
+        break;
+      }
+      __syncwarp();
+      tc_fence_after();
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        const long long row = (long long)tm * BM2 + h * 128 + q * 32 + lane;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * BN);
+#pragma unroll 1
+        for (int c0 = col_half * 128; c0 < col_half * 128 + 128; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + (uint32_t)c0, r);
+          tmem_ld_wait();
+          const long long col = (long long)tn * BN + c0;
+          if (row < a.M) {
+            __nv_bfloat16* dst = a.c + row * a.N + col;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (col + j * 8 + 8 <= a.N) {
+                uint4 u;
+                u.x = f2_to_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+                u.y = f2_to_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+                u.z = f2_to_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+                u.w = f2_to_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+                *reinterpret_cast<uint4*>(dst + j * 8) = u;
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&tmem_empty[h]);  // 256 arrivals (8 warps) free half h for the next tile
+      }
+    }
+    if (!ok && lane == 0) report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, C::kTmemCols);
+}
+
+__global__ void __launch_bounds__(kThreads256, 1)
+    pull_gemm256_kernel(const __grid_constant__ Args a, const __grid_constant__ CUtensorMap tmap_x,
+                        const __grid_constant__ CUtensorMap tmap_w) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ int s_abort;
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  const int ncopy = a.fused ? a.num_copy_ctas : 0;
+  if ((int)blockIdx.x < ncopy) {
+    copy_role<256>(a, (int)blockIdx.x);
+  } else {
+    gemm_role_256(a, &tmap_x, &tmap_w, (int)blockIdx.x - ncopy, (int)gridDim.x - ncopy, smem_raw,
+                  &s_abort);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = (atomicAdd(&a.scratch->ctas_done, 1u) == gridDim.x - 1);
+    if (s_last) {
+      const int npanels = (int)((a.N + 255) / 256);
+      for (int p = 0; p < npanels; ++p) a.scratch->panel_done[p] = 0;
+      a.scratch->ctas_done = 0;
+      __threadfence();
+    }
+  }
+}
+
 // Grid: [num_copy_ctas copy CTAs][GEMM CTAs], 256 threads each.  GEMM CTAs use six warps;
 // the last two only take part in the block-wide barriers.
 //
@@ -429,16 +660,50 @@ static int launch(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, i
   return (int)cudaGetLastError();
 }
 
+static int launch256(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, int grid,
+                     cudaStream_t s) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(pull_gemm256_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg256::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev & 63] = true;
+  }
+  pull_gemm256_kernel<<<grid, kThreads256, Cfg256::kSmemBytes, s>>>(a, tx, tw);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return (int)cudaGetLastError();
+}
+
+// Output-tile height used by run(): 128 (double-buffered accumulators) or 256 (twice the
+// reuse of W per byte loaded).  0 = choose by shape.
+static std::atomic<int> g_tile_m{0};
+
+static int pick_tile_m(long long M, long long N) {
+  int t = g_tile_m.load();
+  if (t == 0) {
+    const char* e = getenv("PSB200_GEMM_TILE");
+    t = e ? atoi(e) : 0;
+  }
+  if (t == 128 || t == 256) return (t == 256 && N >= 256 && M >= 256) ? 256 : 128;
+  // by shape: the tall tile pays off once there are several waves of 256 x 256 tiles
+  const long long tiles256 = ((M + 255) / 256) * ((N + 255) / 256);
+  return (N >= 256 && tiles256 >= 4 * 148) ? 256 : 128;
+}
+
 static int run(Args a, const void* x, const void* w, int num_ctas, cudaStream_t s) {
   if (a.M <= 0 || a.N <= 0 || a.K <= 0 || (a.N & 7) || (a.K & 7)) return PSDEV_ERR_ARG;
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)a.c & 15)) return PSDEV_ERR_ARG;
   int err = 0;
   a.scratch = scratch_for_current_device(&err);
   if (!a.scratch) return err;
-  const int BN = (a.N % 256 == 0 || a.N > 1024) ? 256 : 128;
+  const int tile_m = pick_tile_m(a.M, a.N);
+  const int BN = (tile_m == 256 || a.N % 256 == 0 || a.N > 1024) ? 256 : 128;
   if ((a.N + BN - 1) / BN >= kMaxPanels) return PSDEV_ERR_UNSUPPORTED;
   CUtensorMap tx, tw;
-  int rc = make_tmap(&tx, x, a.M, a.K, BM);
+  int rc = make_tmap(&tx, x, a.M, a.K, tile_m);
   if (rc) return rc;
   rc = make_tmap(&tw, w, a.N, a.K, BN);
   if (rc) return rc;
@@ -446,11 +711,12 @@ static int run(Args a, const void* x, const void* w, int num_ctas, cudaStream_t 
   int dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const long long tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
+  const long long tiles = ((a.M + tile_m - 1) / tile_m) * ((a.N + BN - 1) / BN);
   int gemm_ctas = num_ctas > 0 ? num_ctas : sms;
   if (a.fused) gemm_ctas = gemm_ctas > a.num_copy_ctas + 1 ? gemm_ctas - a.num_copy_ctas : 1;
   if (tiles < gemm_ctas) gemm_ctas = (int)tiles;
   const int grid = gemm_ctas + (a.fused ? a.num_copy_ctas : 0);
+  if (tile_m == 256) return launch256(a, tx, tw, grid, s);
   return BN == 256 ? launch<256>(a, tx, tw, grid, s) : launch<128>(a, tx, tw, grid, s);
 }
 
@@ -490,6 +756,14 @@ extern "C" int psdev_pull_gemm_bf16(const psdev_world_t* w, const psdev_table_t*
   a.blk = t->blk;
   const char* wl = static_cast<const char*>(w->peer_base[w->rank]) + t->weight_off + w_elem_off * 2;
   return gemm::run(a, x, wl, num_ctas, (cudaStream_t)stream);
+}
+
+// Selects the output-tile height of later GEMM launches: 128, 256, or 0 for the built-in
+// choice by shape.
+extern "C" int psdev_gemm_config(int tile_m) {
+  if (tile_m != 0 && tile_m != 128 && tile_m != 256) return PSDEV_ERR_ARG;
+  gemm::g_tile_m.store(tile_m);
+  return 0;
 }
 
 // Reads (synchronously) and clears the error word of the GEMM scratch of the current device.

@@ -9,10 +9,14 @@ def _ref(x, w):
     return (x.float() @ w.float().t())
 
 
+@pytest.mark.parametrize("tile", [128, 256])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 128, 192),
-                                   (1000, 392, 520), (2048, 3072, 1024), (130, 264, 72)])
-def test_gemm_matches_fp32_matmul(cuda_device, M, N, K):
+                                   (1000, 392, 520), (2048, 3072, 1024), (130, 264, 72),
+                                   (4096, 1024, 512)])
+def test_gemm_matches_fp32_matmul(cuda_device, M, N, K, tile):
+    from ps_lite_b200 import _lib
     from ps_lite_b200.ops.gemm import gemm_status, linear_bf16
+    assert _lib.device_lib().psdev_gemm_config(tile) == 0
     torch.manual_seed(M + N + K)
     x = torch.randn(M, K, device=cuda_device).to(torch.bfloat16)
     w = (torch.randn(N, K, device=cuda_device) / K ** 0.5).to(torch.bfloat16)
@@ -20,14 +24,18 @@ def test_gemm_matches_fp32_matmul(cuda_device, M, N, K):
     torch.cuda.synchronize()
     assert gemm_status(cuda_device) == 0
     torch.testing.assert_close(out.float(), _ref(x, w), rtol=2e-2, atol=2e-2)
+    _lib.device_lib().psdev_gemm_config(0)
 
 
+@pytest.mark.parametrize("tile", [128, 256])
 @pytest.mark.parametrize("world,blk", [(2, 4096), (4, 1024), (8, 4096)])
-def test_pull_fused_gemm_emulated_ranks(cuda_device, world, blk):
+def test_pull_fused_gemm_emulated_ranks(cuda_device, world, blk, tile):
     """All ranks' heaps on one GPU: rank r's kernel pulls the other ranks' blocks of W and
     multiplies; every rank must get x @ W^T and end with the complete W in its weight buffer."""
+    from ps_lite_b200 import _lib
     from ps_lite_b200.ops.gemm import gemm_status, pull_linear_bf16
     from ps_lite_b200.parallel import DenseTable, ServerOptimizer, SymmetricHeap
+    assert _lib.device_lib().psdev_gemm_config(tile) == 0
     torch.manual_seed(world)
     M, N, K = 512, 768, 256
     pad = 1024  # W does not start at the beginning of the table
@@ -55,3 +63,4 @@ def test_pull_fused_gemm_emulated_ranks(cuda_device, world, blk):
         torch.testing.assert_close(out.float(), _ref(x, W), rtol=2e-2, atol=2e-2)
         torch.testing.assert_close(t.weight[pad:pad + N * K].float(), W.reshape(-1).float(),
                                    rtol=1e-2, atol=1e-2)
+    _lib.device_lib().psdev_gemm_config(0)
