@@ -51,7 +51,8 @@ class Sparse(C.Structure):
                 ("out_off", C.c_uint64), ("pos_off", C.c_uint64), ("acc_off", C.c_uint64),
                 ("w", C.c_void_p), ("z", C.c_void_p), ("n", C.c_void_p),
                 ("kind", C.c_int32), ("lr", C.c_float), ("alpha", C.c_float),
-                ("beta", C.c_float), ("l1", C.c_float), ("l2", C.c_float)]
+                ("beta", C.c_float), ("l1", C.c_float), ("l2", C.c_float),
+                ("hkeys_off", C.c_uint64), ("capacity", C.c_uint64), ("overflow", C.c_void_p)]
 
 
 class PsdevError(RuntimeError):

@@ -24,27 +24,40 @@ class SparseTable:
 
     def __init__(self, heap: SymmetricHeap, key_space: int, max_keys: int, kind: str = "ftrl",
                  lr: float = 0.01, alpha: float = 0.1, beta: float = 1.0, l1: float = 1.0,
-                 l2: float = 1.0, barrier_channel: int = _lib.NUM_CHANNELS - 2):
+                 l2: float = 1.0, barrier_channel: int = _lib.NUM_CHANNELS - 2,
+                 hash_capacity: int = 0):
         self.heap = heap
         W = heap.world
         self.key_space, self.max_keys, self.kind = int(key_space), int(max_keys), kind
         self.range = (self.key_space + W - 1) // W
+        # store: direct index (one slot per key of the range) or, with hash_capacity > 0, an
+        # open-addressing table of that many slots per server for huge or unbounded key spaces
+        self.capacity = 0
+        if hash_capacity:
+            self.capacity = 1 << (int(hash_capacity) - 1).bit_length()
+        slots = self.capacity or self.range
         self.keys_off = heap.alloc(8 * max_keys)
         self.grads_off = heap.alloc(4 * max_keys)
         self.out_off = heap.alloc(4 * max_keys)
         self.pos_off = heap.alloc(8 * (W + 2))
-        self.acc_off = heap.alloc(4 * self.range)
+        self.acc_off = heap.alloc(4 * slots)
+        self.hkeys_off = heap.alloc(8 * self.capacity) if self.capacity else 0
         self.keys = heap.tensor(self.keys_off, max_keys, torch.int64)  # bit pattern of uint64
         self.grads = heap.tensor(self.grads_off, max_keys, torch.float32)
         self.out = heap.tensor(self.out_off, max_keys, torch.float32)
         self.pos = heap.tensor(self.pos_off, W + 2, torch.int64)
-        self.acc = heap.tensor(self.acc_off, self.range, torch.float32)
+        self.acc = heap.tensor(self.acc_off, slots, torch.float32)
+        self.hkeys = (heap.tensor(self.hkeys_off, self.capacity, torch.int64)
+                      if self.capacity else None)
+        if self.hkeys is not None:
+            self.hkeys.fill_(-1)   # all ones = empty slot
         self.acc.zero_()
         self.pos.zero_()
         dev = heap.device
-        self.w = torch.zeros(self.range, dtype=torch.float32, device=dev)
-        self.z = torch.zeros(self.range, dtype=torch.float32, device=dev) if kind == "ftrl" else None
-        self.n = torch.zeros(self.range, dtype=torch.float32, device=dev) if kind == "ftrl" else None
+        self.w = torch.zeros(slots, dtype=torch.float32, device=dev)
+        self.z = torch.zeros(slots, dtype=torch.float32, device=dev) if kind == "ftrl" else None
+        self.n = torch.zeros(slots, dtype=torch.float32, device=dev) if kind == "ftrl" else None
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
         self._world = heap.world_struct()
         t = _lib.Sparse()
         t.range = self.range
@@ -55,6 +68,8 @@ class SparseTable:
         t.n = self.n.data_ptr() if self.n is not None else None
         t.kind = _KINDS[kind]
         t.lr, t.alpha, t.beta, t.l1, t.l2 = lr, alpha, beta, l1, l2
+        t.hkeys_off, t.capacity = self.hkeys_off, self.capacity
+        t.overflow = self.overflow.data_ptr()
         self._t = t
         self.barrier_channel = barrier_channel
         self.count = 0
@@ -98,6 +113,8 @@ class SparseTable:
 
     def check(self) -> None:
         self.heap.check_channel(self.barrier_channel)
+        if self.capacity and int(self.overflow.item()):
+            raise RuntimeError("sparse hash store is full: raise hash_capacity")
 
     def save(self, path: str) -> None:
         """Write this rank's key range (values and FTRL state) to ``path``."""

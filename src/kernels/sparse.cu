@@ -37,12 +37,62 @@ struct SparseArgs {
   float* z;                      // FTRL z (or NULL)
   float* nacc;                   // FTRL n (or NULL)
   long long n;                   // keys in this worker's request
+  // hash store (capacity != 0): slots are found by open addressing in a key table that lives
+  // in the owner's heap, so that workers can claim slots with remote compare-and-swap
+  unsigned long long hkeys_off;  // heap: u64[capacity], all ones = empty
+  unsigned long long capacity;   // power of two, or 0 for the direct-index store
+  int* overflow;                 // local: set to 1 if a table ran out of slots
   int kind;                      // 0 sum, 1 sgd, 2 ftrl
   float lr, alpha, beta, l1, l2;
 };
 
 __device__ __forceinline__ char* heap(const SparseArgs& a, int r) {
   return reinterpret_cast<char*>(a.base[r]);
+}
+
+constexpr unsigned long long kEmptyKey = ~0ull;
+
+__device__ __forceinline__ unsigned long long mix64(unsigned long long k) {
+  k ^= k >> 33; k *= 0xff51afd7ed558ccdull; k ^= k >> 33; k *= 0xc4ceb9fe1a85ec53ull; k ^= k >> 33;
+  return k;
+}
+// Slot of `key` in the owner's table, claiming an empty slot if the key is new.  `tab` may be
+// peer memory: the claim is a system-scope compare-and-swap.  -1 if the table is full.
+__device__ __forceinline__ long long slot_find_or_insert(unsigned long long* tab,
+                                                         unsigned long long cap,
+                                                         unsigned long long key) {
+  unsigned long long h = mix64(key) & (cap - 1);
+  for (unsigned long long probes = 0; probes < cap; ++probes) {
+    unsigned long long cur;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(cur) : "l"(tab + h) : "memory");
+    if (cur == key) return (long long)h;
+    if (cur == kEmptyKey) {
+      cur = atomicCAS_system(tab + h, kEmptyKey, key);
+      if (cur == kEmptyKey || cur == key) return (long long)h;
+    }
+    h = (h + 1) & (cap - 1);
+  }
+  return -1;
+}
+__device__ __forceinline__ long long slot_find(const unsigned long long* tab,
+                                               unsigned long long cap, unsigned long long key) {
+  unsigned long long h = mix64(key) & (cap - 1);
+  for (unsigned long long probes = 0; probes < cap; ++probes) {
+    unsigned long long cur;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(cur) : "l"(tab + h) : "memory");
+    if (cur == key) return (long long)h;
+    if (cur == kEmptyKey) return -1;
+    h = (h + 1) & (cap - 1);
+  }
+  return -1;
+}
+// Index of `key` in the state arrays of server `rank`.
+__device__ __forceinline__ long long state_index(const SparseArgs& a, int rank,
+                                                 unsigned long long key, bool insert) {
+  if (a.capacity == 0) return (long long)(key - (unsigned long long)rank * a.range);
+  unsigned long long* tab =
+      reinterpret_cast<unsigned long long*>(reinterpret_cast<char*>(a.base[rank]) + a.hkeys_off);
+  return insert ? slot_find_or_insert(tab, a.capacity, key) : slot_find(tab, a.capacity, key);
 }
 
 // K1: pos[s] = first index whose key >= s*range, for s = 0..world; pos[world+1] = n.
@@ -82,7 +132,12 @@ __global__ void sparse_scatter_kernel(const __grid_constant__ SparseArgs a) {
     const unsigned long long k = keys[i];
     const unsigned long long s = k / a.range;
     if (s >= (unsigned long long)a.world) continue;  // outside every range: dropped
-    float* acc = reinterpret_cast<float*>(heap(a, (int)s) + a.acc_off) + (k - s * a.range);
+    const long long idx = state_index(a, (int)s, k, true);
+    if (idx < 0) {
+      *a.overflow = 1;
+      continue;
+    }
+    float* acc = reinterpret_cast<float*>(heap(a, (int)s) + a.acc_off) + idx;
     asm volatile("red.relaxed.sys.global.add.f32 [%0], %1;" ::"l"(acc), "f"(grads[i]) : "memory");
   }
 }
@@ -105,7 +160,8 @@ __global__ void sparse_apply_kernel(const __grid_constant__ SparseArgs a) {
          i += (long long)gridDim.x * blockDim.x) {
       unsigned long long k;
       asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(k) : "l"(keys + i) : "memory");
-      const unsigned long long idx = k - (unsigned long long)a.rank * a.range;
+      const long long idx = state_index(a, a.rank, k, false);
+      if (idx < 0) continue;  // the key found no slot (table full): reported by the scatter
       const float g = atomicExch(acc + idx, 0.f);
       if (g == 0.f) continue;  // already applied for another worker, or nothing to add
       if (a.kind == 0) {
@@ -139,7 +195,8 @@ __global__ void sparse_respond_kernel(const __grid_constant__ SparseArgs a) {
          i += (long long)gridDim.x * blockDim.x) {
       unsigned long long k;
       asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(k) : "l"(keys + i) : "memory");
-      out[i] = a.w[k - (unsigned long long)a.rank * a.range];
+      const long long idx = state_index(a, a.rank, k, false);
+      out[i] = idx >= 0 ? a.w[idx] : 0.f;
     }
   }
 }
@@ -158,6 +215,9 @@ typedef struct {
   float* n;
   int32_t kind;
   float lr, alpha, beta, l1, l2;
+  uint64_t hkeys_off; /* hash store: heap offset of the u64 key table (filled with 0xff) */
+  uint64_t capacity;  /* hash store: slots per server, power of two; 0 = direct index   */
+  int32_t* overflow;  /* hash store: device int set to 1 when a table is full           */
 } psdev_sparse_t;
 
 static int fill(SparseArgs* a, const psdev_world_t* w, const psdev_sparse_t* t, int64_t n) {
@@ -171,6 +231,10 @@ static int fill(SparseArgs* a, const psdev_world_t* w, const psdev_sparse_t* t, 
   a->w = t->w; a->z = t->z; a->nacc = t->n;
   a->n = n; a->kind = t->kind;
   a->lr = t->lr; a->alpha = t->alpha; a->beta = t->beta; a->l1 = t->l1; a->l2 = t->l2;
+  a->hkeys_off = t->hkeys_off;
+  a->capacity = t->capacity;
+  a->overflow = t->overflow;
+  if (t->capacity && ((t->capacity & (t->capacity - 1)) || !t->overflow)) return PSDEV_ERR_ARG;
   return 0;
 }
 

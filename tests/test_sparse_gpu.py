@@ -15,15 +15,17 @@ def _zipf_keys(n, key_space, gen, dev):
     return torch.sort(k).values
 
 
+@pytest.mark.parametrize("store", ["direct", "hash"])
 @pytest.mark.parametrize("world", [1, 2, 8])
 @pytest.mark.parametrize("kind", ["sum", "sgd", "ftrl"])
-def test_sparse_push_pull_matches_oracle(cuda_device, world, kind):
+def test_sparse_push_pull_matches_oracle(cuda_device, world, kind, store):
     from ps_lite_b200.parallel import SparseTable, SymmetricHeap
     key_space, n = 1 << 20, 20000
-    nbytes = 65536 + 20 * n + 4 * ((key_space + world - 1) // world) + (1 << 20)
+    cap = (1 << 17) if store == "hash" else 0
+    nbytes = 65536 + 20 * n + 4 * ((key_space + world - 1) // world) + 12 * cap + (1 << 20)
     heaps = (SymmetricHeap.emulated(nbytes, world, device=cuda_device) if world > 1
              else [SymmetricHeap(nbytes, 0, 1, device=cuda_device)])
-    tables = [SparseTable(h, key_space, n, kind=kind, lr=0.1) for h in heaps]
+    tables = [SparseTable(h, key_space, n, kind=kind, lr=0.1, hash_capacity=cap) for h in heaps]
     gen = torch.Generator(device=cuda_device)
     gen.manual_seed(11)
     W = torch.zeros(key_space, device=cuda_device)
@@ -63,6 +65,7 @@ def test_sparse_push_pull_matches_oracle(cuda_device, world, kind):
             pos = t.pos[: world + 2].tolist()
             assert pos[0] == 0 and pos[world] == keys.numel() and pos[world + 1] == keys.numel()
             assert torch.all(t.acc == 0)  # accumulators are clean for the next step
+            t.check()
 
 
 def test_key_shard_lookup(cuda_device):
