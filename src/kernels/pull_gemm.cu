@@ -547,6 +547,216 @@ __global__ void __launch_bounds__(kThreads256, 1)
   }
 }
 
+// ---- GEMM on CTA pairs (tcgen05 cta_group::2) -------------------------------------------------
+// Two CTAs of a 2-CTA cluster own one 256 x 256 output tile: CTA r of the pair loads rows
+// [r*128, r*128+128) of the X tile and of the W tile (32 KB per k-block instead of 48 KB, i.e.
+// the 64 bytes per tensor-pipe clock an SM can take from L2), keeps the accumulators of its
+// 128 rows in its own tensor memory (two buffers of 256 columns, so the epilogue overlaps the
+// next tile), and the even CTA issues one M=256 MMA per K step for both.  Loads carry no
+// cluster multicast: each CTA fetches its own halves; only the completion counts and the
+// MMA-done signals cross between the two CTAs.
+struct CfgPair {
+  static constexpr int BN = 256;
+  static constexpr int kABytes = 128 * BK * 2;  // this CTA's 128 rows of X
+  static constexpr int kBBytes = 128 * BK * 2;  // this CTA's 128 rows of W
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = 6;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+__device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const CUtensorMap* tmap_w,
+                               int pair_idx, int num_pairs, unsigned char* smem_raw,
+                               volatile int* abort_flag) {
+  using C = CfgPair;
+  constexpr int BN = C::BN;
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* full_bar = bars;                    // [kStages]  used in the leader CTA
+  uint64_t* empty_bar = bars + C::kStages;      // [kStages]  one copy per CTA
+  uint64_t* tmem_full = bars + 2 * C::kStages;  // [2]        one copy per CTA
+  uint64_t* tmem_empty = tmem_full + 2;         // [2]        used in the leader CTA
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader
+  const long long tiles_m = (a.M + 255) / 256;
+  const long long tiles_n = (a.N + BN - 1) / BN;
+  const long long num_tiles = tiles_m * tiles_n;
+  const int num_kb = (int)((a.K + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);   // the leader's arrive.expect_tx; bytes come from both CTAs
+      mbar_init(&empty_bar[s], 1);  // the leader's commit, delivered to both CTAs
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], 256);  // 128 epilogue threads of each CTA
+    }
+    fence_barrier_init();
+    prefetch_tmap(tmap_x);
+    prefetch_tmap(tmap_w);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_base_slot, C::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // both CTAs' barriers exist before anything can signal them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ================= TMA producer (both CTAs) =================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int last_panel = -1;
+      bool ok = true;
+      for (long long t = pair_idx; t < num_tiles && ok; t += num_pairs) {
+        const int tn = (int)(t / tiles_m), tm = (int)(t % tiles_m);
+        if (a.fused && tn != last_panel) {
+          ok = wait_panel(a, tn, abort_flag);
+          if (!ok) break;
+          last_panel = tn;
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag, a.timeout_ns)) {
+            ok = false;
+            break;
+          }
+          unsigned char* sa = smem + stage * C::kStageBytes;
+          if (cta == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * C::kStageBytes);
+          tma_load_2d_pair(sa, tmap_x, kb * BK, tm * 256 + (int)cta * 128, &full_bar[stage]);
+          tma_load_2d_pair(sa + C::kABytes, tmap_w, kb * BK, tn * BN + (int)cta * 128,
+                           &full_bar[stage]);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ================= MMA issuer (leader CTA only) =================
+    if (lane == 0 && cta == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(256, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      long long local = 0;
+      bool ok = true;
+      for (long long t = pair_idx; t < num_tiles && ok; t += num_pairs, ++local) {
+        const int acc = (int)(local & 1);
+        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        if (!mbar_wait_bounded(&tmem_empty[acc], acc_phase ^ 1, abort_flag, a.timeout_ns)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag, a.timeout_ns)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          unsigned char* sa = smem + stage * C::kStageBytes;
+          const uint64_t da = make_desc_k128(sa);
+          const uint64_t db = make_desc_k128(sa + C::kABytes);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_f16_pair(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                          (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(&empty_bar[stage]);  // frees the stage in both CTAs
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair(&tmem_full[acc]);  // wakes the epilogues of both CTAs
+      }
+      if (!ok) report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ================= epilogue (warps 2..5 of both CTAs) =================
+    const int q = warp & 3;
+    long long local = 0;
+    bool ok = true;
+    for (long long t = pair_idx; t < num_tiles && ok; t += num_pairs, ++local) {
+      const int tn = (int)(t / tiles_m), tm = (int)(t % tiles_m);
+      const int acc = (int)(local & 1);
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag, a.timeout_ns)) {
+        ok = false;
+        break;
+      }
+      __syncwarp();
+      tc_fence_after();
+      const long long row = (long long)tm * 256 + (long long)cta * 128 + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + (uint32_t)c0, r);
+        tmem_ld_wait();
+        const long long col = (long long)tn * BN + c0;
+        if (row < a.M) {
+          __nv_bfloat16* dst = a.c + row * a.N + col;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (col + j * 8 + 8 <= a.N) {
+              uint4 u;
+              u.x = f2_to_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+              u.y = f2_to_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              u.z = f2_to_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              u.w = f2_to_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              *reinterpret_cast<uint4*>(dst + j * 8) = u;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_leader(&tmem_empty[acc]);  // counted on the leader, where the MMAs are issued
+    }
+    if (!ok && lane == 0) report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+  }
+
+  // teardown: neither CTA may free its tensor memory while the other might still be used by
+  // a pair MMA, so the whole cluster meets first
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, C::kTmemCols);
+}
+
+// Grid: [copy CTAs (even count)][GEMM CTA pairs], clusters of 2 along x.
+__global__ void __launch_bounds__(kThreads, 1)
+    pull_gemm_pair_kernel(const __grid_constant__ Args a, const __grid_constant__ CUtensorMap tmap_x,
+                          const __grid_constant__ CUtensorMap tmap_w) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ int s_abort;
+  __shared__ int s_last;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  const int ncopy = a.fused ? a.num_copy_ctas : 0;
+  if ((int)blockIdx.x < ncopy) {
+    copy_role<256>(a, (int)blockIdx.x);
+  } else {
+    gemm_role_pair(a, &tmap_x, &tmap_w, ((int)blockIdx.x - ncopy) >> 1,
+                   ((int)gridDim.x - ncopy) >> 1, smem_raw, &s_abort);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = (atomicAdd(&a.scratch->ctas_done, 1u) == gridDim.x - 1);
+    if (s_last) {
+      const int npanels = (int)((a.N + 255) / 256);
+      for (int p = 0; p < npanels; ++p) a.scratch->panel_done[p] = 0;
+      a.scratch->ctas_done = 0;
+      __threadfence();
+    }
+  }
+}
+
 // Grid: [num_copy_ctas copy CTAs][GEMM CTAs], 256 threads each.  GEMM CTAs use six warps;
 // the last two only take part in the block-wide barriers.
 //
@@ -677,6 +887,35 @@ static int launch256(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw
   return (int)cudaGetLastError();
 }
 
+static int launch_pair(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, int grid,
+                       cudaStream_t s) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!attr_set[dev & 63]) {
+    cudaError_t e = cudaFuncSetAttribute(pull_gemm_pair_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         CfgPair::kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    attr_set[dev & 63] = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = CfgPair::kSmemBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, pull_gemm_pair_kernel, a, tx, tw);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return (int)e;
+}
+
 // Output-tile height used by run(): 128 (double-buffered accumulators) or 256 (twice the
 // reuse of W per byte loaded).  0 = choose by shape.
 static std::atomic<int> g_tile_m{0};
@@ -687,6 +926,7 @@ static int pick_tile_m(long long M, long long N, long long K) {
     const char* e = getenv("PSB200_GEMM_TILE");
     t = e ? atoi(e) : 0;
   }
+  if (t == 2) return (N >= 256 && M >= 256) ? 2 : 128;  // 2 = CTA pairs
   if (t == 128 || t == 256) return (t == 256 && N >= 256 && M >= 256) ? 256 : 128;
   // by shape: the tall tile wins when the reduction is long enough to amortise its exposed
   // epilogue (measured: 1.53 vs 1.34 PFLOP/s at K = 8192, but 0.87 vs 1.07 at K = 1024) and
@@ -701,13 +941,16 @@ static int run(Args a, const void* x, const void* w, int num_ctas, cudaStream_t 
   int err = 0;
   a.scratch = scratch_for_current_device(&err);
   if (!a.scratch) return err;
-  const int tile_m = pick_tile_m(a.M, a.N, a.K);
+  const int variant = pick_tile_m(a.M, a.N, a.K);
+  const bool pair = (variant == 2);
+  const int tile_m = pair ? 256 : variant;  // rows of X per output tile (per pair for pairs)
   const int BN = (tile_m == 256 || a.N % 256 == 0 || a.N > 1024) ? 256 : 128;
   if ((a.N + BN - 1) / BN >= kMaxPanels) return PSDEV_ERR_UNSUPPORTED;
   CUtensorMap tx, tw;
-  int rc = make_tmap(&tx, x, a.M, a.K, tile_m);
+  // a CTA of a pair loads 128 rows of each operand per k-block
+  int rc = make_tmap(&tx, x, a.M, a.K, pair ? 128 : tile_m);
   if (rc) return rc;
-  rc = make_tmap(&tw, w, a.N, a.K, BN);
+  rc = make_tmap(&tw, w, a.N, a.K, pair ? 128 : BN);
   if (rc) return rc;
   int sms = 148;
   int dev = 0;
@@ -717,6 +960,14 @@ static int run(Args a, const void* x, const void* w, int num_ctas, cudaStream_t 
   int gemm_ctas = num_ctas > 0 ? num_ctas : sms;
   if (a.fused) gemm_ctas = gemm_ctas > a.num_copy_ctas + 1 ? gemm_ctas - a.num_copy_ctas : 1;
   if (tiles < gemm_ctas) gemm_ctas = (int)tiles;
+  if (pair) {
+    // clusters of two: even number of copy CTAs, GEMM CTAs in pairs (one tile per pair)
+    if (a.fused) a.num_copy_ctas = (a.num_copy_ctas + 1) & ~1;
+    int pairs = (num_ctas > 0 ? num_ctas : sms) / 2 - (a.fused ? a.num_copy_ctas / 2 : 0);
+    if (pairs < 1) pairs = 1;
+    if (tiles < pairs) pairs = (int)tiles;
+    return launch_pair(a, tx, tw, 2 * pairs + (a.fused ? a.num_copy_ctas : 0), s);
+  }
   const int grid = gemm_ctas + (a.fused ? a.num_copy_ctas : 0);
   if (tile_m == 256) return launch256(a, tx, tw, grid, s);
   return BN == 256 ? launch<256>(a, tx, tw, grid, s) : launch<128>(a, tx, tw, grid, s);
@@ -760,10 +1011,10 @@ extern "C" int psdev_pull_gemm_bf16(const psdev_world_t* w, const psdev_table_t*
   return gemm::run(a, x, wl, num_ctas, (cudaStream_t)stream);
 }
 
-// Selects the output-tile height of later GEMM launches: 128, 256, or 0 for the built-in
-// choice by shape.
+// Selects the kernel variant of later GEMM launches: 128 or 256 (output-tile height of the
+// one-CTA kernels), 2 (CTA pairs, tcgen05 cta_group::2), or 0 for the built-in choice by shape.
 extern "C" int psdev_gemm_config(int tile_m) {
-  if (tile_m != 0 && tile_m != 128 && tile_m != 256) return PSDEV_ERR_ARG;
+  if (tile_m != 0 && tile_m != 128 && tile_m != 256 && tile_m != 2) return PSDEV_ERR_ARG;
   gemm::g_tile_m.store(tile_m);
   return 0;
 }

@@ -196,3 +196,22 @@ def test_shard_checkpoint_round_trip(cuda_device, tmp_path):
     torch.cuda.synchronize()
     torch.testing.assert_close(t.weight[:50_000], saved[0][:50_000])
     heap.close()
+
+
+def test_cpp_device_kv_worker(cuda_device):
+    """C++ DeviceKVWorker (timestamps, callbacks, Wait, error on a missing peer)."""
+    import os
+    import subprocess
+    from ps_lite_b200 import _build
+    root = str(_build.ROOT)
+    lib = _build.build_device()
+    core = _build.build_core()
+    out = os.path.join(root, "build", "tests", "device_kv")
+    os.makedirs(os.path.dirname(out), exist_ok=True)
+    cmd = [_build.NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O1",
+           "-I", os.path.join(root, "include"), os.path.join(root, "tests", "cuda", "device_kv.cu"),
+           "-o", out, str(lib), str(core), "-Xlinker", f"-rpath={os.path.dirname(str(lib))}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    r = subprocess.run([out], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "DEVICE_KV_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

@@ -9,7 +9,7 @@ def _ref(x, w):
     return (x.float() @ w.float().t())
 
 
-@pytest.mark.parametrize("tile", [128, 256])
+@pytest.mark.parametrize("tile", [128, 256, 2])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 128, 192),
                                    (1000, 392, 520), (2048, 3072, 1024), (130, 264, 72),
                                    (4096, 1024, 512)])
@@ -27,7 +27,7 @@ def test_gemm_matches_fp32_matmul(cuda_device, M, N, K, tile):
     _lib.device_lib().psdev_gemm_config(0)
 
 
-@pytest.mark.parametrize("tile", [128, 256])
+@pytest.mark.parametrize("tile", [128, 256, 2])
 @pytest.mark.parametrize("world,blk", [(2, 4096), (4, 1024), (8, 4096)])
 def test_pull_fused_gemm_emulated_ranks(cuda_device, world, blk, tile):
     """All ranks' heaps on one GPU: rank r's kernel pulls the other ranks' blocks of W and
