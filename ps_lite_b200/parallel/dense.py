@@ -64,6 +64,19 @@ def default_timeout_s() -> float:
     return float(os.environ.get("PSB200_DEVICE_TIMEOUT_S", "20"))
 
 
+_NVTX = None
+_OP_NAMES = {1: "ps.push", 2: "ps.pull", 3: "ps.push_pull", 5: "ps.push_publish"}
+
+
+def _nvtx_enabled() -> bool:
+    """NVTX ranges around every request when PSB200_NVTX=1 (for timeline tools)."""
+    global _NVTX
+    if _NVTX is None:
+        import os
+        _NVTX = os.environ.get("PSB200_NVTX") == "1"
+    return _NVTX
+
+
 class DenseTable:
     """``n`` values sharded block-cyclically over the ranks of ``heap``.
 
@@ -151,11 +164,15 @@ class DenseTable:
         o = self.optimizer.to_struct(max(self.step, 1))
         s = stream or torch.cuda.current_stream(self.heap.device)
         tmo = int((timeout_s if timeout_s is not None else default_timeout_s()) * 1e9)
+        if _nvtx_enabled():
+            torch.cuda.nvtx.range_push(f"{_OP_NAMES.get(op, 'ps.op')}[{begin}:{end}]")
         rc = self.heap.lib.psdev_dense_op(C.byref(self._world), C.byref(self._table), op,
                                           int(begin), int(end), C.byref(o), self.channel,
                                           self.num_ctas, tmo,
                                           (1 if sync else 0) | (2 if self.nvls else 0),
                                           s.cuda_stream)
+        if _nvtx_enabled():
+            torch.cuda.nvtx.range_pop()
         _lib.check(rc, "psdev_dense_op")
 
     def push(self, begin: int = 0, end: Optional[int] = None, *, sync: bool = True, stream=None,
