@@ -928,11 +928,16 @@ static int pick_tile_m(long long M, long long N, long long K) {
   }
   if (t == 2) return (N >= 256 && M >= 256) ? 2 : 128;  // 2 = CTA pairs
   if (t == 128 || t == 256) return (t == 256 && N >= 256 && M >= 256) ? 256 : 128;
-  // by shape: the tall tile wins when the reduction is long enough to amortise its exposed
-  // epilogue (measured: 1.53 vs 1.34 PFLOP/s at K = 8192, but 0.87 vs 1.07 at K = 1024) and
-  // there are enough 256 x 256 tiles to fill the SMs a few times
+  // by shape (measured on one B200, bf16, TFLOP/s):
+  //   16384x3072x1024: pairs 1198, 128-row tile 1070, 256-row tile 868
+  //   16384x4096x1024: pairs 1398, 128-row tile 1169
+  //   8192x8192x8192 : 256-row tile 1533, pairs 1477, 128-row tile 1341
+  // CTA pairs whenever there is at least one 256 x 256 tile per pair of SMs; the one-CTA
+  // 256-row tile for long reductions, where its exposed epilogue is amortised.
   const long long tiles256 = ((M + 255) / 256) * ((N + 255) / 256);
-  return (N >= 256 && K >= 2048 && tiles256 >= 2 * 148) ? 256 : 128;
+  if (N >= 256 && M >= 256 && K >= 4096 && tiles256 >= 2 * 148) return 256;
+  if (N >= 256 && M >= 256 && tiles256 >= 74) return 2;
+  return 128;
 }
 
 static int run(Args a, const void* x, const void* w, int num_ctas, cudaStream_t s) {
