@@ -109,7 +109,10 @@ __device__ __forceinline__ void multimem_st_v2(void* mc, uint2 v) {
 __device__ __forceinline__ bool wait_flag_ge(const unsigned long long* flag,
                                              unsigned long long want,
                                              unsigned long long timeout_ns) {
-  if (ld_acquire_sys(flag) >= want) return true;
+  // the common case is a peer that is a few microseconds away: poll without pausing first,
+  // then back off so that a long wait does not hammer the memory system
+  for (int i = 0; i < 64; ++i)
+    if (ld_acquire_sys(flag) >= want) return true;
   const unsigned long long t0 = globaltimer_ns();
   unsigned int backoff = 32;
   for (;;) {
