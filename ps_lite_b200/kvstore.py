@@ -38,6 +38,10 @@ class Context:
             device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
+        # host staging buffers and copy threads next to the GPU (matters with several GPUs
+        # per host: a pinned buffer on the far socket crosses the inter-socket link)
+        from .utils.affinity import bind_to_gpu_cpus
+        self.cpus = bind_to_gpu_cpus(self.device.index or 0)
         self.heap = SymmetricHeap(heap_bytes, self.rank, self.world, group=group,
                                   device=self.device)
         self._next_channel = 0
