@@ -40,6 +40,9 @@ def parse_args():
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--trainer", default="ps", choices=["ps", "ddp"],
+                    help="model workloads: this package's server-side optimizer, or the "
+                         "torch DistributedDataParallel + torch.optim baseline over NCCL")
     return ap.parse_args()
 
 

@@ -57,6 +57,8 @@ def run(args):
         def fwd(x, y):
             return model(x, y)
     nparam = sum(p.numel() for p in model.parameters())
+    if getattr(args, "trainer", "ps") == "ddp":
+        return _run_ddp(args, model, fwd, make, rank, world, dev, metric, unit, per_step, nparam)
     ctx = kvstore.init(heap_bytes=nparam * 8 + (256 << 20), device=dev)
     fused = args.workload == "bert"
     dopt = DistributedOptimizer(model.parameters(), ctx.heap, sopt, grad_dtype=torch.bfloat16,
@@ -116,4 +118,61 @@ def run(args):
     kvstore.finalize()
     if world > 1:
         import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def _run_ddp(args, model, fwd, make, rank, world, dev, metric, unit, per_step, nparam):
+    """Library baseline: DistributedDataParallel (NCCL all-reduce in buckets, overlapped with
+    backward) and the fused torch optimizers, same model, data path and timing."""
+    import torch.distributed as dist
+    from ps_lite_b200.utils.timing import max_over_ranks
+    net = model
+    if world > 1:
+        net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[dev.index],
+                                                        gradient_as_bucket_view=True)
+    if args.workload == "resnet50":
+        opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+    else:
+        opt = torch.optim.Adam(model.parameters(), lr=1e-4, eps=1e-6, fused=True)
+    hx, hy = make()
+    if net is not model:
+        # route the forward through the DDP wrapper so that its hooks fire
+        if args.workload == "resnet50":
+            def fwd(x, y):  # noqa: F811
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    out = net(x.contiguous(memory_format=torch.channels_last))
+                return F.cross_entropy(out.float(), y)
+        else:
+            def fwd(x, y):  # noqa: F811
+                return net(x, y)
+
+    def step():
+        x = hx.to(dev, non_blocking=True)
+        y = hy.to(dev, non_blocking=True)
+        opt.zero_grad(set_to_none=True)
+        loss = fwd(x, y)
+        loss.backward()
+        opt.step()
+        return loss
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        float(step().item())
+    e1.record()
+    torch.cuda.synchronize()
+    ms = max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
+    if rank == 0:
+        print(json.dumps({"metric": metric, "value": round(world * per_step / (ms * 1e-3), 2),
+                          "unit": unit, "n_gpus": world, "steps": args.steps,
+                          "ms_per_step": round(ms, 3), "impl": "torch DDP + torch.optim (NCCL)",
+                          "dtype": "bf16", "data": "synthetic",
+                          "config": {"model": args.workload, "global_batch": per_step * world,
+                                     "parameters": nparam}}), flush=True)
+    if world > 1:
         dist.destroy_process_group()
