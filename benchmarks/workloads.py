@@ -62,12 +62,12 @@ def run(args):
     ctx = kvstore.init(heap_bytes=nparam * 8 + (256 << 20), device=dev)
     fused = args.workload == "bert"
     dopt = DistributedOptimizer(model.parameters(), ctx.heap, sopt, grad_dtype=torch.bfloat16,
-                                num_ctas=args.ctas or 32, publish_first=1 if fused else 0)
+                                num_ctas=args.ctas or 32,
+                                publish_params=[model.layers[0].qkv.weight] if fused else ())
     if fused:
         # the first GEMM that consumes pulled weights (layer-0 QKV) pulls them itself
         from ps_lite_b200.ops.gemm import pull_linear
         qkv_w = model.layers[0].qkv.weight
-        assert dopt.params[0] is qkv_w
         off = dopt.offset_of(qkv_w)
         model.layers[0].qkv_fn = lambda x: pull_linear(x, qkv_w, dopt.table, off)
     hx, hy = make()

@@ -67,7 +67,7 @@ class DistributedOptimizer:
                  optimizer: ServerOptimizer, grad_dtype=torch.bfloat16, blk: int = 4096,
                  slice_bytes: int = 4 << 20, slices_per_event: int = 2, channel: int = 0,
                  num_ctas: int = 32, overlap: bool = True, publish_first: int = 0,
-                 nvls: Optional[bool] = None):
+                 nvls: Optional[bool] = None, publish_params=()):
         self.params = [p for p in params if p.requires_grad]
         if not self.params:
             raise ValueError("no trainable parameters")
@@ -90,6 +90,8 @@ class DistributedOptimizer:
         # the first `publish_first` parameters are pushed with publish instead of push+pull:
         # their weights are pulled by a GEMM-fused pull in the next forward pass
         self.publish_first = publish_first
+        pub = {id(p) for p in publish_params}
+        self._publish = [i < publish_first or id(p) in pub for i, p in enumerate(self.params)]
         self.steps = 0
         self.launched_slices = 0
         # initial weights: rank 0's values, installed through an "assign" push
@@ -122,7 +124,7 @@ class DistributedOptimizer:
                 self.table.step = self.steps + 1
             # reverse layer order: parameter 0 (needed first by the next forward) is most urgent
             pri = n_params - index
-            if index < self.publish_first:
+            if self._publish[index]:
                 pri = -1 - index  # published slices carry no pull: least urgent
             self.sched.add(o, o + ((n + 7) & ~7), pri)
             self._launch(self.slices_per_event)
