@@ -1,5 +1,6 @@
-// Fundamental types and node-group identifiers (same values as the reference,
-// include/ps/base.h:10-30, because they appear on the wire and in user programs).
+// Fundamental types and node-group identifiers.  The numeric values are those of the
+// reference (include/ps/base.h:10-30) because they travel on the wire and appear in user
+// programs: scheduler = 1, server group = 2, worker group = 4, and any sum of them.
 #ifndef PS_BASE_H_
 #define PS_BASE_H_
 #include <cstdint>
@@ -9,19 +10,27 @@
 
 namespace ps {
 
+// Key type: 64-bit unless the library is built with USE_KEY32.
 #ifdef USE_KEY32
-using Key = uint32_t;
+typedef uint32_t Key;
 #else
-using Key = uint64_t;
+typedef uint64_t Key;
 #endif
-// largest key value
-static const Key kMaxKey = std::numeric_limits<Key>::max();
 
-// Node ids below 8 name groups: bit 0 = scheduler, bit 1 = all servers, bit 2 = all
-// workers; any OR of them is a valid group (e.g. 6 = servers + workers, 7 = everyone).
-static const int kScheduler = 1;
-static const int kServerGroup = 2;
-static const int kWorkerGroup = 4;
+// Largest key; server ranges are cut from [0, kMaxKey).
+constexpr Key kMaxKey = std::numeric_limits<Key>::max();
+
+// Group identifiers are bit flags below 8; concrete node ids start at 8.
+enum : int {
+  kScheduler = 1 << 0,
+  kServerGroup = 1 << 1,
+  kWorkerGroup = 1 << 2,
+};
+
+// True for an id that names a group (or a union of groups) rather than a node.
+constexpr bool IsGroupId(int id) { return id > 0 && id < 8; }
+// The union of all nodes.
+constexpr int kAllNodes = kScheduler | kServerGroup | kWorkerGroup;
 
 }  // namespace ps
 #endif  // PS_BASE_H_
