@@ -35,7 +35,9 @@ extern "C" {
 #define PSDEV_IPC_HANDLE_BYTES 64
 
 /* element types of gradients (wire) and of pulled weights */
-enum { PSDEV_F32 = 0, PSDEV_BF16 = 1 };
+/* PSDEV_I8 (gradients only): int8 values with one fp32 scale per 256 values, as written by
+ * psdev_filter_int8_pack; the push kernel applies the scales while it reduces */
+enum { PSDEV_F32 = 0, PSDEV_BF16 = 1, PSDEV_I8 = 2 };
 
 /* built-in server handles (the "request handle" of a KVServer, run on device) */
 enum {
@@ -100,6 +102,7 @@ typedef struct {
   float* state2;       /* Adam v, or NULL                                        */
   int32_t grad_dtype;  /* PSDEV_F32 | PSDEV_BF16                                 */
   int32_t out_dtype;   /* dtype of the pulled-weight buffer                      */
+  uint64_t gscale_off; /* PSDEV_I8 gradients: heap offset of the fp32 scales     */
 } psdev_table_t;
 
 /* ---- symmetric heap ------------------------------------------------------ */

@@ -37,6 +37,7 @@ struct DenseArgs {
   void* mc_base;  // multicast alias of the heap (used by the MC kernel variant only)
   int rank, world;
   unsigned long long grad_off, weight_off;
+  unsigned long long gscale_off;  // int8 gradients: heap offset of the fp32 scales (one per 256)
   long long blk, begin, end;
   long long first_owned;  // first block index owned by this rank that meets [begin,end)
   long long n_owned;      // how many owned blocks meet the range
@@ -128,6 +129,22 @@ struct VecOf<__nv_bfloat16> {
 
 // Stores VEC weights as OT at dst.  MC: dst is a multicast address (one store reaches every
 // rank's buffer); otherwise an ordinary (local or peer) address.
+// int8 gradients with one fp32 scale per 256 values (the block-scale filter): sixteen values
+// per 16-byte load; the scale is applied when the vector is added to the sum.
+template <>
+struct VecOf<signed char> {
+  static constexpr int kPer16 = 16;
+  __device__ static __forceinline__ void unpack(const uint4& u, float* f) {
+    const unsigned int w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int b = 0; b < 4; ++b) f[4 * j + b] = (float)(signed char)((w[j] >> (8 * b)) & 0xff);
+    }
+  }
+};
+constexpr int kInt8Group = 256;
+
 template <typename OT, int VEC, bool MC = false>
 __device__ __forceinline__ void store_out(OT* dst, const float* w) {
   if constexpr (sizeof(OT) == 4) {
@@ -138,7 +155,15 @@ __device__ __forceinline__ void store_out(OT* dst, const float* w) {
       if constexpr (MC) multimem_st_v4(dst + 4 * q, u); else st_v4(dst + 4 * q, u);
     }
   } else {
-    if constexpr (VEC == 8) {
+    if constexpr (VEC == 16) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float* x = w + 8 * h;
+        uint4 u = make_uint4(f2_to_bf16x2(x[0], x[1]), f2_to_bf16x2(x[2], x[3]),
+                             f2_to_bf16x2(x[4], x[5]), f2_to_bf16x2(x[6], x[7]));
+        if constexpr (MC) multimem_st_v4(dst + 8 * h, u); else st_v4(dst + 8 * h, u);
+      }
+    } else if constexpr (VEC == 8) {
       uint4 u = make_uint4(f2_to_bf16x2(w[0], w[1]), f2_to_bf16x2(w[2], w[3]),
                            f2_to_bf16x2(w[4], w[5]), f2_to_bf16x2(w[6], w[7]));
       if constexpr (MC) multimem_st_v4(dst, u); else st_v4(dst, u);
@@ -246,7 +271,7 @@ template <typename GT, typename OT, bool REDUCE, int WMAX>
 struct DenseTile {
   static constexpr int kVec = DenseVec<GT, OT, REDUCE>::kVec;
   static constexpr int kBase = DenseShape<WMAX>::kUnroll;
-  static constexpr int kUnroll = (kVec == 8 && kBase > 2) ? 2 : kBase;
+  static constexpr int kUnroll = kVec == 16 ? 1 : ((kVec == 8 && kBase > 2) ? 2 : kBase);
   static constexpr int kElems = kDenseThreads * kVec * kUnroll;
 };
 
@@ -312,7 +337,7 @@ __global__ void __launch_bounds__(kDenseThreads)
               const GT* src = reinterpret_cast<const GT*>(
                                   reinterpret_cast<const char*>(a.mc_base) + a.grad_off) + i;
               if constexpr (sizeof(GT) == 4) gv[u][0] = multimem_ld_reduce_f32x4(src);
-              else gv[u][0] = multimem_ld_reduce_bf16x8(src);
+              else if constexpr (sizeof(GT) == 2) gv[u][0] = multimem_ld_reduce_bf16x8(src);
             }
           } else {
 #pragma unroll
@@ -346,8 +371,15 @@ __global__ void __launch_bounds__(kDenseThreads)
             if (MC || p < W) {
               float f[VEC];
               VecOf<GT>::unpack(gv[u][p], f);
+              float sc = 1.f;
+              if constexpr (sizeof(GT) == 1) {
+                // a vector of 16 never straddles a group of 256
+                const long long gi = (i0 + (long long)u * kDenseThreads * VEC) / kInt8Group;
+                sc = *(reinterpret_cast<const volatile float*>(
+                           reinterpret_cast<const char*>(a.base[p]) + a.gscale_off) + gi);
+              }
 #pragma unroll
-              for (int q = 0; q < VEC; ++q) g[q] += f[q];
+              for (int q = 0; q < VEC; ++q) g[q] = fmaf(f[q], sc, g[q]);
             }
           }
 #pragma unroll

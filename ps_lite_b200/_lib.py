@@ -16,7 +16,7 @@ NUM_CHANNELS = 64
 CTRL_BYTES = 65536
 IPC_HANDLE_BYTES = 64
 
-F32, BF16 = 0, 1
+F32, BF16, I8 = 0, 1, 2
 OPT_SUM, OPT_SGD, OPT_MOMENTUM, OPT_ADAM, OPT_ASSIGN = 0, 1, 2, 3, 4
 OP_PUSH, OP_PULL, OP_PUSHPULL, OP_PUBLISH = 1, 2, 3, 4
 
@@ -43,7 +43,7 @@ class Table(C.Structure):
     _fields_ = [("grad_off", C.c_uint64), ("weight_off", C.c_uint64),
                 ("n", C.c_int64), ("blk", C.c_int64),
                 ("master", C.c_void_p), ("state1", C.c_void_p), ("state2", C.c_void_p),
-                ("grad_dtype", C.c_int32), ("out_dtype", C.c_int32)]
+                ("grad_dtype", C.c_int32), ("out_dtype", C.c_int32), ("gscale_off", C.c_uint64)]
 
 
 class Sparse(C.Structure):

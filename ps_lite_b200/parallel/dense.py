@@ -21,7 +21,7 @@ import torch
 from .. import _lib
 from .heap import SymmetricHeap
 
-_DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+_DT = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.int8: _lib.I8}
 
 
 @dataclasses.dataclass
@@ -90,10 +90,12 @@ class DenseTable:
         self.heap = heap
         W = heap.world
         self.n_user = int(n)
-        self.n = (int(n) + 7) & ~7
+        # int8 gradients carry one scale per 256 values: everything is aligned to 256 then
+        align = 256 if grad_dtype == torch.int8 else 8
+        self.n = (int(n) + align - 1) // align * align
         if blk is None:  # contiguous ranges, one per server
             blk = (self.n + W - 1) // W
-        self.blk = max(8, (int(blk) + 7) & ~7)
+        self.blk = max(align, (int(blk) + align - 1) // align * align)
         self.nblocks = (self.n + self.blk - 1) // self.blk
         self.local_blocks = (self.nblocks + W - 1) // W
         self.local_len = self.local_blocks * self.blk
@@ -114,6 +116,11 @@ class DenseTable:
         self.weight_off = heap.alloc(self.n * osz)
         self.grad = heap.tensor(self.grad_off, self.n, grad_dtype)
         self.weight = heap.tensor(self.weight_off, self.n, out_dtype)
+        self.gscale_off, self.gscale = 0, None
+        if grad_dtype == torch.int8:
+            self.gscale_off = heap.alloc(4 * (self.n // 256))
+            self.gscale = heap.tensor(self.gscale_off, self.n // 256, torch.float32)
+            self.gscale.fill_(1.0)
         dev = heap.device
         self.master = torch.zeros(self.local_len, dtype=torch.float32, device=dev)
         ns = self.optimizer.num_states
@@ -127,8 +134,23 @@ class DenseTable:
         t.state1 = self.state1.data_ptr() if self.state1 is not None else None
         t.state2 = self.state2.data_ptr() if self.state2 is not None else None
         t.grad_dtype, t.out_dtype = _DT[grad_dtype], _DT[out_dtype]
+        t.gscale_off = self.gscale_off
         self.grad.zero_()
         self.weight.zero_()
+
+    def stage_int8(self, grad: torch.Tensor, begin: int = 0) -> None:
+        """Compress an fp32 gradient into this table's int8 gradient buffer starting at element
+        ``begin`` (a multiple of 256): values plus one scale per 256 (the block-scale filter)."""
+        if self.gscale is None:
+            raise TypeError("table was not created with grad_dtype=torch.int8")
+        if begin % 256:
+            raise ValueError("begin must be a multiple of 256")
+        g = grad.reshape(-1).contiguous()
+        s = torch.cuda.current_stream(self.heap.device)
+        rc = self.heap.lib.psdev_filter_int8_pack(
+            g.data_ptr(), self.grad[begin:].data_ptr(), self.gscale[begin // 256:].data_ptr(),
+            g.numel(), s.cuda_stream)
+        _lib.check(rc, "psdev_filter_int8_pack")
 
     # -- ownership helpers (host math mirrored by the kernels) ------------------------------
     def owner_of(self, i: int) -> int:

@@ -11,6 +11,8 @@ int dense_dispatch_f32_f32(int op, const DenseArgs& a, int ctas, cudaStream_t s)
 int dense_dispatch_bf16_bf16(int op, const DenseArgs& a, int ctas, cudaStream_t s);
 int dense_dispatch_bf16_f32(int op, const DenseArgs& a, int ctas, cudaStream_t s);
 int dense_dispatch_f32_bf16(int op, const DenseArgs& a, int ctas, cudaStream_t s);
+int dense_dispatch_i8_f32(int op, const DenseArgs& a, int ctas, cudaStream_t s);
+int dense_dispatch_i8_bf16(int op, const DenseArgs& a, int ctas, cudaStream_t s);
 }  // namespace psdev
 
 // ---- P3 slice schedule (device side) ----------------------------------------------------------
@@ -164,6 +166,14 @@ static int dense_op_impl(const psdev_world_t* w, const psdev_table_t* t, int op,
   const int ctas = num_ctas;
   cudaStream_t s = (cudaStream_t)stream;
   const bool gbf = t->grad_dtype == PSDEV_BF16, obf = t->out_dtype == PSDEV_BF16;
+  if (t->grad_dtype == PSDEV_I8) {
+    // int8 block-scale gradients: 16 values per vector, ranges aligned to 16, no multicast
+    // reduction (the switch cannot apply per-block scales)
+    if ((begin & 15) || (end & 15) || (t->blk & 15) || (t->blk % 256) != 0) return PSDEV_ERR_ARG;
+    a.gscale_off = t->gscale_off;
+    if (op & PSDEV_OP_PUSH) a.mc_base = nullptr;
+    return obf ? dense_dispatch_i8_bf16(op, a, ctas, s) : dense_dispatch_i8_f32(op, a, ctas, s);
+  }
   if (gbf && obf) return dense_dispatch_bf16_bf16(op, a, ctas, s);
   if (gbf && !obf) return dense_dispatch_bf16_f32(op, a, ctas, s);
   if (!gbf && obf) return dense_dispatch_f32_bf16(op, a, ctas, s);

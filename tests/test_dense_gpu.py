@@ -215,3 +215,38 @@ def test_cpp_device_kv_worker(cuda_device):
     assert r.returncode == 0, r.stderr[-3000:]
     r = subprocess.run([out], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "DEVICE_KV_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("world", [1, 4])
+@pytest.mark.parametrize("odt", [torch.float32, torch.bfloat16])
+def test_int8_block_scale_gradients(cuda_device, world, odt):
+    """Gradients travel as int8 + one scale per 256 values; the push kernel dequantises while
+    it reduces.  The reference is the same update applied to the dequantised gradients."""
+    from ps_lite_b200.ops.filters import int8_pack, int8_unpack
+    from ps_lite_b200.parallel import ServerOptimizer
+    torch.manual_seed(5)
+    n = 100_000
+    opt = ServerOptimizer("momentum", lr=0.1, momentum=0.9)
+    heaps, tables = _mk_tables(world, n, torch.int8, odt, 1024, opt, cuda_device)
+    npad = tables[0].n
+    assert npad % 256 == 0
+    w0 = torch.randn(npad, device=cuda_device)
+    ref_w, s1 = w0.clone(), torch.zeros(npad, device=cuda_device)
+    for t in tables:
+        t.load_master(w0)
+    for step in range(2):
+        deq = []
+        for t in tables:
+            g = torch.randn(npad, device=cuda_device) * (1 + step)
+            t.stage_int8(g)
+            q, sc = int8_pack(g)
+            deq.append(int8_unpack(q, sc))
+        for t in tables:
+            t.push_pull(sync=False)
+        torch.cuda.synchronize()
+        dense_update(ref_w, deq, "momentum", lr=0.1, momentum=0.9, s1=s1)
+        for t in tables:
+            torch.testing.assert_close(t.weight[:n].float(), ref_w[:n].to(odt).float(),
+                                       **_tol(torch.float32, odt))
+    for h in heaps:
+        h.close()
