@@ -3,8 +3,10 @@
 Shape: the layer-0 QKV projection of BERT-large, X[16384,1024] * W[3072,1024]^T, W sharded
 block-cyclically over the ranks.  Each timed iteration is one server update of W and one use:
   unfused: push+pull of W (fused dense kernel, all-gather included), then the tcgen05 GEMM;
-  fused  : push with publish, then the GEMM kernel whose copy CTAs pull W panel by panel.
-CUDA events, max over ranks, one JSON line on rank 0.
+  fused  : push with publish, then the GEMM kernel that pulls W panel by panel itself, with the
+           spare warps of its GEMM CTAs (fused) or with 16 CTAs set aside (fused_copy_ctas).
+PULL_GEMM_SHAPE=M,N,K selects another shape.  CUDA events, max over ranks, one JSON line on
+rank 0.
 """
 import json
 import os
@@ -28,8 +30,8 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    M, N, K = 16384, 3072, 1024
-    ctx = kvstore.init(heap_bytes=64 << 20, device=dev)
+    M, N, K = (int(v) for v in os.environ.get("PULL_GEMM_SHAPE", "16384,3072,1024").split(","))
+    ctx = kvstore.init(heap_bytes=(64 << 20) + 8 * N * K, device=dev)
     t = DenseTable(ctx.heap, N * K, torch.bfloat16, torch.bfloat16, blk=4096,
                    optimizer=ServerOptimizer("sgd", lr=0.01), channel=ctx.new_channel())
     t.load_master(torch.randn(N * K, device=dev) * 0.02)
@@ -46,11 +48,23 @@ def main():
         t.push(opt_step=False, publish=True)
         pull_linear_bf16(t, 0, N, x, out)
 
+    def fused_copy_ctas():
+        t.push(opt_step=False, publish=True)
+        pull_linear_bf16(t, 0, N, x, out, num_copy_ctas=16)
+
     def gemm_only():
         linear_bf16(x, W, out)
 
+    def push_pull_only():
+        t.push_pull(opt_step=False)
+
+    def publish_only():
+        t.push(opt_step=False, publish=True)
+
     res = {}
-    for name, fn in (("gemm_only", gemm_only), ("unfused", unfused), ("fused", fused)):
+    for name, fn in (("gemm_only", gemm_only), ("push_pull_only", push_pull_only),
+                     ("publish_only", publish_only), ("unfused", unfused), ("fused", fused),
+                     ("fused_copy_ctas", fused_copy_ctas)):
         for _ in range(5):
             fn()
         torch.cuda.synchronize()

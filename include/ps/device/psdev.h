@@ -174,10 +174,22 @@ int psdev_gemm_bf16(const void* x, const void* w, void* c, int64_t M, int64_t N,
  * buffer: copy CTAs fetch the blocks owned by other ranks over NVLink panel by panel while
  * the tensor cores work on the panels that have landed.  Must follow, on `stream`, a
  * PUSH|PUBLISH of that range by every rank.  Uses a small per-device scratch block that the
- * library allocates on first use. */
+ * library allocates on first use.  num_copy_ctas > 0 sets that many CTAs aside for the copy;
+ * num_copy_ctas <= 0 selects ring mode: one thread of every GEMM CTA moves its share of the
+ * remote blocks with bulk copies through a ring in shared memory (a cooperative launch, so
+ * that all CTAs are resident; if that is not granted, 16 copy CTAs are used instead). */
 int psdev_pull_gemm_bf16(const psdev_world_t* w, const psdev_table_t* t, int64_t w_elem_off,
                          const void* x, void* c, int64_t M, int64_t N, int64_t K,
                          int num_copy_ctas, int num_ctas, uint64_t timeout_ns, void* stream);
+/* Ring mode of psdev_pull_gemm_bf16 for later launches: mode 1 (default) moves W with bulk
+ * (TMA) loads and stores issued by two threads per CTA, mode 0 with 16-byte asynchronous
+ * copies by two warps per CTA; chunk_bytes is 4096, 8192, 16384 or 0 for the default (8192). */
+int psdev_pull_ring_config(int mode, int chunk_bytes);
+/* Host-side view of the pull plan of psdev_pull_gemm_bf16 in ring mode, for tests: returns the
+ * number of chunk slots for W = elements [w_elem_off, w_elem_off + nk) and, for 0 <= i < that,
+ * the owner and element range of slot i (empty when *begin >= *end). */
+int64_t psdev_pull_plan_chunk(int64_t w_elem_off, int64_t nk, int blk, int world, int rank,
+                              int64_t i, int* owner, int64_t* begin, int64_t* end);
 /* Reads and clears the error word of the GEMM kernels on the current device (synchronous). */
 int psdev_gemm_status(int32_t* status);
 

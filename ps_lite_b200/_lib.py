@@ -96,6 +96,9 @@ def _declare(lib: C.CDLL) -> None:
         "psdev_pull_gemm_bf16": (i32, [C.POINTER(World), C.POINTER(Table), i64, vp, vp, i64, i64,
                                        i64, i32, i32, u64, vp]),
         "psdev_gemm_config": (i32, [i32]),
+        "psdev_pull_ring_config": (i32, [i32, i32]),
+        "psdev_pull_plan_chunk": (i64, [i64, i64, i32, i32, i32, i64, C.POINTER(C.c_int),
+                                        C.POINTER(i64), C.POINTER(i64)]),
         "psdev_gemm_status": (i32, [C.POINTER(C.c_int32)]),
         "psdev_filter_cast": (i32, [vp, vp, i64, C.c_float, i32, vp]),
         "psdev_filter_int8_pack": (i32, [vp, vp, vp, i64, vp]),

@@ -45,6 +45,11 @@ constexpr int UMMA_K = 16;
 constexpr int kThreads = 256;      // warps 0..5 have roles in a GEMM CTA
 constexpr int kCopyThreads = kThreads;
 constexpr int kCopyUnroll = 8;
+// pull ring of the GEMM CTAs (see pull_ring_role)
+constexpr int kRingMaxSlots = 8;
+constexpr int kRingChunkElems = 4096;                      // default chunk: 8 KB of bf16
+constexpr int kRingBytes = 32768;                          // slots = kRingBytes / chunk bytes
+constexpr int kRingBarIndex = 24;                          // ring barriers: bars[24..31]
 constexpr int kMaxPanels = 1024;
 
 // Device scratch of the fused kernel: zero between launches (the last CTA to leave resets it).
@@ -61,6 +66,10 @@ struct Args {
   unsigned long long timeout_ns;
   // fused pull
   int fused, num_copy_ctas;
+  int inline_copy;          // ring mode: one thread of every GEMM CTA pulls W (no copy CTAs)
+  int ring_chunk;           // elements per chunk of the pull ring: 2048, 4096 or 8192
+  int ring_mode;            // 0: two warps per CTA, load/store path; 1: one thread, bulk loads
+  unsigned int panel_want;  // arrivals that complete a panel
   void* base[PSDEV_MAX_RANKS];
   int rank, world;
   unsigned long long weight_off;  // heap offset of the table's weight buffer
@@ -75,7 +84,7 @@ struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + kRingBytes;
 };
 
 __device__ __forceinline__ void report(Scratch* s, int code) { atomicMin(&s->status, code); }
@@ -125,8 +134,290 @@ __device__ void copy_role(const Args& a, int copy_idx) {
   }
 }
 
+// ---- pull ring: the all-gather of W done by one thread of every GEMM CTA ---------------------
+// With no CTA set aside for copying, every SM multiplies.  The blocks of W that other ranks
+// own are cut into chunks of at most 8 KB; chunk i belongs to CTA i mod (number of CTAs).  One
+// thread per CTA moves its chunks through a ring of buffers (32 KB) in shared memory: an
+// untiled bulk load from the owner's memory (over NVLink) into a slot, then a bulk store from
+// the slot into this rank's weight buffer.  All slots but one hold loads in flight -- 24 KB,
+// about 3.5 MB over 148 SMs, which covers the NVLink round trip -- and the thread itself only
+// issues and waits.  Chunks are visited in address order, so once the oldest incomplete chunk
+// starts at or beyond the end of panel p this CTA has nothing left in panel p and counts one
+// arrival on panel_done[p]; a panel is complete when every CTA has arrived.
+
+// The chunks of the remote blocks of W, in address order.  Elements are indices into the
+// table's weight buffer.
+struct PullPlan {
+  long long e0, e1;   // W = elements [e0, e1)
+  long long g0;       // first group of `world` consecutive blocks that touches W
+  long long n;        // number of chunk slots (some are empty after clipping to W)
+  int blk, cpb, chunk, world, rank;
+};
+__host__ __device__ inline PullPlan make_pull_plan(long long w_elem_off, long long nk, int blk,
+                                                   int world, int rank,
+                                                   int chunk_elems = kRingChunkElems) {
+  PullPlan pl;
+  pl.e0 = w_elem_off;
+  pl.e1 = w_elem_off + nk;
+  pl.blk = blk;
+  pl.world = world;
+  pl.rank = rank;
+  pl.chunk = blk < chunk_elems ? blk : chunk_elems;
+  pl.cpb = (blk + pl.chunk - 1) / pl.chunk;
+  pl.g0 = (pl.e0 / blk) / world;
+  const long long g1 = ((pl.e1 - 1) / blk) / world;
+  pl.n = nk > 0 ? (g1 - pl.g0 + 1) * (world - 1) * pl.cpb : 0;
+  return pl;
+}
+// Chunk slot i -> owner and element range [s, e) (empty when s >= e).  Slot numbers fit in 32
+// bits (the launcher checks), which keeps the divisions cheap on the device.
+__host__ __device__ inline void pull_chunk(const PullPlan& pl, long long i, int* owner,
+                                           long long* s, long long* e) {
+  const unsigned int iu = (unsigned int)i;
+  const unsigned int q = iu / (unsigned int)pl.cpb;
+  const int c = (int)(iu - q * (unsigned int)pl.cpb);
+  const unsigned int g = q / (unsigned int)(pl.world - 1);
+  const int r = (int)(q - g * (unsigned int)(pl.world - 1));
+  const int o = r + (r >= pl.rank ? 1 : 0);
+  const long long block = (pl.g0 + g) * pl.world + o;
+  long long cs = block * pl.blk + (long long)c * pl.chunk;
+  long long ce = cs + pl.chunk;
+  const long long be = (block + 1) * pl.blk;
+  if (ce > be) ce = be;
+  if (cs < pl.e0) cs = pl.e0;
+  if (ce > pl.e1) ce = pl.e1;
+  *owner = o;
+  *s = cs;
+  *e = ce;
+}
+
+struct ChunkIter {
+  long long i, s, e;
+  int owner;
+  bool valid;
+};
+__device__ __forceinline__ void chunk_seek(const PullPlan& pl, ChunkIter& it, int stride) {
+  // moves to the first non-empty chunk at or after it.i (in steps of `stride`)
+  for (; it.i < pl.n; it.i += stride) {
+    pull_chunk(pl, it.i, &it.owner, &it.s, &it.e);
+    if (it.s < it.e) {
+      it.valid = true;
+      return;
+    }
+  }
+  it.valid = false;
+  it.s = it.e = 0x7fffffffffffffffLL;
+}
+
+// Arrivals of one copying agent on the panels of W.  An arrival costs two fences, and every
+// agent arrives on every panel, so after the first panels (which the first wave of tiles is
+// waiting for) arrivals are made in batches: one pair of fences, then one add per panel.
+struct PanelArrivals {
+  Scratch* sc;
+  long long e0, panel_elems, total;
+  int npanels, batch, sig;
+  __device__ void init(const Args& a, int bnp) {
+    sc = a.scratch;
+    e0 = a.w_elem_off;
+    panel_elems = (long long)bnp * a.K;
+    total = a.N * a.K;
+    npanels = (int)((a.N + bnp - 1) / bnp);
+    batch = npanels / 16 > 1 ? npanels / 16 : 1;
+    sig = 0;
+  }
+  // Panels that end at or before element `oldest` (the start of the oldest chunk of this agent
+  // that may be incomplete) hold nothing more of this agent.
+  __device__ int ready(long long oldest) const {
+    if (oldest >= e0 + total) return npanels;
+    const long long r = (oldest - e0) / panel_elems;
+    return r < 0 ? 0 : (int)r;
+  }
+  __device__ bool due(int rdy) const { return rdy - sig >= (sig < 8 ? 1 : batch); }
+  // The caller has made sure that this agent's stores to panels [sig, rdy) are complete.
+  __device__ void arrive(int rdy) {
+    fence_proxy_async_global();  // the bulk stores went through the async proxy
+    __threadfence();
+    for (; sig < rdy; ++sig) atomicAdd(&sc->panel_done[sig], 1u);
+  }
+};
+
+// Executed by TWO threads (of different warps) of CTA `me` of `nctas`: part 0 issues the bulk
+// loads, part 1 the bulk stores and the arrivals.  The split keeps the fences of an arrival
+// away from the thread that has remote loads in flight.  `ring` is kRingBytes of shared
+// memory (16-byte aligned); bar[0..3] count the bytes that land in a slot, bar[4..7] tell the
+// loader that a slot has been stored (all initialised with count 1).  BNP: rows of W per panel.
+__device__ void pull_ring_role(const Args& a, int part, int me, int nctas, int bnp,
+                               unsigned char* ring, uint64_t* bar, volatile int* abort_flag) {
+  const PullPlan pl =
+      make_pull_plan(a.w_elem_off, a.N * a.K, (int)a.blk, a.world, a.rank, a.ring_chunk);
+  const int slot_bytes = a.ring_chunk * 2;
+  const int slots = kRingBytes / slot_bytes;  // 2 or 4
+  uint64_t* full = bar;
+  uint64_t* empty = bar + 4;
+  ChunkIter it{me, 0, 0, 0, false};
+  chunk_seek(pl, it, nctas);
+  long long t = 0;
+  if (part == 0) {
+    // ---- loader ----
+    bool ok = true;
+    for (; it.valid; ++t) {
+      const int slot = (int)(t % slots);
+      const long long round = t / slots;
+      if (round > 0 &&
+          !mbar_wait_bounded(&empty[slot], (uint32_t)((round - 1) & 1), abort_flag, a.timeout_ns)) {
+        ok = false;
+        break;
+      }
+      const uint32_t bytes = (uint32_t)((it.e - it.s) * 2);
+      mbar_arrive_expect_tx(&full[slot], bytes);
+      bulk_load(ring + slot * slot_bytes,
+                reinterpret_cast<const char*>(a.base[it.owner]) + a.weight_off + it.s * 2, bytes,
+                &full[slot]);
+      it.i += nctas;
+      chunk_seek(pl, it, nctas);
+    }
+    if (!ok || *abort_flag) {
+      // loads still in flight must land before the CTA gives up its shared memory
+      const unsigned long long t0 = gtimer_ns();
+      for (long long u = t > slots ? t - slots : 0; u < t; ++u) {
+        const int slot = (int)(u % slots);
+        while (!mbar_try_wait(&full[slot], (uint32_t)((u / slots) & 1)) &&
+               gtimer_ns() - t0 < a.timeout_ns) {
+        }
+      }
+    }
+    return;
+  }
+  // ---- storer ----
+  char* mine = reinterpret_cast<char*>(a.base[a.rank]) + a.weight_off;
+  // Stores complete a while after they were issued, so arrivals lag: after the store of chunk
+  // k has been committed, only the stores up to chunk k - kSignalLag are awaited, and panels
+  // are judged against the start of the oldest chunk that may still be incomplete.
+  constexpr int kSignalLag = 3;
+  long long lag_s[kSignalLag];  // starts of the last kSignalLag chunks stored, oldest first
+#pragma unroll
+  for (int i = 0; i < kSignalLag; ++i) lag_s[i] = -1;
+  PanelArrivals arr;
+  arr.init(a, bnp);
+  bool ok = true;
+  for (; it.valid; ++t) {
+    const int slot = (int)(t % slots);
+    if (!mbar_wait_bounded(&full[slot], (uint32_t)((t / slots) & 1), abort_flag, a.timeout_ns)) {
+      ok = false;
+      break;
+    }
+    fence_proxy_async_smem();
+    bulk_store(mine + it.s * 2, ring + slot * slot_bytes, (uint32_t)((it.e - it.s) * 2));
+    bulk_commit();
+    if (t > 0) {
+      bulk_wait_read<1>();  // the previous store has left its slot: the loader may refill it
+      mbar_arrive(&empty[(int)((t - 1) % slots)]);
+    }
+    const long long oldest = lag_s[1] >= 0 ? lag_s[1] : (lag_s[2] >= 0 ? lag_s[2] : it.s);
+#pragma unroll
+    for (int i = 0; i + 1 < kSignalLag; ++i) lag_s[i] = lag_s[i + 1];
+    lag_s[kSignalLag - 1] = it.s;
+    const int rdy = arr.ready(oldest);
+    if (arr.due(rdy)) {
+      bulk_wait<kSignalLag>();  // stores before `oldest` (all but the last kSignalLag) are complete
+      arr.arrive(rdy);
+    }
+    it.i += nctas;
+    chunk_seek(pl, it, nctas);
+  }
+  bulk_wait<0>();
+  if (ok) {
+    arr.arrive(arr.npanels);
+  } else {
+    report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+  }
+}
+
+// The same pull done by whole warps through the load/store path: the lanes of a warp fetch a
+// chunk with 16-byte asynchronous copies (global -> shared, several chunks in flight per warp),
+// and lane 0 sends each landed chunk on to this rank's weight buffer with one bulk store.
+// `ring` is this warp's share of the ring (`ring_bytes`, 2, 4 or 8 chunks).  Arrivals are
+// counted per warp.
+__device__ __forceinline__ void cp_async_wait_upto(int n) {
+  switch (n) {
+    case 0: cp_async_wait<0>(); break;
+    case 2: cp_async_wait<2>(); break;
+    default: cp_async_wait<6>(); break;
+  }
+}
+__device__ void pull_warp_role(const Args& a, int wid, int nwarps, int bnp, unsigned char* ring,
+                               int ring_bytes, int lane) {
+  const PullPlan pl =
+      make_pull_plan(a.w_elem_off, a.N * a.K, (int)a.blk, a.world, a.rank, a.ring_chunk);
+  const int slot_bytes = a.ring_chunk * 2;
+  const int slots = ring_bytes / slot_bytes;  // 2, 4 or 8
+  char* mine = reinterpret_cast<char*>(a.base[a.rank]) + a.weight_off;
+  ChunkIter ld{wid, 0, 0, 0, false}, st{wid, 0, 0, 0, false};
+  chunk_seek(pl, ld, nwarps);
+  st = ld;
+  long long nl = 0, ns = 0;
+  auto issue = [&](const ChunkIter& c, long long t) {
+    const uint32_t bytes = (uint32_t)((c.e - c.s) * 2);
+    const char* src = reinterpret_cast<const char*>(a.base[c.owner]) + a.weight_off + c.s * 2;
+    unsigned char* dst = ring + (int)(t % slots) * slot_bytes;
+    for (uint32_t off = (uint32_t)lane * 16; off < bytes; off += 512) cp_async_16(dst + off, src + off);
+  };
+  // exactly slots-1 groups are committed ahead, empty ones included, so that "all but the
+  // newest slots-2 groups" always means "the chunk that is stored next"
+  for (int j = 0; j < slots - 1; ++j) {
+    if (ld.valid) {
+      issue(ld, nl++);
+      ld.i += nwarps;
+      chunk_seek(pl, ld, nwarps);
+    }
+    cp_async_commit();
+  }
+  constexpr int kSignalLag = 3;
+  long long lag_s[kSignalLag];
+#pragma unroll
+  for (int i = 0; i < kSignalLag; ++i) lag_s[i] = -1;
+  PanelArrivals arr;
+  arr.init(a, bnp);
+  while (st.valid) {
+    cp_async_wait_upto(slots - 2);  // this lane's pieces of the oldest chunk have landed
+    fence_proxy_async_smem();       // ... and may be read by the bulk store
+    __syncwarp();
+    if (lane == 0) {
+      bulk_store(mine + st.s * 2, ring + (int)(ns % slots) * slot_bytes,
+                 (uint32_t)((st.e - st.s) * 2));
+      bulk_commit();
+      const long long oldest = lag_s[1] >= 0 ? lag_s[1] : (lag_s[2] >= 0 ? lag_s[2] : st.s);
+#pragma unroll
+      for (int i = 0; i + 1 < kSignalLag; ++i) lag_s[i] = lag_s[i + 1];
+      lag_s[kSignalLag - 1] = st.s;
+      const int rdy = arr.ready(oldest);
+      if (arr.due(rdy)) {
+        bulk_wait<kSignalLag>();
+        arr.arrive(rdy);
+      }
+      bulk_wait_read<1>();  // the previous store has left its slot: the slot may be refilled
+    }
+    __syncwarp();
+    ++ns;
+    st.i += nwarps;
+    chunk_seek(pl, st, nwarps);
+    if (ld.valid) {
+      issue(ld, nl++);
+      ld.i += nwarps;
+      chunk_seek(pl, ld, nwarps);
+    }
+    cp_async_commit();
+  }
+  cp_async_wait<0>();
+  if (lane == 0) {
+    bulk_wait<0>();
+    arr.arrive(arr.npanels);
+  }
+  __syncwarp();
+}
+
 __device__ __forceinline__ bool wait_panel(const Args& a, int p, volatile int* abort_flag) {
-  const unsigned int want = (unsigned int)a.num_copy_ctas;
+  const unsigned int want = a.panel_want;
   const unsigned long long t0 = gtimer_ns();
   while (ld_acquire_gpu_u32(&a.scratch->panel_done[p]) < want) {
     if (*abort_flag) return false;
@@ -154,6 +445,8 @@ __device__ void gemm_role(const Args& a, const CUtensorMap* tmap_x, const CUtens
   uint64_t* tmem_full = bars + 2 * C::kStages;   // [2]
   uint64_t* tmem_empty = tmem_full + 2;          // [2]
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* ring_bar = bars + kRingBarIndex;     // [kRingMaxSlots]
+  unsigned char* ring = smem + C::kStages * C::kStageBytes + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long tiles_m = (a.M + BM - 1) / BM;
@@ -170,6 +463,7 @@ __device__ void gemm_role(const Args& a, const CUtensorMap* tmap_x, const CUtens
       mbar_init(&tmem_full[i], 1);
       mbar_init(&tmem_empty[i], 128);
     }
+    for (int i = 0; i < kRingMaxSlots; ++i) mbar_init(&ring_bar[i], 1);
     fence_barrier_init();
     prefetch_tmap(tmap_x);
     prefetch_tmap(tmap_w);
@@ -308,6 +602,13 @@ __device__ void gemm_role(const Args& a, const CUtensorMap* tmap_x, const CUtens
       mbar_arrive(&tmem_empty[acc]);
     }
     if (!ok && lane == 0) report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+  } else if (a.fused && a.inline_copy) {
+    // warps 6 and 7: pull W while the other warps multiply
+    if (a.ring_mode == 0)
+      pull_warp_role(a, gemm_idx * 2 + (warp - 6), num_gemm_ctas * 2, BN,
+                     ring + (warp - 6) * (kRingBytes / 2), kRingBytes / 2, lane);
+    else if (lane == 0)
+      pull_ring_role(a, warp - 6, gemm_idx, num_gemm_ctas, BN, ring, ring_bar, abort_flag);
   }
 
   // teardown: everyone is done with tensor memory
@@ -325,7 +626,7 @@ __device__ void gemm_role(const Args& a, const CUtensorMap* tmap_x, const CUtens
 // therefore capped near two thirds of the tensor peak, while this shape needs exactly 64.
 // The price is that the accumulators are not double buffered: the epilogue of a tile is only
 // overlapped with the next tile's first k-blocks half by half, so eight warps drain it.
-constexpr int kThreads256 = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int kThreads256 = 384;  // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue, 10..11 pull ring
 
 struct Cfg256 {
   static constexpr int BN = 256, BM2 = 256;
@@ -334,7 +635,7 @@ struct Cfg256 {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = 3;
   static constexpr int kTmemCols = 512;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kRingBytes;
 };
 
 __device__ void gemm_role_256(const Args& a, const CUtensorMap* tmap_x, const CUtensorMap* tmap_w,
@@ -350,6 +651,8 @@ __device__ void gemm_role_256(const Args& a, const CUtensorMap* tmap_x, const CU
   uint64_t* tmem_full = bars + 2 * C::kStages;  // [1]: both halves of the tile are complete
   uint64_t* tmem_empty = tmem_full + 1;         // [2]: half h has been drained
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* ring_bar = bars + kRingBarIndex;     // [kRingMaxSlots]
+  unsigned char* ring = smem + C::kStages * C::kStageBytes + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long tiles_m = (a.M + BM2 - 1) / BM2;
@@ -365,6 +668,7 @@ __device__ void gemm_role_256(const Args& a, const CUtensorMap* tmap_x, const CU
     mbar_init(&tmem_full[0], 1);
     mbar_init(&tmem_empty[0], 256);  // all eight epilogue warps arrive once per half
     mbar_init(&tmem_empty[1], 256);
+    for (int i = 0; i < kRingMaxSlots; ++i) mbar_init(&ring_bar[i], 1);
     fence_barrier_init();
     prefetch_tmap(tmap_x);
     prefetch_tmap(tmap_w);
@@ -466,7 +770,7 @@ __device__ void gemm_role_256(const Args& a, const CUtensorMap* tmap_x, const CU
       if (!ok) report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
     }
     __syncwarp();
-  } else {
+  } else if (warp < 10) {
     // epilogue: warp w reads lane quarter (w & 3); warps 2..5 take columns [0,128) of each
     // half, warps 6..9 columns [128,256)
     const int q = warp & 3;
@@ -511,6 +815,13 @@ __device__ void gemm_role_256(const Args& a, const CUtensorMap* tmap_x, const CU
       }
     }
     if (!ok && lane == 0) report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+  } else if (a.fused && a.inline_copy) {
+    // warps 10 and 11: pull W while the other warps multiply
+    if (a.ring_mode == 0)
+      pull_warp_role(a, gemm_idx * 2 + (warp - 10), num_gemm_ctas * 2, BN,
+                     ring + (warp - 10) * (kRingBytes / 2), kRingBytes / 2, lane);
+    else if (lane == 0)
+      pull_ring_role(a, warp - 10, gemm_idx, num_gemm_ctas, BN, ring, ring_bar, abort_flag);
   }
 
   tc_fence_before();
@@ -562,7 +873,7 @@ struct CfgPair {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = 6;
   static constexpr int kTmemCols = 512;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kRingBytes;
 };
 
 __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const CUtensorMap* tmap_w,
@@ -578,6 +889,8 @@ __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const C
   uint64_t* tmem_full = bars + 2 * C::kStages;  // [2]        one copy per CTA
   uint64_t* tmem_empty = tmem_full + 2;         // [2]        used in the leader CTA
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* ring_bar = bars + kRingBarIndex;     // [kRingMaxSlots]
+  unsigned char* ring = smem + C::kStages * C::kStageBytes + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();  // 0 = leader
@@ -595,6 +908,7 @@ __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const C
       mbar_init(&tmem_full[i], 1);
       mbar_init(&tmem_empty[i], 256);  // 128 epilogue threads of each CTA
     }
+    for (int i = 0; i < kRingMaxSlots; ++i) mbar_init(&ring_bar[i], 1);
     fence_barrier_init();
     prefetch_tmap(tmap_x);
     prefetch_tmap(tmap_w);
@@ -718,6 +1032,14 @@ __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const C
       mbar_arrive_leader(&tmem_empty[acc]);  // counted on the leader, where the MMAs are issued
     }
     if (!ok && lane == 0) report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
+  } else if (a.fused && a.inline_copy) {
+    // warps 6 and 7: pull W while the other warps multiply
+    const int cta_lin = pair_idx * 2 + (int)cta;
+    if (a.ring_mode == 0)
+      pull_warp_role(a, cta_lin * 2 + (warp - 6), num_pairs * 4, BN,
+                     ring + (warp - 6) * (kRingBytes / 2), kRingBytes / 2, lane);
+    else if (lane == 0)
+      pull_ring_role(a, warp - 6, cta_lin, num_pairs * 2, BN, ring, ring_bar, abort_flag);
   }
 
   // teardown: neither CTA may free its tensor memory while the other might still be used by
@@ -852,6 +1174,43 @@ static Scratch* scratch_for_current_device(int* err) {
   return table[dev];
 }
 
+// One launch; `cluster` CTAs per cluster along x.  In ring mode every CTA's pull thread feeds
+// every other CTA, so the launch asks for all CTAs to be resident together (cooperative).
+typedef void (*GemmKernel)(const Args, const CUtensorMap, const CUtensorMap);
+static int launch_ex(GemmKernel k, const Args& a, const CUtensorMap& tx, const CUtensorMap& tw,
+                     int grid, int threads, int smem, int cluster, cudaStream_t s) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3((unsigned)threads, 1, 1);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = (unsigned)cluster;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  // PSB200_PULL_GEMM_COOP=0 drops the co-residency request (measurements only: without it
+  // a busy GPU can leave a CTA waiting for a pull thread that has not been scheduled)
+  static const bool coop = [] {
+    const char* e = getenv("PSB200_PULL_GEMM_COOP");
+    return !(e && e[0] == '0');
+  }();
+  if (a.fused && a.inline_copy && coop) {
+    attr[n].id = cudaLaunchAttributeCooperative;
+    attr[n].val.cooperative = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = (unsigned)n;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, k, a, tx, tw);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return (int)e;
+}
+
 template <int BN>
 static int launch(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, int grid,
                   cudaStream_t s) {
@@ -865,9 +1224,7 @@ static int launch(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, i
     if (e != cudaSuccess) return (int)e;
     attr_set[dev & 63] = true;
   }
-  pull_gemm_kernel<BN><<<grid, kThreads, Cfg<BN>::kSmemBytes, s>>>(a, tx, tw);
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  return (int)cudaGetLastError();
+  return launch_ex(pull_gemm_kernel<BN>, a, tx, tw, grid, kThreads, Cfg<BN>::kSmemBytes, 1, s);
 }
 
 static int launch256(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, int grid,
@@ -882,9 +1239,7 @@ static int launch256(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw
     if (e != cudaSuccess) return (int)e;
     attr_set[dev & 63] = true;
   }
-  pull_gemm256_kernel<<<grid, kThreads256, Cfg256::kSmemBytes, s>>>(a, tx, tw);
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  return (int)cudaGetLastError();
+  return launch_ex(pull_gemm256_kernel, a, tx, tw, grid, kThreads256, Cfg256::kSmemBytes, 1, s);
 }
 
 static int launch_pair(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, int grid,
@@ -899,21 +1254,7 @@ static int launch_pair(const Args& a, const CUtensorMap& tx, const CUtensorMap& 
     if (e != cudaSuccess) return (int)e;
     attr_set[dev & 63] = true;
   }
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
-  cfg.dynamicSmemBytes = CfgPair::kSmemBytes;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, pull_gemm_pair_kernel, a, tx, tw);
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  return (int)e;
+  return launch_ex(pull_gemm_pair_kernel, a, tx, tw, grid, kThreads, CfgPair::kSmemBytes, 2, s);
 }
 
 // Output-tile height used by run(): 128 (double-buffered accumulators) or 256 (twice the
@@ -962,20 +1303,47 @@ static int run(Args a, const void* x, const void* w, int num_ctas, cudaStream_t 
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const long long tiles = ((a.M + tile_m - 1) / tile_m) * ((a.N + BN - 1) / BN);
-  int gemm_ctas = num_ctas > 0 ? num_ctas : sms;
-  if (a.fused) gemm_ctas = gemm_ctas > a.num_copy_ctas + 1 ? gemm_ctas - a.num_copy_ctas : 1;
-  if (tiles < gemm_ctas) gemm_ctas = (int)tiles;
-  if (pair) {
-    // clusters of two: even number of copy CTAs, GEMM CTAs in pairs (one tile per pair)
-    if (a.fused) a.num_copy_ctas = (a.num_copy_ctas + 1) & ~1;
-    int pairs = (num_ctas > 0 ? num_ctas : sms) / 2 - (a.fused ? a.num_copy_ctas / 2 : 0);
-    if (pairs < 1) pairs = 1;
-    if (tiles < pairs) pairs = (int)tiles;
-    return launch_pair(a, tx, tw, 2 * pairs + (a.fused ? a.num_copy_ctas : 0), s);
+  const int avail = num_ctas > 0 ? num_ctas : sms;
+  // One launch of the chosen variant with `copy` CTAs set aside (0: ring mode or not fused).
+  auto go = [&](int copy) -> int {
+    if (pair) {
+      // clusters of two: even number of copy CTAs, GEMM CTAs in pairs (one tile per pair)
+      copy = (copy + 1) & ~1;
+      int pairs = avail / 2 - copy / 2;
+      if (pairs < 1) pairs = 1;
+      if (tiles < pairs) pairs = (int)tiles;
+      a.num_copy_ctas = copy;
+      a.panel_want = (unsigned int)(copy ? copy : 2 * pairs * (a.ring_mode == 0 ? 2 : 1));
+      return launch_pair(a, tx, tw, 2 * pairs + copy, s);
+    }
+    int gemm_ctas = avail > copy + 1 ? avail - copy : 1;
+    if (tiles < gemm_ctas) gemm_ctas = (int)tiles;
+    a.num_copy_ctas = copy;
+    a.panel_want = (unsigned int)(copy ? copy : gemm_ctas * (a.ring_mode == 0 ? 2 : 1));
+    const int grid = gemm_ctas + copy;
+    if (tile_m == 256) return launch256(a, tx, tw, grid, s);
+    return BN == 256 ? launch<256>(a, tx, tw, grid, s) : launch<128>(a, tx, tw, grid, s);
+  };
+  if (!a.fused) {
+    a.inline_copy = 0;
+    return go(0);
   }
-  const int grid = gemm_ctas + (a.fused ? a.num_copy_ctas : 0);
-  if (tile_m == 256) return launch256(a, tx, tw, grid, s);
-  return BN == 256 ? launch<256>(a, tx, tw, grid, s) : launch<128>(a, tx, tw, grid, s);
+  if (a.inline_copy &&
+      make_pull_plan(a.w_elem_off, a.N * a.K, (int)a.blk, a.world, a.rank, a.ring_chunk).n >=
+          (1ll << 31)) {
+    a.inline_copy = 0;  // chunk slots are numbered in 32 bits on the device
+    a.num_copy_ctas = 16;
+  }
+  if (a.inline_copy) {
+    // ring mode: no copy CTAs, one thread of every GEMM CTA pulls W
+    if (go(0) == 0) return 0;
+    // co-residency could not be granted: set copy CTAs aside instead (they come first in the
+    // grid, so the CTAs that wait for them never keep them from starting)
+    cudaGetLastError();
+    a.inline_copy = 0;
+    a.num_copy_ctas = 16;
+  }
+  return go(a.num_copy_ctas);
 }
 
 }  // namespace gemm
@@ -993,6 +1361,29 @@ extern "C" int psdev_gemm_bf16(const void* x, const void* w, void* c, int64_t M,
   return gemm::run(a, x, w, num_ctas, (cudaStream_t)stream);
 }
 
+// How ring mode moves W: 1 = two threads per CTA, bulk (TMA) loads and stores; 0 = two warps
+// per CTA, 16-byte asynchronous copies through the load/store path and bulk stores.  Chunk
+// size in elements.  The defaults can be preset with PSB200_PULL_RING=tma|lsu and
+// PSB200_PULL_RING_CHUNK=<bytes: 4096, 8192 or 16384>.
+static std::atomic<int> g_ring_mode{[] {
+  const char* e = getenv("PSB200_PULL_RING");
+  return (e && e[0] == 'l') ? 0 : 1;
+}()};
+static std::atomic<int> g_ring_chunk{[] {
+  const char* e = getenv("PSB200_PULL_RING_CHUNK");
+  const int v = e ? atoi(e) : 0;
+  return (v == 4096 || v == 8192 || v == 16384) ? v / 2 : 4096;
+}()};
+
+extern "C" int psdev_pull_ring_config(int mode, int chunk_bytes) {
+  if (mode != 0 && mode != 1) return PSDEV_ERR_ARG;
+  if (chunk_bytes != 0 && chunk_bytes != 4096 && chunk_bytes != 8192 && chunk_bytes != 16384)
+    return PSDEV_ERR_ARG;
+  g_ring_mode.store(mode, std::memory_order_relaxed);
+  g_ring_chunk.store(chunk_bytes ? chunk_bytes / 2 : 4096, std::memory_order_relaxed);
+  return 0;
+}
+
 extern "C" int psdev_pull_gemm_bf16(const psdev_world_t* w, const psdev_table_t* t,
                                     int64_t w_elem_off, const void* x, void* c, int64_t M,
                                     int64_t N, int64_t K, int num_copy_ctas, int num_ctas,
@@ -1005,6 +1396,16 @@ extern "C" int psdev_pull_gemm_bf16(const psdev_world_t* w, const psdev_table_t*
   a.c = static_cast<__nv_bfloat16*>(c);
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
   a.fused = w->world > 1 ? 1 : 0;
+  // num_copy_ctas > 0: that many CTAs are set aside for the all-gather; <= 0: ring mode, one
+  // thread of every GEMM CTA moves W with bulk copies through shared memory
+  if (t->blk <= 0 || (t->blk & 7)) return PSDEV_ERR_ARG;
+  const int ring_mode = g_ring_mode.load(std::memory_order_relaxed);
+  const int ring_chunk = g_ring_chunk.load(std::memory_order_relaxed);
+  a.ring_mode = ring_mode;
+  // load/store path: 16 KB of ring per warp, at least two chunks; bulk loads: at most 4 slots
+  a.ring_chunk = ring_mode == 0 ? (ring_chunk > 4096 ? 4096 : ring_chunk)
+                                : (ring_chunk < 4096 ? 4096 : ring_chunk);
+  a.inline_copy = (a.fused && num_copy_ctas <= 0) ? 1 : 0;
   a.num_copy_ctas = a.fused ? (num_copy_ctas > 0 ? num_copy_ctas : 16) : 0;
   for (int p = 0; p < w->world; ++p) a.base[p] = w->peer_base[p];
   a.rank = w->rank;
@@ -1014,6 +1415,20 @@ extern "C" int psdev_pull_gemm_bf16(const psdev_world_t* w, const psdev_table_t*
   a.blk = t->blk;
   const char* wl = static_cast<const char*>(w->peer_base[w->rank]) + t->weight_off + w_elem_off * 2;
   return gemm::run(a, x, wl, num_ctas, (cudaStream_t)stream);
+}
+
+extern "C" int64_t psdev_pull_plan_chunk(int64_t w_elem_off, int64_t nk, int blk, int world,
+                                         int rank, int64_t i, int* owner, int64_t* begin,
+                                         int64_t* end) {
+  if (nk <= 0 || blk <= 0 || world < 2 || rank < 0 || rank >= world) return 0;
+  const gemm::PullPlan pl = gemm::make_pull_plan(w_elem_off, nk, blk, world, rank);
+  if (i >= 0 && i < pl.n && owner && begin && end) {
+    long long b = 0, e = 0;
+    gemm::pull_chunk(pl, i, owner, &b, &e);
+    *begin = b;
+    *end = e;
+  }
+  return pl.n;
 }
 
 // Selects the kernel variant of later GEMM launches: 128 or 256 (output-tile height of the

@@ -25,17 +25,21 @@ def test_gemm_matches_fp32_matmul(cuda_device, M, N, K, tile):
     assert gemm_status(cuda_device) == 0
     torch.testing.assert_close(out.float(), _ref(x, w), rtol=2e-2, atol=2e-2)
     _lib.device_lib().psdev_gemm_config(0)
+    _lib.device_lib().psdev_pull_ring_config(1, 0)
 
 
 @pytest.mark.parametrize("tile", [128, 256, 2])
+@pytest.mark.parametrize("copy_ctas", [0, -1, 16])
 @pytest.mark.parametrize("world,blk", [(2, 4096), (4, 1024), (8, 4096)])
-def test_pull_fused_gemm_emulated_ranks(cuda_device, world, blk, tile):
+def test_pull_fused_gemm_emulated_ranks(cuda_device, world, blk, tile, copy_ctas):
     """All ranks' heaps on one GPU: rank r's kernel pulls the other ranks' blocks of W and
     multiplies; every rank must get x @ W^T and end with the complete W in its weight buffer."""
     from ps_lite_b200 import _lib
     from ps_lite_b200.ops.gemm import gemm_status, pull_linear_bf16
     from ps_lite_b200.parallel import DenseTable, ServerOptimizer, SymmetricHeap
     assert _lib.device_lib().psdev_gemm_config(tile) == 0
+    # 0: ring of bulk loads (default); -1: ring on the load/store path; 16: copy CTAs
+    assert _lib.device_lib().psdev_pull_ring_config(0 if copy_ctas < 0 else 1, 0) == 0
     torch.manual_seed(world)
     M, N, K = 512, 768, 256
     pad = 1024  # W does not start at the beginning of the table
@@ -57,10 +61,11 @@ def test_pull_fused_gemm_emulated_ranks(cuda_device, world, blk, tile):
     W = w_new[pad:pad + N * K].to(torch.bfloat16).view(N, K)
     x = torch.randn(M, K, device=cuda_device).to(torch.bfloat16)
     for t in tables:
-        out = pull_linear_bf16(t, pad, N, x)
+        out = pull_linear_bf16(t, pad, N, x, num_copy_ctas=copy_ctas)
         torch.cuda.synchronize()
         assert gemm_status(cuda_device) == 0
         torch.testing.assert_close(out.float(), _ref(x, W), rtol=2e-2, atol=2e-2)
         torch.testing.assert_close(t.weight[pad:pad + N * K].float(), W.reshape(-1).float(),
                                    rtol=1e-2, atol=1e-2)
     _lib.device_lib().psdev_gemm_config(0)
+    _lib.device_lib().psdev_pull_ring_config(1, 0)
