@@ -43,6 +43,8 @@ build/make/libpsb200_device.so: $(DEV_OBJ)
 build/make/tests/%: tests/cpp/%.cc build/make/libps.a
 	@mkdir -p $(dir $@)
 	$(CXX) $(CXXFLAGS) $< build/make/libps.a -o $@
+lint:
+	python tests/lint.py
 clean:
 	rm -rf build/make
-.PHONY: all device test clean
+.PHONY: all device test lint clean

@@ -32,7 +32,10 @@ struct SumSgdHandle {
         off += len;
         slot.waiting.push_back(m);
         if (++slot.arrived == NumWorkers()) {
-          for (size_t j = 0; j < len; ++j) { slot.master[j] -= 0.01f * slot.acc[j]; slot.acc[j] = 0.f; }
+          for (size_t j = 0; j < len; ++j) {
+            slot.master[j] -= 0.01f * slot.acc[j];
+            slot.acc[j] = 0.f;
+          }
           slot.arrived = 0;
           for (const KVMeta& w : slot.waiting) s->Response(w);
           slot.waiting.clear();

@@ -4,7 +4,6 @@ Times the library's 16-byte load/store copy kernel for: local->local, peer->loca
 loads) and local->peer (remote stores), one active rank at a time and all ranks together.
 Rank 0 prints one JSON line per measurement.
 """
-import ctypes as C
 import json
 import os
 import sys

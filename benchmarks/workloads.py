@@ -4,7 +4,6 @@ from __future__ import annotations
 
 import json
 import os
-import time
 
 import torch
 import torch.nn.functional as F

@@ -137,7 +137,8 @@ int psdev_channel_clear(void* local_base, int channel);
  *   PUSHPULL : both in one pass; the summed gradient never touches memory.
  * `sync` is a bit set.  Bit 1 (value 2): reduce and broadcast through the NVSwitch multicast
  * alias `w->mc_base` (multimem.ld_reduce / multimem.st) instead of per-peer loads and stores;
- * ignored when mc_base is NULL.  Bit 0 (value 1) set: ranks rendezvous through epoch flags in the heap on `channel`
+ * ignored when mc_base is NULL.  Bit 0 (value 1) set: ranks rendezvous through epoch flags in
+ * the heap on `channel`
  * (every rank must issue the same sequence of calls per channel).  Bit 0 clear:
  * no flags are touched (used when the caller has already ordered the ranks, and
  * to run all ranks' roles back to back on one GPU).

@@ -27,7 +27,8 @@ size_t ParallelOrderedMatch(const SArray<K>& src_key, const SArray<V>& src_val,
   if (dst_val->empty()) dst_val->resize(dst_key.size() * k);
   CHECK_EQ(dst_val->size(), dst_key.size() * k);
   if (src_key.empty() || dst_key.empty()) return 0;
-  const size_t parts = std::max<size_t>(1, std::min<size_t>(num_threads, src_key.size() / 1024 + 1));
+  const size_t parts =
+      std::max<size_t>(1, std::min<size_t>(num_threads, src_key.size() / 1024 + 1));
   std::atomic<size_t> matched{0};
   auto work = [&](size_t lo, size_t hi) {
     const K* sk = src_key.data();
@@ -42,7 +43,8 @@ size_t ParallelOrderedMatch(const SArray<K>& src_key, const SArray<V>& src_val,
         ++d;
       } else {
         const size_t j = static_cast<size_t>(d - dst_key.begin());
-        for (int c = 0; c < k; ++c) AssignFunc(src_val.data()[i * k + c], op, dst_val->data() + j * k + c);
+        for (int c = 0; c < k; ++c)
+          AssignFunc(src_val.data()[i * k + c], op, dst_val->data() + j * k + c);
         ++n; ++i; ++d;
       }
     }

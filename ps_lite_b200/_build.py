@@ -60,7 +60,8 @@ def _headers_stamp() -> str:
 
 def _compile_one(src: Path, stamp: str, verbose: bool) -> Path:
     flags = NVCC_FLAGS if src.suffix == ".cu" else CXX_FLAGS
-    tag = hashlib.sha1(src.read_bytes() + stamp.encode() + " ".join(flags).replace(str(ROOT), "").encode()).hexdigest()[:12]
+    flag_text = " ".join(flags).replace(str(ROOT), "")
+    tag = hashlib.sha1(src.read_bytes() + stamp.encode() + flag_text.encode()).hexdigest()[:12]
     obj = OBJ_DIR / f"{src.stem}.{tag}.o"
     if obj.exists():
         return obj

@@ -9,7 +9,6 @@ from __future__ import annotations
 import ctypes as C
 import os
 import threading
-from pathlib import Path
 
 MAX_RANKS = 8
 NUM_CHANNELS = 64

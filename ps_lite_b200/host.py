@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes as C
 import threading
-from typing import Callable, Optional, Sequence
+from typing import Callable, Optional
 
 import numpy as np
 

@@ -13,7 +13,7 @@ import os
 import socket
 import subprocess
 import threading
-from typing import Callable, Dict, List, Optional, Sequence
+from typing import Callable, Dict, Optional, Sequence
 
 
 def free_port(lo: int = 9091, hi: int = 9999) -> int:

@@ -9,7 +9,6 @@ pushed.  See ``src/kernels/sparse.cu`` for the kernels.
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional
 
 import torch
 

@@ -5,7 +5,6 @@ The reference accumulates ``send_bytes_``/``recv_bytes_`` in its van but never r
 the number of kernels the device plane has launched and the heap usage."""
 from __future__ import annotations
 
-from typing import Optional
 
 
 def snapshot(heap=None, host: bool = False) -> dict:

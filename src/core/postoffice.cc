@@ -62,7 +62,8 @@ void Postoffice::Start(int customer_id, const char* argv0, const bool do_barrier
     }
     ++started_customers_;
   }
-  if (argv0 && verbose_ >= 1) LOG(INFO) << "starting " << argv0 << " (customer " << customer_id << ")";
+  if (argv0 && verbose_ >= 1)
+    LOG(INFO) << "starting " << argv0 << " (customer " << customer_id << ")";
 
   van_->Start(customer_id);
 

@@ -75,9 +75,11 @@ int psdev_filter_cast(const void* in, void* out, int64_t n, float scale, int dir
   if (n == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   if (dir == 0)
-    filt::cast_scale_f32_to_bf16<<<592, 256, 0, s>>>((const float*)in, (__nv_bfloat16*)out, n, scale);
+    filt::cast_scale_f32_to_bf16<<<592, 256, 0, s>>>((const float*)in, (__nv_bfloat16*)out, n,
+                                                     scale);
   else
-    filt::cast_scale_bf16_to_f32<<<592, 256, 0, s>>>((const __nv_bfloat16*)in, (float*)out, n, scale);
+    filt::cast_scale_bf16_to_f32<<<592, 256, 0, s>>>((const __nv_bfloat16*)in, (float*)out, n,
+                                                     scale);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return (int)cudaGetLastError();
 }

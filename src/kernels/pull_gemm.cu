@@ -84,7 +84,8 @@ struct Cfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + kRingBytes;
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/ + kRingBytes;
 };
 
 __device__ __forceinline__ void report(Scratch* s, int code) { atomicMin(&s->status, code); }
@@ -360,7 +361,8 @@ __device__ void pull_warp_role(const Args& a, int wid, int nwarps, int bnp, unsi
     const uint32_t bytes = (uint32_t)((c.e - c.s) * 2);
     const char* src = reinterpret_cast<const char*>(a.base[c.owner]) + a.weight_off + c.s * 2;
     unsigned char* dst = ring + (int)(t % slots) * slot_bytes;
-    for (uint32_t off = (uint32_t)lane * 16; off < bytes; off += 512) cp_async_16(dst + off, src + off);
+    for (uint32_t off = (uint32_t)lane * 16; off < bytes; off += 512)
+      cp_async_16(dst + off, src + off);
   };
   // exactly slots-1 groups are committed ahead, empty ones included, so that "all but the
   // newest slots-2 groups" always means "the chunk that is stored next"
@@ -1052,7 +1054,8 @@ __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const C
 
 // Grid: [copy CTAs (even count)][GEMM CTA pairs], clusters of 2 along x.
 __global__ void __launch_bounds__(kThreads, 1)
-    pull_gemm_pair_kernel(const __grid_constant__ Args a, const __grid_constant__ CUtensorMap tmap_x,
+    pull_gemm_pair_kernel(const __grid_constant__ Args a,
+                          const __grid_constant__ CUtensorMap tmap_x,
                           const __grid_constant__ CUtensorMap tmap_w) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ int s_abort;

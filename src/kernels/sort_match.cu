@@ -104,7 +104,8 @@ __global__ void scatter_kernel(const unsigned long long* keys_in, unsigned long 
   __syncthreads();
   unsigned int pos[kDigits];
 #pragma unroll
-  for (int j = 0; j < kDigits; ++j) pos[j] = offsets[j * nblocks + blockIdx.x] + cnt[j][threadIdx.x];
+  for (int j = 0; j < kDigits; ++j)
+    pos[j] = offsets[j * nblocks + blockIdx.x] + cnt[j][threadIdx.x];
 #pragma unroll
   for (int i = 0; i < kItems; ++i) {
     if (d[i] >= 0) {
@@ -199,7 +200,8 @@ int psdev_sort_keys(uint64_t* keys, uint32_t* perm, int64_t n, int key_bits, voi
   if (n < 0 || key_bits < 1 || key_bits > 64 || !keys) return PSDEV_ERR_ARG;
   if (n == 0) return 0;
   if (n >= (int64_t)1 << 32) return PSDEV_ERR_UNSUPPORTED;
-  if (!scratch || scratch_bytes < psdev_sort_scratch_bytes(n, perm != nullptr)) return PSDEV_ERR_ARG;
+  if (!scratch || scratch_bytes < psdev_sort_scratch_bytes(n, perm != nullptr))
+    return PSDEV_ERR_ARG;
   cudaStream_t s = (cudaStream_t)stream;
   const int nblocks = (int)((n + kTile - 1) / kTile);
   char* p = static_cast<char*>(scratch);

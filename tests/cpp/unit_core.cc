@@ -249,7 +249,8 @@ static void TestCodec() {
     r.request = rng() & 1; r.push = rng() & 1; r.pull = rng() & 1; r.simple_app = rng() & 1;
     r.priority = static_cast<int>(rng()) % 1000;
     r.body.assign(rng() % 20, 'x');
-    for (unsigned k = 0; k < rng() % 4; ++k) r.data_type.push_back(static_cast<DataType>(rng() % 14));
+    for (unsigned k = 0; k < rng() % 4; ++k)
+      r.data_type.push_back(static_cast<DataType>(rng() % 14));
     std::string s;
     pb::EncodeMeta(r, &s);
     Meta q;

@@ -6,7 +6,14 @@
 
 #include "ps/device/kv_device.h"
 
-#define CK(x) do { auto _e = (x); if (_e != 0) { printf("FAILED %s = %d line %d\n", #x, (int)_e, __LINE__); return 1; } } while (0)
+#define CK(x)                                                           \
+  do {                                                                  \
+    auto _e = (x);                                                      \
+    if (_e != 0) {                                                      \
+      printf("FAILED %s = %d line %d\n", #x, (int)_e, __LINE__);        \
+      return 1;                                                         \
+    }                                                                   \
+  } while (0)
 
 int main() {
   const int64_t n = 1 << 16;
@@ -44,7 +51,8 @@ int main() {
     kv.Wait(ts[2]);
     if (cbs.load() != 3) { printf("FAILED callbacks %d\n", cbs.load()); return 1; }
     std::vector<float> out(n);
-    CK(cudaMemcpy(out.data(), (char*)heap0 + t.weight_off, n * sizeof(float), cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(out.data(), (char*)heap0 + t.weight_off, n * sizeof(float),
+                  cudaMemcpyDeviceToHost));
     for (int64_t i = 0; i < n; ++i)
       if (out[i] != 3.f) { printf("FAILED value %f at %lld\n", out[i], (long long)i); return 1; }
     kv.Wait(kv.Pull(0, n, s));

@@ -1,5 +1,4 @@
 """Fused dense push/pull kernel against a plain PyTorch fp32 statement of the same update."""
-import itertools
 
 import pytest
 import torch

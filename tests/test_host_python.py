@@ -1,6 +1,5 @@
 """Python binding of the host runtime, wire codec against google.protobuf, launchers."""
 import os
-import subprocess
 import sys
 
 import numpy as np
@@ -211,3 +210,10 @@ def test_p3_scheduler_order():
         got.append(s.pop())
     assert got == [(100, 116, 5), (0, 16, 1), (16, 32, 1), (32, 40, 1), (200, 216, 1),
                    (216, 232, 1)]
+
+
+def test_lint_is_clean():
+    """tests/lint.py (style and hygiene rules for C++/CUDA and Python sources) reports nothing."""
+    r = __import__("subprocess").run([sys.executable, os.path.join(ROOT, "tests", "lint.py")],
+                                     capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:]

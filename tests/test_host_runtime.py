@@ -6,7 +6,6 @@ tests/local.sh: one process per role on one host); here they are built with g++ 
 """
 import os
 import subprocess
-import sys
 import time
 
 import pytest

@@ -69,7 +69,6 @@ def test_sparse_push_pull_matches_oracle(cuda_device, world, kind, store):
 
 
 def test_key_shard_lookup(cuda_device):
-    import ctypes as C
     from ps_lite_b200 import _lib
     lib = _lib.device_lib()
     keys = torch.tensor([0, 5, 9, 10, 11, 29, 30, 31, 45], device=cuda_device, dtype=torch.int64)
