@@ -178,7 +178,9 @@ int psdev_gemm_bf16(const void* x, const void* w, void* c, int64_t M, int64_t N,
  * library allocates on first use.  num_copy_ctas > 0 sets that many CTAs aside for the copy;
  * num_copy_ctas <= 0 selects ring mode: one thread of every GEMM CTA moves its share of the
  * remote blocks with bulk copies through a ring in shared memory (a cooperative launch, so
- * that all CTAs are resident; if that is not granted, 16 copy CTAs are used instead). */
+ * that all CTAs are resident; if that is not granted, 16 copy CTAs are used instead).
+ * All GEMM launches on one device share the scratch block (panel counters, error word): order
+ * them on one stream or with events; two of them running at the same time would mix counters. */
 int psdev_pull_gemm_bf16(const psdev_world_t* w, const psdev_table_t* t, int64_t w_elem_off,
                          const void* x, void* c, int64_t M, int64_t N, int64_t K,
                          int num_copy_ctas, int num_ctas, uint64_t timeout_ns, void* stream);

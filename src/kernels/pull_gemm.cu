@@ -310,10 +310,10 @@ __device__ void pull_ring_role(const Args& a, int part, int me, int nctas, int b
     fence_proxy_async_smem();
     bulk_store(mine + it.s * 2, ring + slot * slot_bytes, (uint32_t)((it.e - it.s) * 2));
     bulk_commit();
-    if (t > 0) {
-      bulk_wait_read<1>();  // the previous store has left its slot: the loader may refill it
-      mbar_arrive(&empty[(int)((t - 1) % slots)]);
-    }
+    // Hand the slot back as soon as the store has read it (a local copy out of shared memory,
+    // a fraction of a microsecond): peer reads need every slot in flight to cover their latency.
+    bulk_wait_read<0>();
+    mbar_arrive(&empty[slot]);
     const long long oldest = lag_s[1] >= 0 ? lag_s[1] : (lag_s[2] >= 0 ? lag_s[2] : it.s);
 #pragma unroll
     for (int i = 0; i + 1 < kSignalLag; ++i) lag_s[i] = lag_s[i + 1];
