@@ -26,6 +26,7 @@ device: build/make/libpsb200_device.so
 test: $(TESTS)
 	build/make/tests/unit_core
 	build/make/tests/loop_kv
+	build/make/tests/shm_frames
 	python -m ps_lite_b200.launch.local -n 2 -s 2 build/make/tests/kv_config1
 
 build/make/%.o: %.cc

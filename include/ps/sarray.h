@@ -21,6 +21,7 @@
 #include <vector>
 
 #include "ps/internal/logging.h"
+#include "ps/internal/shm_pool.h"
 #include "ps/range.h"
 
 namespace ps {
@@ -64,11 +65,29 @@ class SArray {
     }
   }
 
+  // Fresh storage for n elements.  Large arrays of plain data come from the shared-memory pool
+  // (ps/internal/shm_pool.h), so that a van between processes of one host can pass them by
+  // reference; everything else comes from the heap.
+  static V* NewStorage(size_t n, bool* pooled) {
+    const size_t bytes = (n ? n : 1) * sizeof(V);
+    *pooled = std::is_trivially_copyable<V>::value && bytes >= (size_t(64) << 10);
+    if (*pooled) return reinterpret_cast<V*>(shm::ArrayAlloc(bytes));
+    return new V[n ? n : 1];
+  }
+  void ResetOwned(V* p, size_t size, bool pooled) {
+    if (pooled) {
+      reset(p, size, [](V* q) { shm::ArrayFree(reinterpret_cast<char*>(q)); });
+    } else {
+      reset(p, size, [](V* q) { delete[] q; });
+    }
+  }
+
   // Deep copies.
   void CopyFrom(const V* src, size_t size) {
-    V* fresh = new V[size ? size : 1];
+    bool pooled = false;
+    V* fresh = NewStorage(size, &pooled);
     if (size) memcpy(fresh, src, size * sizeof(V));
-    reset(fresh, size, [](V* p) { delete[] p; });
+    ResetOwned(fresh, size, pooled);
   }
   void CopyFrom(const SArray<V>& other) {
     if (this == &other) return;
@@ -78,9 +97,10 @@ class SArray {
   template <typename ForwardIt>
   void CopyFrom(const ForwardIt& first, const ForwardIt& last) {
     const size_t n = static_cast<size_t>(std::distance(first, last));
-    V* fresh = new V[n ? n : 1];
+    bool pooled = false;
+    V* fresh = NewStorage(n, &pooled);
     std::copy(first, last, fresh);
-    reset(fresh, n, [](V* p) { delete[] p; });
+    ResetOwned(fresh, n, pooled);
   }
 
   explicit SArray(const std::vector<V>& vec) { CopyFrom(vec.data(), vec.size()); }
@@ -123,10 +143,12 @@ class SArray {
     CHECK(kind_ == MemKind::kHost) << "resize needs host memory";
     const size_t old = size_;
     if (size > capacity_) {
-      const size_t cap = size + size / 2 + 4;
-      V* fresh = new V[cap];
+      // an empty array grows to exactly what was asked for; a filled one gets slack
+      const size_t cap = old ? size + size / 2 + 4 : size;
+      bool pooled = false;
+      V* fresh = NewStorage(cap, &pooled);
       if (old) memcpy(fresh, data_, old * sizeof(V));
-      reset(fresh, size, [](V* p) { delete[] p; });
+      ResetOwned(fresh, size, pooled);
       capacity_ = cap;
     } else {
       size_ = size;

@@ -26,11 +26,13 @@
 
 #include <chrono>
 #include <cstring>
+#include <deque>
 #include <map>
 #include <random>
 
 #include "ps/internal/pb_codec.h"
 #include "ps/internal/postoffice.h"
+#include "ps/internal/shm_pool.h"
 #include "van/backends.h"
 
 namespace ps {
@@ -50,17 +52,41 @@ static_assert(sizeof(FrameHeader) == 20, "frame header layout");
 
 std::string UnixPath(int port) { return "/tmp/psb200_" + std::to_string(port) + ".sock"; }
 
-bool WriteAll(int fd, struct iovec* iov, int iovcnt) {
+// A data frame whose length word has this bit set does not carry its bytes: the array lives in
+// a shared-memory segment (ps/internal/shm_pool.h), the frame body is a ShmRef and the segment's
+// file descriptor rides on the message as SCM_RIGHTS ancillary data (Unix sockets only), in
+// frame order.
+constexpr uint64_t kShmFrame = 1ull << 63;
+struct ShmRef {
+  uint64_t seg_size;
+  uint64_t offset;
+};
+
+// Writes all of iov.  `fds` (may be empty) are attached to the first byte.
+bool WriteAll(int fd, struct iovec* iov, int iovcnt, const std::vector<int>& fds) {
+  bool first = true;
+  alignas(struct cmsghdr) char ctrl[CMSG_SPACE(sizeof(int) * kMaxFrames)];
   while (iovcnt > 0) {
     struct msghdr mh {};
     mh.msg_iov = iov;
     mh.msg_iovlen = static_cast<size_t>(iovcnt > IOV_MAX ? IOV_MAX : iovcnt);
+    if (first && !fds.empty()) {
+      memset(ctrl, 0, sizeof(ctrl));
+      mh.msg_control = ctrl;
+      mh.msg_controllen = CMSG_SPACE(sizeof(int) * fds.size());
+      struct cmsghdr* cm = CMSG_FIRSTHDR(&mh);
+      cm->cmsg_level = SOL_SOCKET;
+      cm->cmsg_type = SCM_RIGHTS;
+      cm->cmsg_len = CMSG_LEN(sizeof(int) * fds.size());
+      memcpy(CMSG_DATA(cm), fds.data(), sizeof(int) * fds.size());
+    }
     // MSG_NOSIGNAL: a peer that has gone away yields EPIPE here, not a SIGPIPE
     ssize_t n = ::sendmsg(fd, &mh, MSG_NOSIGNAL);
     if (n < 0) {
       if (errno == EINTR) continue;
       return false;
     }
+    if (n > 0) first = false;
     size_t left = static_cast<size_t>(n);
     while (iovcnt > 0 && left >= iov->iov_len) {
       left -= iov->iov_len;
@@ -75,6 +101,56 @@ bool WriteAll(int fd, struct iovec* iov, int iovcnt) {
   return true;
 }
 
+// Recycles large receive buffers.  A fresh allocation of tens of megabytes costs about as much
+// in page faults and zero-filling as copying the bytes into it, so buffers of at least 1 MiB go
+// back to a free list (bounded by PS_RECV_POOL_MB, default 256) when their array is released.
+class RecvPool {
+ public:
+  RecvPool() : limit_(static_cast<size_t>(GetEnv("PS_RECV_POOL_MB", 256)) << 20) {}
+  ~RecvPool() {
+    for (auto& kv : free_) delete[] kv.second;
+  }
+  static constexpr size_t kMin = size_t(1) << 20;
+  // A buffer of at least `len` bytes; *cap is what to hand back to Put.
+  char* Get(size_t len, size_t* cap) {
+    if (len < kMin) {
+      *cap = 0;
+      return new char[len ? len : 1];
+    }
+    const size_t want = (len + kMin - 1) / kMin * kMin;
+    {
+      std::lock_guard<std::mutex> lk(mu_);
+      auto it = free_.lower_bound(want);
+      if (it != free_.end() && it->first <= want + want / 4) {
+        char* p = it->second;
+        *cap = it->first;
+        held_ -= it->first;
+        free_.erase(it);
+        return p;
+      }
+    }
+    *cap = want;
+    return new char[want];
+  }
+  void Put(char* p, size_t cap) {
+    if (cap >= kMin) {
+      std::lock_guard<std::mutex> lk(mu_);
+      if (held_ + cap <= limit_) {
+        free_.emplace(cap, p);
+        held_ += cap;
+        return;
+      }
+    }
+    delete[] p;
+  }
+
+ private:
+  std::mutex mu_;
+  std::multimap<size_t, char*> free_;
+  size_t held_ = 0;
+  const size_t limit_;
+};
+
 // Receive-side state of one accepted connection.
 struct InConn {
   int fd = -1;
@@ -87,6 +163,10 @@ struct InConn {
   char* dst = nullptr;    // where the current phase reads into
   size_t need = 0, got = 0;
   char* frame_buf = nullptr;  // buffer of the data frame being read (not yet owned by msg)
+  size_t frame_cap = 0;       // what RecvPool::Put wants back with it
+  ShmRef shm_ref{};           // body of a shared-memory frame
+  bool frame_is_shm = false;
+  std::deque<int> fds;        // descriptors received and not yet claimed by a frame
 };
 
 struct OutConn {
@@ -126,6 +206,7 @@ class TcpVan : public Van {
     for (auto& kv : in_) {
       ::close(kv.first);
       delete[] kv.second.frame_buf;
+      for (int f : kv.second.fds) ::close(f);
     }
     in_.clear();
     {
@@ -216,6 +297,8 @@ class TcpVan : public Van {
     FrameHeader h{kMagic, msg.meta.sender, msg.meta.recver, static_cast<uint32_t>(meta.size()),
                   static_cast<uint32_t>(n)};
     std::vector<uint64_t> lens(n);
+    std::vector<ShmRef> refs(n);
+    std::vector<int> fds;
     std::vector<struct iovec> iov;
     iov.reserve(3 + n);
     iov.push_back({&h, sizeof(h)});
@@ -225,22 +308,38 @@ class TcpVan : public Van {
           << "device-resident payloads travel through the device data plane, not the socket van";
       lens[i] = msg.data[i].size();
       total += lens[i] + 8;
+      int fd = -1;
+      if (local_ && lens[i] &&
+          shm::Share(msg.data[i].data(), lens[i], &fd, &refs[i].offset, &refs[i].seg_size)) {
+        // the peer maps the segment instead of receiving the bytes
+        lens[i] |= kShmFrame;
+        fds.push_back(fd);
+      }
     }
     if (n) iov.push_back({lens.data(), n * sizeof(uint64_t)});
     iov.push_back({const_cast<char*>(meta.data()), meta.size()});
-    for (size_t i = 0; i < n; ++i)
-      if (lens[i]) iov.push_back({msg.data[i].data(), static_cast<size_t>(lens[i])});
+    for (size_t i = 0; i < n; ++i) {
+      if (lens[i] & kShmFrame) {
+        iov.push_back({&refs[i], sizeof(ShmRef)});
+      } else if (lens[i]) {
+        iov.push_back({msg.data[i].data(), static_cast<size_t>(lens[i])});
+      }
+    }
 
     std::lock_guard<std::mutex> lk(c->mu);
     for (int attempt = 0; attempt < 2; ++attempt) {
       if (c->fd < 0) c->fd = Dial(c->host, c->port);
-      if (c->fd < 0) return -1;
+      if (c->fd < 0) break;
       std::vector<struct iovec> tmp = iov;
-      if (WriteAll(c->fd, tmp.data(), static_cast<int>(tmp.size()))) return static_cast<int>(total);
+      if (WriteAll(c->fd, tmp.data(), static_cast<int>(tmp.size()), fds))
+        return static_cast<int>(total);
       // the peer went away (for instance it was replaced): reconnect once
       ::close(c->fd);
       c->fd = -1;
     }
+    // nobody will map the shared frames of this message
+    for (size_t i = 0; i < n; ++i)
+      if (lens[i] & kShmFrame) shm::Unshare(msg.data[i].data());
     return -1;
   }
 
@@ -366,8 +465,25 @@ class TcpVan : public Van {
         case InConn::kData: {
           // frame `c->frame` is complete: hand its buffer to the message
           SArray<char> arr;
-          arr.reset(c->frame_buf, c->lens[c->frame], [](char* p) { delete[] p; });
-          c->frame_buf = nullptr;
+          if (c->frame_is_shm) {
+            // the bytes stay where the sender has them: map its segment
+            const uint64_t len = c->lens[c->frame] & ~kShmFrame;
+            if (c->fds.empty()) return false;
+            const int fd = c->fds.front();
+            c->fds.pop_front();
+            if (c->shm_ref.offset + len > c->shm_ref.seg_size) {
+              ::close(fd);
+              return false;
+            }
+            char* base = shm::Import(fd, c->shm_ref.seg_size);
+            if (!base) return false;
+            arr.reset(base + c->shm_ref.offset, len, [base](char*) { shm::Release(base); });
+          } else {
+            std::shared_ptr<RecvPool> pool = recv_pool_;
+            const size_t cap = c->frame_cap;
+            arr.reset(c->frame_buf, c->lens[c->frame], [pool, cap](char* p) { pool->Put(p, cap); });
+            c->frame_buf = nullptr;
+          }
           c->msg.data.push_back(arr);
           ++c->frame;
           if (!NextFrame(c)) return true;
@@ -383,14 +499,20 @@ class TcpVan : public Van {
   bool NextFrame(InConn* c) {
     if (c->frame >= c->lens.size()) {
       size_t bytes = c->meta.size();
-      for (uint64_t l : c->lens) bytes += l;
+      for (uint64_t l : c->lens) bytes += (l & ~kShmFrame);
       c->msg.meta.data_size = static_cast<int>(bytes - c->meta.size());
       Deliver(std::move(c->msg));
       Arm(c, InConn::kHeader, reinterpret_cast<char*>(&c->hdr), sizeof(FrameHeader));
       return false;
     }
+    if (c->lens[c->frame] & kShmFrame) {
+      c->frame_is_shm = true;
+      Arm(c, InConn::kData, reinterpret_cast<char*>(&c->shm_ref), sizeof(ShmRef));
+      return true;
+    }
+    c->frame_is_shm = false;
     const size_t len = c->lens[c->frame];
-    c->frame_buf = new char[len ? len : 1];
+    c->frame_buf = recv_pool_->Get(len, &c->frame_cap);
     Arm(c, InConn::kData, c->frame_buf, len);
     return true;
   }
@@ -401,8 +523,32 @@ class TcpVan : public Van {
     auto it = in_.find(fd);
     if (it != in_.end()) {
       delete[] it->second.frame_buf;
+      for (int f : it->second.fds) ::close(f);
       in_.erase(it);
     }
+  }
+
+  // read() for a Unix socket: descriptors that ride on the bytes are queued on the connection.
+  ssize_t ReadWithFds(int fd, InConn* c) {
+    alignas(struct cmsghdr) char ctrl[CMSG_SPACE(sizeof(int) * kMaxFrames)];
+    struct iovec iov {c->dst + c->got, c->need - c->got};
+    struct msghdr mh {};
+    mh.msg_iov = &iov;
+    mh.msg_iovlen = 1;
+    mh.msg_control = ctrl;
+    mh.msg_controllen = sizeof(ctrl);
+    ssize_t n = ::recvmsg(fd, &mh, MSG_CMSG_CLOEXEC);
+    if (n < 0) return n;
+    for (struct cmsghdr* cm = CMSG_FIRSTHDR(&mh); cm; cm = CMSG_NXTHDR(&mh, cm)) {
+      if (cm->cmsg_level != SOL_SOCKET || cm->cmsg_type != SCM_RIGHTS) continue;
+      const size_t cnt = (cm->cmsg_len - CMSG_LEN(0)) / sizeof(int);
+      for (size_t i = 0; i < cnt; ++i) {
+        int f;
+        memcpy(&f, CMSG_DATA(cm) + i * sizeof(int), sizeof(int));
+        c->fds.push_back(f);
+      }
+    }
+    return n;
   }
 
   void OnReadable(int fd) {
@@ -417,7 +563,7 @@ class TcpVan : public Van {
           return;
         }
       }
-      ssize_t n = ::read(fd, c->dst + c->got, c->need - c->got);
+      ssize_t n = local_ ? ReadWithFds(fd, c) : ::read(fd, c->dst + c->got, c->need - c->got);
       if (n > 0) {
         c->got += static_cast<size_t>(n);
         continue;
@@ -469,6 +615,7 @@ class TcpVan : public Van {
   }
 
   bool local_ = false;
+  std::shared_ptr<RecvPool> recv_pool_ = std::make_shared<RecvPool>();
   int epfd_ = -1, wakefd_ = -1, listen_fd_ = -1;
   std::string unix_path_;
   std::atomic<bool> io_stop_{false};

@@ -94,6 +94,23 @@ def test_two_customers_in_one_worker_process(core_lib):
     assert rc == 0 and "CUSTOMER_OK 0" in out and "CUSTOMER_OK 1" in out, out[-3000:]
 
 
+def test_shm_pool_unit(core_lib):
+    """Shared-memory array pool: recycling, views that outlive their array, own segments echoed."""
+    r = subprocess.run([_prog("shm_frames", core_lib)], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "SHM_UNIT_OK" in r.stderr, r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("env", [{}, {"PS_RESEND": "1", "PS_RESEND_TIMEOUT": "200",
+                                      "PS_DROP_MSG": "10"}], ids=["plain", "drop-resend"])
+def test_shm_frames_between_processes(core_lib, env):
+    """DMLC_LOCAL=1: large arrays are mapped by the receiver instead of being copied through the
+    socket; a server that keeps received arrays must see them unchanged after the worker has
+    freed and recycled its buffers."""
+    env = dict(env, DMLC_LOCAL="1")
+    rc, out = _job([_prog("shm_frames", core_lib), "job"], num_workers=2, num_servers=2, env=env)
+    assert rc == 0 and out.count("SHM_JOB_OK") == 2, out[-3000:]
+
+
 @pytest.mark.parametrize("repeat", range(3))
 def test_message_loss_with_resend(core_lib, repeat):
     """10 % of received messages are dropped; ACK/resend/de-duplication must hide it."""
