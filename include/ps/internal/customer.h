@@ -28,8 +28,13 @@ class Customer {
   using RecvHandle = std::function<void(const Message& recved)>;
   enum Side { kWorkerSide = 0, kServerSide = 1 };
 
-  // Registers with the Postoffice and starts the handler thread.
-  Customer(int app_id, int customer_id, const RecvHandle& recv_handle, Side side = kWorkerSide);
+  // Registers with the Postoffice and starts the handler thread.  With start = false the
+  // thread is started by StartReceiving(): an application object that stores the pointer to
+  // its Customer needs that store to happen before the first message is handled (messages
+  // that arrive earlier wait in the queue).
+  Customer(int app_id, int customer_id, const RecvHandle& recv_handle, Side side = kWorkerSide,
+           bool start = true);
+  void StartReceiving();
   // Unregisters, drains and joins the handler thread.
   ~Customer();
 

@@ -41,6 +41,8 @@ class Postoffice {
 
   void AddCustomer(Customer* customer);
   void RemoveCustomer(Customer* customer);
+  // The lock under which the van delivers a message to a customer (see customer_gate_).
+  std::mutex& customer_gate() { return customer_gate_; }
   // Looks up a registered customer; polls up to `timeout` seconds for it to appear.
   // `side` < 0 accepts either side (worker-side preferred).
   Customer* GetCustomer(int app_id, int customer_id, int timeout = 0, int side = -1) const;
@@ -94,6 +96,9 @@ class Postoffice {
 
   Van* van_ = nullptr;
   mutable std::mutex mu_;
+  // Held by the van while it looks a customer up and hands it a message, and by
+  // RemoveCustomer: once a customer has been removed, no delivery to it is under way.
+  std::mutex customer_gate_;
   // (app_id, customer_id, side) -> customer
   std::map<std::tuple<int, int, int>, Customer*> customers_;
   std::unordered_map<int, std::vector<int>> node_ids_;

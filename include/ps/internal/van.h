@@ -18,6 +18,7 @@
 #define PS_INTERNAL_VAN_H_
 #include <atomic>
 #include <chrono>
+#include <condition_variable>
 #include <ctime>
 #include <memory>
 #include <mutex>
@@ -127,6 +128,12 @@ class Van {
 
   std::atomic<bool> ready_{false};
   std::atomic<bool> stopping_{false};
+  // Send gate: Stop() closes it and waits for the sends that are inside, so that a response
+  // still being sent by an application thread never meets a half-dismantled van.
+  std::mutex send_gate_mu_;
+  std::condition_variable send_gate_cv_;
+  int sends_in_flight_ = 0;
+  bool send_closed_ = false;
   std::atomic<size_t> send_bytes_{0};
   std::atomic<size_t> recv_bytes_{0};
   std::atomic<int> timestamp_{0};

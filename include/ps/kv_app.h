@@ -8,7 +8,10 @@
 #ifndef PS_KV_APP_H_
 #define PS_KV_APP_H_
 #include <algorithm>
+#include <chrono>
+#include <condition_variable>
 #include <functional>
+#include <memory>
 #include <mutex>
 #include <unordered_map>
 #include <utility>
@@ -43,7 +46,8 @@ class KVWorker : public SimpleApp {
     slicer_ = [this](const KVPairs<Val>& send, const std::vector<Range>& ranges,
                      SlicedKVs* sliced) { DefaultSlicer(send, ranges, sliced); };
     obj_ = new Customer(app_id, customer_id, [this](const Message& m) { Process(m); },
-                        Customer::kWorkerSide);
+                        Customer::kWorkerSide, /*start=*/false);
+    obj_->StartReceiving();  // only now: Process uses obj_
   }
   virtual ~KVWorker() {
     delete obj_;
@@ -357,7 +361,8 @@ class KVServer : public SimpleApp {
   // The server-side endpoint of app `app_id`.
   explicit KVServer(int app_id) : SimpleApp() {
     obj_ = new Customer(app_id, app_id, [this](const Message& m) { Process(m); },
-                        Customer::kServerSide);
+                        Customer::kServerSide, /*start=*/false);
+    obj_->StartReceiving();  // only now: Process uses obj_
   }
   virtual ~KVServer() {
     delete obj_;
@@ -370,7 +375,11 @@ class KVServer : public SimpleApp {
                                        KVServer* server)>;
   void set_request_handle(const ReqHandle& request_handle) {
     CHECK(request_handle) << "invalid request handle";
-    request_handle_ = request_handle;
+    {
+      std::lock_guard<std::mutex> lk(handle_mu_);
+      request_handle_ = std::make_shared<ReqHandle>(request_handle);
+    }
+    handle_cv_.notify_all();
   }
 
   // Answers request `req`; `res` carries the pulled pairs (empty for a push).
@@ -420,11 +429,24 @@ class KVServer : public SimpleApp {
       }
     }
     data.priority = msg.meta.priority;
-    CHECK(request_handle_) << "no request handle set on the server";
-    request_handle_(meta, data, this);
+    // A request can arrive between the construction of the server and set_request_handle
+    // (the receive thread starts with the constructor): it waits for the handle instead of
+    // failing.  One instance of the handle serves every request, so a handle with state of
+    // its own (such as KVServerDefaultHandle's store) keeps it.
+    std::shared_ptr<ReqHandle> handle;
+    {
+      std::unique_lock<std::mutex> lk(handle_mu_);
+      handle_cv_.wait_for(lk, std::chrono::seconds(30),
+                          [this] { return request_handle_ != nullptr; });
+      handle = request_handle_;
+    }
+    CHECK(handle) << "no request handle set on the server";
+    (*handle)(meta, data, this);
   }
 
-  ReqHandle request_handle_;
+  std::mutex handle_mu_;
+  std::condition_variable handle_cv_;
+  std::shared_ptr<ReqHandle> request_handle_;
 };
 
 // Example server handle: values are accumulated per key (push: store[key] += val; pull:

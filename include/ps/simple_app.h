@@ -3,6 +3,8 @@
 #ifndef PS_SIMPLE_APP_H_
 #define PS_SIMPLE_APP_H_
 #include <functional>
+#include <memory>
+#include <mutex>
 #include <string>
 
 #include "ps/internal/message.h"
@@ -24,8 +26,9 @@ class SimpleApp {
   // `app_id` must match on every node that talks to this app; `customer_id` distinguishes
   // several endpoints of the app inside one process.
   explicit SimpleApp(int app_id, int customer_id) : SimpleApp() {
-    obj_ = new Customer(app_id, customer_id,
-                        [this](const Message& msg) { this->Process(msg); });
+    obj_ = new Customer(app_id, customer_id, [this](const Message& msg) { this->Process(msg); },
+                        Customer::kWorkerSide, /*start=*/false);
+    obj_->StartReceiving();  // only now: Process and Response use obj_
   }
   virtual ~SimpleApp() {
     delete obj_;
@@ -67,21 +70,26 @@ class SimpleApp {
   }
 
   using Handle = std::function<void(const SimpleData& recved, SimpleApp* app)>;
+  // Handles may be replaced while messages are already arriving (the receive thread starts
+  // with the constructor): a message is served by the handle installed when it is processed.
   virtual inline void set_request_handle(const Handle& request_handle) {
     CHECK(request_handle) << "invalid request handle";
-    request_handle_ = request_handle;
+    std::lock_guard<std::mutex> lk(handle_mu_);
+    request_handle_ = std::make_shared<Handle>(request_handle);
   }
   virtual inline void set_response_handle(const Handle& response_handle) {
     CHECK(response_handle) << "invalid response handle";
-    response_handle_ = response_handle;
+    std::lock_guard<std::mutex> lk(handle_mu_);
+    response_handle_ = std::make_shared<Handle>(response_handle);
   }
   virtual inline Customer* get_customer() { return obj_; }
 
  protected:
   // For subclasses that create their own Customer.
   inline SimpleApp() : obj_(nullptr) {
-    request_handle_ = [](const SimpleData& recved, SimpleApp* app) { app->Response(recved); };
-    response_handle_ = [](const SimpleData&, SimpleApp*) {};
+    request_handle_ = std::make_shared<Handle>(
+        [](const SimpleData& recved, SimpleApp* app) { app->Response(recved); });
+    response_handle_ = std::make_shared<Handle>([](const SimpleData&, SimpleApp*) {});
   }
   // Dispatches a received simple-app message to the request or response handler.
   virtual inline void Process(const Message& msg) {
@@ -91,15 +99,19 @@ class SimpleApp {
     recv.body = msg.meta.body;
     recv.timestamp = msg.meta.timestamp;
     recv.customer_id = msg.meta.customer_id;
+    std::shared_ptr<Handle> handle;
+    {
+      std::lock_guard<std::mutex> lk(handle_mu_);
+      handle = msg.meta.request ? request_handle_ : response_handle_;
+    }
+    CHECK(handle && *handle);
     if (msg.meta.request) {
-      CHECK(request_handle_);
       // a process with several node ids answers from the id that was addressed
       reply_from_ = msg.meta.recver;
-      request_handle_(recv, this);
+      (*handle)(recv, this);
       reply_from_ = Meta::kEmpty;
     } else {
-      CHECK(response_handle_);
-      response_handle_(recv, this);
+      (*handle)(recv, this);
     }
   }
 
@@ -108,8 +120,9 @@ class SimpleApp {
   int reply_from_ = Meta::kEmpty;
 
  private:
-  Handle request_handle_;
-  Handle response_handle_;
+  std::mutex handle_mu_;
+  std::shared_ptr<Handle> request_handle_;
+  std::shared_ptr<Handle> response_handle_;
 };
 
 }  // namespace ps

@@ -6,10 +6,15 @@
 
 namespace ps {
 
-Customer::Customer(int app_id, int customer_id, const RecvHandle& recv_handle, Side side)
+Customer::Customer(int app_id, int customer_id, const RecvHandle& recv_handle, Side side,
+                   bool start)
     : app_id_(app_id), customer_id_(customer_id), side_(side), recv_handle_(recv_handle) {
   Postoffice::Get()->AddCustomer(this);
-  recv_thread_.reset(new std::thread(&Customer::Receiving, this));
+  if (start) StartReceiving();
+}
+
+void Customer::StartReceiving() {
+  if (!recv_thread_) recv_thread_.reset(new std::thread(&Customer::Receiving, this));
 }
 
 Customer::~Customer() {
@@ -19,7 +24,7 @@ Customer::~Customer() {
   // lowest possible priority: everything already queued is handled first
   stop.meta.priority = INT_MIN;
   recv_queue_.Push(stop);
-  recv_thread_->join();
+  if (recv_thread_) recv_thread_->join();
 }
 
 int Customer::NewRequest(int recver) {

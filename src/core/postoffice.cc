@@ -164,6 +164,7 @@ void Postoffice::AddCustomer(Customer* customer) {
 }
 
 void Postoffice::RemoveCustomer(Customer* customer) {
+  std::lock_guard<std::mutex> gate(customer_gate_);
   std::lock_guard<std::mutex> lk(mu_);
   customers_.erase(std::make_tuple(customer->app_id(), customer->customer_id(),
                                    static_cast<int>(customer->side())));

@@ -172,6 +172,7 @@ struct InConn {
 struct OutConn {
   std::mutex mu;
   int fd = -1;
+  bool was_connected = false;  // a connection to this address has existed before
   std::string host;
   int port = 0;
 };
@@ -328,8 +329,9 @@ class TcpVan : public Van {
 
     std::lock_guard<std::mutex> lk(c->mu);
     for (int attempt = 0; attempt < 2; ++attempt) {
-      if (c->fd < 0) c->fd = Dial(c->host, c->port);
+      if (c->fd < 0) c->fd = Dial(c->host, c->port, c->was_connected);
       if (c->fd < 0) break;
+      c->was_connected = true;
       std::vector<struct iovec> tmp = iov;
       if (WriteAll(c->fd, tmp.data(), static_cast<int>(tmp.size()), fds))
         return static_cast<int>(total);
@@ -382,10 +384,16 @@ class TcpVan : public Van {
   }
 
   // Blocking connect with retries: peers may still be starting.
-  int Dial(const std::string& host, int port) {
+  // Connects to host:port.  A peer that has never been reached may still be starting up, so
+  // the first connection keeps trying for PS_CONNECT_TIMEOUT seconds.  A peer that was
+  // connected before and no longer accepts has gone away: `redial` gives it a quarter of a
+  // second, so that a caller with more to send (the resender, above all) is not held up.
+  int Dial(const std::string& host, int port, bool redial) {
     const int water = GetEnv("DMLC_PS_WATER_MARK", 0);
-    const auto deadline = std::chrono::steady_clock::now() +
-                          std::chrono::seconds(GetEnv("PS_CONNECT_TIMEOUT", 60));
+    const auto deadline =
+        std::chrono::steady_clock::now() +
+        (redial ? std::chrono::milliseconds(250)
+                : std::chrono::milliseconds(1000LL * GetEnv("PS_CONNECT_TIMEOUT", 60)));
     while (!stopping()) {
       int fd = -1;
       bool ok = false;

@@ -80,6 +80,10 @@ void Van::Start(int customer_id) {
     std::lock_guard<std::mutex> lk(start_mu_);
     if (init_stage_ == 0) {
       stopping_ = false;
+      {
+        std::lock_guard<std::mutex> gate(send_gate_mu_);
+        send_closed_ = false;
+      }
       scheduler_.hostname = GetEnv("DMLC_PS_ROOT_URI", std::string("127.0.0.1"));
       scheduler_.port = GetEnv("DMLC_PS_ROOT_PORT", 0);
       scheduler_.role = Node::SCHEDULER;
@@ -175,9 +179,12 @@ void Van::Start(int customer_id) {
 
 void Van::Stop() {
   if (resender_) {
-    // give lost final messages (for instance a barrier release) a chance to be resent
+    // Give lost final messages (for instance a barrier release) a chance to be resent: a peer
+    // that never gets it would wait forever.  Retransmissions back off (after 1, 3, 6 and 10
+    // timeouts), so ten timeouts cover four of them; with everything acknowledged this
+    // returns at once.
     resender_->set_quiet(true);
-    resender_->WaitDrained(3 * GetEnv("PS_RESEND_TIMEOUT", 1000));
+    resender_->WaitDrained(10 * GetEnv("PS_RESEND_TIMEOUT", 1000));
   }
   // wake the receive loop with a TERMINATE addressed to ourselves
   Message exit;
@@ -199,6 +206,12 @@ void Van::Stop() {
   }
   if (heartbeat_thread_) heartbeat_thread_->join();
   heartbeat_thread_.reset();
+  {
+    // no send may be inside the van while it is taken apart; later ones are refused
+    std::unique_lock<std::mutex> lk(send_gate_mu_);
+    send_closed_ = true;
+    send_gate_cv_.wait(lk, [this] { return sends_in_flight_ == 0; });
+  }
   delete resender_;
   resender_ = nullptr;
   StopBackend();
@@ -231,6 +244,18 @@ int Van::Send(const Message& msg) {
 }
 
 int Van::Transmit(const Message& m) {
+  {
+    std::lock_guard<std::mutex> lk(send_gate_mu_);
+    if (send_closed_) return -1;
+    ++sends_in_flight_;
+  }
+  struct Leave {
+    Van* v;
+    ~Leave() {
+      std::lock_guard<std::mutex> lk(v->send_gate_mu_);
+      if (--v->sends_in_flight_ == 0) v->send_gate_cv_.notify_all();
+    }
+  } leave{this};
   int bytes;
   if (ready_.load() && IsLocalId(m.meta.recver)) {
     bytes = DeliverLocal(m);
@@ -334,9 +359,12 @@ void Van::ProcessDataMsg(Message* msg) {
   CHECK_NE(msg->meta.sender, Meta::kEmpty);
   CHECK_NE(msg->meta.recver, Meta::kEmpty);
   CHECK_NE(msg->meta.app_id, Meta::kEmpty);
-  if (Customer* c = FindCustomer(*msg)) {
-    c->Accept(*msg);
-    return;
+  {
+    std::lock_guard<std::mutex> gate(Postoffice::Get()->customer_gate());
+    if (Customer* c = FindCustomer(*msg)) {
+      c->Accept(*msg);
+      return;
+    }
   }
   // The application endpoint does not exist yet (a peer was faster than this node's own
   // start-up).  The receive loop must not wait for it -- the barrier release that lets the
@@ -350,8 +378,15 @@ void Van::RetryParked() {
   const int limit_s = GetEnv("PS_CUSTOMER_TIMEOUT", 30);
   const auto now = std::chrono::steady_clock::now();
   for (auto it = parked_.begin(); it != parked_.end();) {
-    if (Customer* c = FindCustomer(it->msg)) {
-      c->Accept(it->msg);
+    bool delivered = false;
+    {
+      std::lock_guard<std::mutex> gate(Postoffice::Get()->customer_gate());
+      if (Customer* c = FindCustomer(it->msg)) {
+        c->Accept(it->msg);
+        delivered = true;
+      }
+    }
+    if (delivered) {
       it = parked_.erase(it);
     } else if (now - it->since > std::chrono::seconds(limit_s)) {
       LOG(ERROR) << "dropping a message for which no customer appeared within " << limit_s

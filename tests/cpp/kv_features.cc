@@ -76,6 +76,9 @@ int main() {
     CHECK_EQ(d.body, std::string("ack"));
     ++responses;
   });
+  // a request that arrives before the handles above are installed would be answered by the
+  // default handle: nobody sends one before everybody is here
+  Postoffice::Get()->Barrier(0, kScheduler + kServerGroup + kWorkerGroup);
 
   if (IsWorker()) {
     KVWorker<float> kv(0, 0);

@@ -1,0 +1,83 @@
+"""Race and memory-error detection for the host runtime: the C++ test programs rebuilt with
+ThreadSanitizer and AddressSanitizer (+ leak check) and run in the usual layouts.
+
+Takes a few minutes of compile time, so it only runs when ``PS_RUN_SANITIZERS=1`` is set
+(``PS_RUN_SANITIZERS=1 python -m pytest tests/test_sanitizers.py -q``).  The reference offers
+the same through ``make ASAN=1`` (Makefile:29-31 there); ``make ASAN=1`` / ``make TSAN=1`` work
+here too.
+"""
+import glob
+import os
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.skipif(os.environ.get("PS_RUN_SANITIZERS") != "1",
+                                reason="set PS_RUN_SANITIZERS=1 to run the sanitizer builds")
+PROGRAMS = ["unit_core", "loop_kv", "shm_frames", "kv_config1", "kv_features"]
+MARKS = {"thread": "WARNING: ThreadSanitizer", "address": "ERROR: AddressSanitizer"}
+
+
+@pytest.fixture(scope="module", params=["thread", "address"])
+def san(request):
+    kind = request.param
+    out = os.path.join(ROOT, "build", "san", kind)
+    os.makedirs(out, exist_ok=True)
+    flags = ["-std=c++17", "-O1", "-g", "-fPIC", "-pthread", f"-fsanitize={kind}",
+             "-fno-omit-frame-pointer", "-I", os.path.join(ROOT, "include"),
+             "-I", os.path.join(ROOT, "src")]
+    objs, procs = [], []
+    for src in sorted(glob.glob(os.path.join(ROOT, "src", "core", "*.cc")) +
+                      glob.glob(os.path.join(ROOT, "src", "van", "*.cc"))):
+        obj = os.path.join(out, os.path.basename(src)[:-3] + ".o")
+        objs.append(obj)
+        procs.append(subprocess.Popen(["g++", *flags, "-c", src, "-o", obj]))
+    assert all(p.wait() == 0 for p in procs)
+    lib = os.path.join(out, "libps_san.a")
+    if os.path.exists(lib):
+        os.remove(lib)
+    subprocess.check_call(["ar", "cr", lib, *objs])
+    procs = [subprocess.Popen(["g++", *flags, os.path.join(ROOT, "tests", "cpp", p + ".cc"), lib,
+                               "-o", os.path.join(out, p)]) for p in PROGRAMS]
+    assert all(p.wait() == 0 for p in procs)
+    return kind, out
+
+
+def _clean(kind, text):
+    assert MARKS[kind] not in text, text[text.find(MARKS[kind]):][:4000]
+    assert "LeakSanitizer" not in text, text[text.find("LeakSanitizer"):][:4000]
+
+
+@pytest.mark.parametrize("prog,token", [("unit_core", "UNIT_OK"), ("loop_kv", "LOOP_OK"),
+                                        ("shm_frames", "SHM_UNIT_OK")])
+def test_single_process_programs(san, prog, token):
+    kind, out = san
+    r = subprocess.run([os.path.join(out, prog)], capture_output=True, text=True, timeout=600)
+    _clean(kind, r.stdout + r.stderr)
+    assert r.returncode == 0 and token in r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("prog,args,env,layout,token,count", [
+    ("kv_config1", [], {}, dict(num_workers=2, num_servers=2), "CONFIG1_OK", 2),
+    ("kv_config1", [], {"DMLC_LOCAL": "1"}, dict(num_workers=2, num_servers=2), "CONFIG1_OK", 2),
+    ("kv_config1", [], {"DMLC_PS_VAN_TYPE": "p3"}, dict(num_workers=2, num_servers=2),
+     "CONFIG1_OK", 2),
+    ("kv_config1", [], {}, dict(num_joint=2), "CONFIG1_OK", 2),
+    ("kv_features", [], {}, dict(num_workers=3, num_servers=2), "FEATURES_OK", 3),
+    ("kv_features", [], {}, dict(num_joint=3), "FEATURES_OK", 3),
+    ("shm_frames", ["job"], {"DMLC_LOCAL": "1"}, dict(num_workers=2, num_servers=2),
+     "SHM_JOB_OK", 2),
+    ("shm_frames", ["job"], {"DMLC_LOCAL": "1", "PS_RESEND": "1", "PS_RESEND_TIMEOUT": "300",
+                             "PS_DROP_MSG": "10"}, dict(num_workers=2, num_servers=2),
+     "SHM_JOB_OK", 2),
+])
+def test_multi_process_programs(san, prog, args, env, layout, token, count):
+    from ps_lite_b200.launch.local import LocalJob
+    kind, out = san
+    job = LocalJob([os.path.join(out, prog), *args], capture=True, env=env, **layout)
+    job.start()
+    rc = job.wait(600)
+    text = job.output()
+    _clean(kind, text)
+    assert rc == 0 and text.count(token) == count, text[-3000:]
