@@ -262,10 +262,12 @@ class TcpVan : public Van {
       if (!still_used) {
         auto oc = out_.find(old);
         if (oc != out_.end()) {
-          std::lock_guard<std::mutex> l2(oc->second->mu);
-          if (oc->second->fd >= 0) ::close(oc->second->fd);
-          oc->second->fd = -1;
+          // keep the connection object alive until its lock has been released
+          std::shared_ptr<OutConn> gone = oc->second;
           out_.erase(oc);
+          std::lock_guard<std::mutex> l2(gone->mu);
+          if (gone->fd >= 0) ::close(gone->fd);
+          gone->fd = -1;
         }
       }
     }

@@ -15,7 +15,8 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.skipif(os.environ.get("PS_RUN_SANITIZERS") != "1",
                                 reason="set PS_RUN_SANITIZERS=1 to run the sanitizer builds")
-PROGRAMS = ["unit_core", "loop_kv", "shm_frames", "kv_config1", "kv_features"]
+PROGRAMS = ["unit_core", "loop_kv", "shm_frames", "kv_config1", "kv_features", "multi_customer",
+            "recovery"]
 MARKS = {"thread": "WARNING: ThreadSanitizer", "address": "ERROR: AddressSanitizer"}
 
 
@@ -81,3 +82,30 @@ def test_multi_process_programs(san, prog, args, env, layout, token, count):
     text = job.output()
     _clean(kind, text)
     assert rc == 0 and text.count(token) == count, text[-3000:]
+
+
+@pytest.mark.parametrize("which", ["test_two_customers_in_one_worker_process",
+                                   "test_dead_node_detection_and_recovery"])
+def test_orchestrated_layouts(san, which, monkeypatch):
+    """Two customer threads in one worker process; a worker that dies, is detected through
+    heartbeats and replaced -- the orchestration of tests/test_host_runtime.py on the
+    instrumented binaries."""
+    import importlib.util
+    from ps_lite_b200.launch import local
+    kind, out = san
+    spec = importlib.util.spec_from_file_location(
+        "host_runtime_tests", os.path.join(ROOT, "tests", "test_host_runtime.py"))
+    m = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(m)
+    monkeypatch.setattr(m, "_prog", lambda name, core_lib: os.path.join(out, name))
+    texts = []
+    original = local.LocalJob.output
+
+    def recording(self):
+        texts.append(original(self))
+        return texts[-1]
+    monkeypatch.setattr(local.LocalJob, "output", recording)
+    getattr(m, which)("unused")
+    assert texts
+    for t in texts:
+        _clean(kind, t)
