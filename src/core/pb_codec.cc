@@ -191,6 +191,12 @@ void EncodeMeta(const Meta& m, std::string* out) {
   PutInt32(13, m.priority, out);
 }
 
+// A type tag from the wire; values outside the enumeration (a newer or a corrupt sender)
+// become OTHER instead of an out-of-range enum value.
+static DataType ToDataType(int32_t x) {
+  return (x >= 0 && x <= static_cast<int32_t>(FLOAT16)) ? static_cast<DataType>(x) : OTHER;
+}
+
 bool DecodeMeta(const char* buf, size_t len, Meta* m) {
   Reader r{buf, len};
   const int sender = m->sender, recver = m->recver;
@@ -211,7 +217,7 @@ bool DecodeMeta(const char* buf, size_t len, Meta* m) {
         case 6: m->simple_app = (v != 0); break;
         case 7: m->app_id = x; break;
         case 8: m->timestamp = x; break;
-        case 9: m->data_type.push_back(static_cast<DataType>(x)); break;  // unpacked form
+        case 9: m->data_type.push_back(ToDataType(x)); break;  // unpacked form
         case 10: m->customer_id = x; break;
         case 11: m->data_size = x; break;
         case 12: m->pull = (v != 0); break;
@@ -230,7 +236,7 @@ bool DecodeMeta(const char* buf, size_t len, Meta* m) {
         size_t q = 0;
         while (q < n) {
           if (!GetVarint(p, n, &q, &v)) return false;
-          m->data_type.push_back(static_cast<DataType>(static_cast<int32_t>(v)));
+          m->data_type.push_back(ToDataType(static_cast<int32_t>(v)));
         }
       }
     } else if (!r.skip(wt)) {

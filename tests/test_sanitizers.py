@@ -1,5 +1,6 @@
 """Race and memory-error detection for the host runtime: the C++ test programs rebuilt with
-ThreadSanitizer and AddressSanitizer (+ leak check) and run in the usual layouts.
+ThreadSanitizer, AddressSanitizer (+ leak check) and UndefinedBehaviorSanitizer and run in the
+usual layouts.
 
 Takes a few minutes of compile time, so it only runs when ``PS_RUN_SANITIZERS=1`` is set
 (``PS_RUN_SANITIZERS=1 python -m pytest tests/test_sanitizers.py -q``).  The reference offers
@@ -17,10 +18,11 @@ pytestmark = pytest.mark.skipif(os.environ.get("PS_RUN_SANITIZERS") != "1",
                                 reason="set PS_RUN_SANITIZERS=1 to run the sanitizer builds")
 PROGRAMS = ["unit_core", "loop_kv", "shm_frames", "kv_config1", "kv_features", "multi_customer",
             "recovery"]
-MARKS = {"thread": "WARNING: ThreadSanitizer", "address": "ERROR: AddressSanitizer"}
+MARKS = {"thread": "WARNING: ThreadSanitizer", "address": "ERROR: AddressSanitizer",
+         "undefined": "runtime error:"}
 
 
-@pytest.fixture(scope="module", params=["thread", "address"])
+@pytest.fixture(scope="module", params=["thread", "address", "undefined"])
 def san(request):
     kind = request.param
     out = os.path.join(ROOT, "build", "san", kind)
