@@ -42,8 +42,7 @@ using namespace sm100;
 constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr int kThreads = 256;      // warps 0..5 have roles in a GEMM CTA
-constexpr int kCopyThreads = kThreads;
+constexpr int kThreads = 256;      // warps 0..5: TMA, MMA, 4 x epilogue; warps 6..7: pull ring
 constexpr int kCopyUnroll = 8;
 // pull ring of the GEMM CTAs (see pull_ring_role)
 constexpr int kRingMaxSlots = 8;
