@@ -283,8 +283,8 @@ static void TestMisc() {
   Message d;
   d.AddData(SArray<Key>({1, 2}));
   d.AddData(SArray<float>({1.f, 2.f}));
-  CHECK_EQ(d.meta.data_size, 24);
-  CHECK(d.DebugString().find("UINT64") != std::string::npos);
+  CHECK_EQ(d.meta.data_size, static_cast<int>(2 * sizeof(Key) + 2 * sizeof(float)));
+  CHECK(d.DebugString().find(sizeof(Key) == 8 ? "UINT64" : "UINT32") != std::string::npos);
   bool threw = false;
   try { CHECK_EQ(1, 2) << "boom"; } catch (const dmlc::Error& e) {
     threw = std::string(e.what()).find("boom") != std::string::npos;

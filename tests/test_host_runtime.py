@@ -94,6 +94,33 @@ def test_two_customers_in_one_worker_process(core_lib):
     assert rc == 0 and "CUSTOMER_OK 0" in out and "CUSTOMER_OK 1" in out, out[-3000:]
 
 
+def test_key32_build(tmp_path):
+    """USE_KEY32 (make/ps.mk:8-10 of the reference): keys are 32 bits wide; the runtime, the
+    unit tests and the 2 x 2 correctness job are rebuilt with it."""
+    import glob
+    out = os.path.join(ROOT, "build", "key32")
+    os.makedirs(out, exist_ok=True)
+    flags = ["-std=c++17", "-O1", "-fPIC", "-pthread", "-DUSE_KEY32=1", "-I",
+             os.path.join(ROOT, "include"), "-I", os.path.join(ROOT, "src")]
+    objs, procs = [], []
+    for src in sorted(glob.glob(os.path.join(ROOT, "src", "core", "*.cc")) +
+                      glob.glob(os.path.join(ROOT, "src", "van", "*.cc"))):
+        objs.append(os.path.join(out, os.path.basename(src)[:-3] + ".o"))
+        procs.append(subprocess.Popen(["g++", *flags, "-c", src, "-o", objs[-1]]))
+    assert all(p.wait() == 0 for p in procs)
+    lib = os.path.join(out, "libps_key32.a")
+    if os.path.exists(lib):
+        os.remove(lib)
+    subprocess.check_call(["ar", "cr", lib, *objs])
+    for prog in ("unit_core", "kv_config1"):
+        subprocess.check_call(["g++", *flags, os.path.join(ROOT, "tests", "cpp", prog + ".cc"), lib,
+                               "-o", os.path.join(out, prog)])
+    r = subprocess.run([os.path.join(out, "unit_core")], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "UNIT_OK" in r.stdout, r.stderr[-3000:]
+    rc, text = _job([os.path.join(out, "kv_config1")], num_workers=2, num_servers=2)
+    assert rc == 0 and text.count("CONFIG1_OK") == 2, text[-3000:]
+
+
 def test_shm_pool_unit(core_lib):
     """Shared-memory array pool: recycling, views that outlive their array, own segments echoed."""
     r = subprocess.run([_prog("shm_frames", core_lib)], capture_output=True, text=True, timeout=60)
