@@ -94,6 +94,18 @@ def test_two_customers_in_one_worker_process(core_lib):
     assert rc == 0 and "CUSTOMER_OK 0" in out and "CUSTOMER_OK 1" in out, out[-3000:]
 
 
+@pytest.mark.parametrize("std", ["c++11", "c++14"])
+def test_public_headers_compile_with_older_standards(std):
+    """Programs written for the reference are built with -std=c++11 (its Makefile:21): the
+    public headers must not need anything newer."""
+    for prog in ("kv_config1", "kv_features"):
+        r = subprocess.run(["g++", f"-std={std}", "-O0", "-fsyntax-only", "-I",
+                            os.path.join(ROOT, "include"),
+                            os.path.join(ROOT, "tests", "cpp", prog + ".cc")],
+                           capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-3000:]
+
+
 def test_key32_build(tmp_path):
     """USE_KEY32 (make/ps.mk:8-10 of the reference): keys are 32 bits wide; the runtime, the
     unit tests and the 2 x 2 correctness job are rebuilt with it."""
