@@ -113,6 +113,18 @@ int psdev_heap_destroy(void* base);
 /* Enable direct access from the current device to `peer_device` (same process). */
 int psdev_enable_peer(int peer_device);
 
+/* Arena from the virtual-memory-management API (src/device/vmm_heap.cu): physical memory
+ * exported as a POSIX file descriptor and mapped by every rank.  psdev_vmm_supported: 1 when
+ * the current device offers it.  psdev_vmm_create: arena of at least `bytes` on the current
+ * device; *mapped_bytes is the rounded size that peers pass to psdev_vmm_import, *fd belongs
+ * to the caller (send it to the peers over a Unix socket, then close it); the control region
+ * is cleared.  psdev_vmm_import maps a peer's arena from its descriptor (which stays the
+ * caller's).  psdev_vmm_release unmaps either kind.  No NVSwitch multicast binding is made. */
+int psdev_vmm_supported(void);
+int psdev_vmm_create(size_t bytes, void** base, int* fd, size_t* mapped_bytes);
+int psdev_vmm_import(int fd, size_t mapped_bytes, void** base);
+int psdev_vmm_release(void* base);
+
 /* first-fit sub-allocator over [PSDEV_CTRL_BYTES, bytes): pure host bookkeeping,
  * deterministic, so every rank that issues the same calls gets the same offsets */
 void* psdev_suballoc_new(size_t heap_bytes);

@@ -76,6 +76,10 @@ def _declare(lib: C.CDLL) -> None:
         "psdev_heap_close": (i32, [vp]),
         "psdev_heap_destroy": (i32, [vp]),
         "psdev_enable_peer": (i32, [i32]),
+        "psdev_vmm_supported": (i32, []),
+        "psdev_vmm_create": (i32, [sz, C.POINTER(vp), C.POINTER(C.c_int), C.POINTER(sz)]),
+        "psdev_vmm_import": (i32, [i32, sz, C.POINTER(vp)]),
+        "psdev_vmm_release": (i32, [vp]),
         "psdev_suballoc_new": (vp, [sz]),
         "psdev_suballoc_delete": (None, [vp]),
         "psdev_suballoc_alloc": (i64, [vp, sz, sz]),

@@ -73,6 +73,9 @@ class SymmetricHeap:
             except Exception as exc:  # fall back to CUDA IPC (no multicast alias then)
                 import warnings
                 warnings.warn(f"symmetric-memory heap unavailable ({exc}); using CUDA IPC")
+        if backend == "vmm":
+            self._init_vmm(group, exchange)
+            return
         with torch.cuda.device(self.device):
             base = C.c_void_p()
             handle = C.create_string_buffer(_lib.IPC_HANDLE_BYTES)
@@ -96,6 +99,51 @@ class SymmetricHeap:
                     _lib.check(self.lib.psdev_heap_open(h, C.byref(ptr)), f"psdev_heap_open({p})")
                     self.bases[p] = ptr.value
                     self._opened.append(ptr.value)
+
+    def _init_vmm(self, group, exchange) -> None:
+        """Arena from the virtual-memory-management API (src/device/vmm_heap.cu): the physical
+        allocation is exported as a file descriptor, the descriptors go round over Unix sockets
+        (``fd_exchange.py``) and every rank maps every arena.  No multicast alias."""
+        import os
+        from .fd_exchange import exchange_fds
+        with torch.cuda.device(self.device):
+            if not self.lib.psdev_vmm_supported():
+                raise RuntimeError("this device cannot export allocations as file descriptors")
+            base, fd, mapped = C.c_void_p(), C.c_int(-1), C.c_size_t(0)
+            _lib.check(self.lib.psdev_vmm_create(self.nbytes, C.byref(base), C.byref(fd),
+                                                 C.byref(mapped)), "psdev_vmm_create")
+            self._base = base.value
+            self._vmm_bytes = int(mapped.value)
+            self.bases = [0] * self.world
+            self.bases[self.rank] = self._base
+            self.backend = "vmm"
+            try:
+                if self.world > 1:
+                    if exchange is not None:
+                        gather = exchange
+                    else:
+                        import torch.distributed as dist
+
+                        def gather(payload: bytes):
+                            got = [None] * self.world
+                            dist.all_gather_object(got, payload, group=group)
+                            return got
+                    sizes = [int(x) for x in gather(str(self._vmm_bytes).encode())]
+                    fds = exchange_fds(self.rank, self.world, fd.value, gather)
+                    try:
+                        for p in range(self.world):
+                            if p == self.rank:
+                                continue
+                            ptr = C.c_void_p()
+                            _lib.check(self.lib.psdev_vmm_import(fds[p], sizes[p], C.byref(ptr)),
+                                       f"psdev_vmm_import({p})")
+                            self.bases[p] = ptr.value
+                            self._opened.append(ptr.value)
+                    finally:
+                        for f in fds:
+                            os.close(f)
+            finally:
+                os.close(fd.value)
 
     def _init_symm(self, group) -> None:
         """Arena from torch's symmetric memory: cuMem allocations exchanged among the ranks
@@ -121,7 +169,8 @@ class SymmetricHeap:
 
     # -- single-GPU emulation of a multi-rank job --------------------------------------
     @classmethod
-    def emulated(cls, nbytes: int, world: int, device=None) -> list["SymmetricHeap"]:
+    def emulated(cls, nbytes: int, world: int, device=None,
+                 backend: str = "ipc") -> list["SymmetricHeap"]:
         """``world`` heaps on one GPU in one process; element r is rank r's view.
 
         Kernels that rendezvous must not be launched on these views (all "ranks" share a
@@ -129,7 +178,7 @@ class SymmetricHeap:
         """
         dev = torch.device(device) if device is not None else torch.device(
             "cuda", torch.cuda.current_device())
-        owners = [cls(nbytes, 0, 1, device=dev) for _ in range(world)]
+        owners = [cls(nbytes, 0, 1, device=dev, backend=backend) for _ in range(world)]
         bases = [h._base for h in owners]
         views = [cls(nbytes, r, world, device=dev, _bases=bases, _owner=False)
                  for r in range(world)]
@@ -203,9 +252,10 @@ class SymmetricHeap:
             return
         with torch.cuda.device(self.device):
             torch.cuda.synchronize()
+            vmm = self.backend == "vmm"
             for p in self._opened:
-                self.lib.psdev_heap_close(p)
+                (self.lib.psdev_vmm_release if vmm else self.lib.psdev_heap_close)(p)
             self._opened = []
             if self._base:
-                self.lib.psdev_heap_destroy(self._base)
+                (self.lib.psdev_vmm_release if vmm else self.lib.psdev_heap_destroy)(self._base)
                 self._base = 0

@@ -110,8 +110,7 @@ def test_key32_build(tmp_path):
     """USE_KEY32 (make/ps.mk:8-10 of the reference): keys are 32 bits wide; the runtime, the
     unit tests and the 2 x 2 correctness job are rebuilt with it."""
     import glob
-    out = os.path.join(ROOT, "build", "key32")
-    os.makedirs(out, exist_ok=True)
+    out = str(tmp_path)
     flags = ["-std=c++17", "-O1", "-fPIC", "-pthread", "-DUSE_KEY32=1", "-I",
              os.path.join(ROOT, "include"), "-I", os.path.join(ROOT, "src")]
     objs, procs = [], []

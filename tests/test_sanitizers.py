@@ -10,6 +10,7 @@ here too.
 import glob
 import os
 import subprocess
+import tempfile
 
 import pytest
 
@@ -25,7 +26,8 @@ MARKS = {"thread": "WARNING: ThreadSanitizer", "address": "ERROR: AddressSanitiz
 @pytest.fixture(scope="module", params=["thread", "address", "undefined"])
 def san(request):
     kind = request.param
-    out = os.path.join(ROOT, "build", "san", kind)
+    # outside the source tree: the instrumented objects are large
+    out = os.path.join(tempfile.gettempdir(), f"psb200_san_{os.getuid()}", kind)
     os.makedirs(out, exist_ok=True)
     flags = ["-std=c++17", "-O1", "-g", "-fPIC", "-pthread", f"-fsanitize={kind}",
              "-fno-omit-frame-pointer", "-I", os.path.join(ROOT, "include"),
