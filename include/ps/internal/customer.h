@@ -9,6 +9,7 @@
 // WaitRequest reports it instead of blocking forever.
 #ifndef PS_INTERNAL_CUSTOMER_H_
 #define PS_INTERNAL_CUSTOMER_H_
+#include <chrono>
 #include <atomic>
 #include <condition_variable>
 #include <functional>
@@ -56,10 +57,17 @@ class Customer {
   void AddResponse(int timestamp, int num = 1);
   // Hands a received message to this customer (called by the van's receive thread).
   void Accept(const Message& recved) { recv_queue_.Push(recved); }
+  // False during the first milliseconds of a customer's life (PS_HANDLE_GRACE_MS, default 20).
+  // An application object is constructed first and given its handles afterwards
+  // (`SimpleApp app(0, 0); app.set_request_handle(...)`): a request that was already waiting
+  // for the customer would otherwise be answered by the default handle.  The van keeps such
+  // requests parked until the customer is mature.
+  bool Mature() const;
 
  private:
   void Receiving();
 
+  const std::chrono::steady_clock::time_point created_ = std::chrono::steady_clock::now();
   const int app_id_;
   const int customer_id_;
   const Side side_;

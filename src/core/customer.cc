@@ -13,6 +13,11 @@ Customer::Customer(int app_id, int customer_id, const RecvHandle& recv_handle, S
   if (start) StartReceiving();
 }
 
+bool Customer::Mature() const {
+  static const int grace_ms = GetEnv("PS_HANDLE_GRACE_MS", 20);
+  return std::chrono::steady_clock::now() - created_ >= std::chrono::milliseconds(grace_ms);
+}
+
 void Customer::StartReceiving() {
   if (!recv_thread_) recv_thread_.reset(new std::thread(&Customer::Receiving, this));
 }

@@ -56,7 +56,15 @@ bool Van::IsLocalId(int id) const {
 }
 
 int Van::RecvMsg(Message* msg) {
-  inbox_.WaitAndPop(msg);
+  if (parked_.empty()) {
+    inbox_.WaitAndPop(msg);
+  } else if (!inbox_.WaitAndPopFor(msg, 5)) {
+    // nothing arrived: look at the parked messages again (their customer may exist or be
+    // mature by now) -- same effect as Kick()
+    *msg = Message();
+    msg->meta.body = "__kick__";
+    msg->meta.sender = msg->meta.recver = my_node_.id;
+  }
   return static_cast<int>(MessageBytes(*msg)) + 64;
 }
 
@@ -355,13 +363,20 @@ Customer* Van::FindCustomer(const Message& msg) {
   return c;
 }
 
+// A simple-app request for a customer that has only just been created waits a moment: its
+// application object may not have been given its request handle yet (see Customer::Mature).
+static bool Deliverable(const Message& msg, const Customer* c) {
+  return !(msg.meta.simple_app && msg.meta.request) || c->Mature();
+}
+
 void Van::ProcessDataMsg(Message* msg) {
   CHECK_NE(msg->meta.sender, Meta::kEmpty);
   CHECK_NE(msg->meta.recver, Meta::kEmpty);
   CHECK_NE(msg->meta.app_id, Meta::kEmpty);
   {
     std::lock_guard<std::mutex> gate(Postoffice::Get()->customer_gate());
-    if (Customer* c = FindCustomer(*msg)) {
+    Customer* c = FindCustomer(*msg);
+    if (c && Deliverable(*msg, c)) {
       c->Accept(*msg);
       return;
     }
@@ -381,7 +396,8 @@ void Van::RetryParked() {
     bool delivered = false;
     {
       std::lock_guard<std::mutex> gate(Postoffice::Get()->customer_gate());
-      if (Customer* c = FindCustomer(it->msg)) {
+      Customer* c = FindCustomer(it->msg);
+      if (c && Deliverable(it->msg, c)) {
         c->Accept(it->msg);
         delivered = true;
       }
