@@ -62,7 +62,10 @@ enum {
   PSDEV_ERR_TIMEOUT_EXIT = -3,  /* a peer never finished reading/writing  */
   PSDEV_ERR_UNSUPPORTED = -4,
   PSDEV_ERR_NOMEM = -5,
-  PSDEV_ERR_TIMEOUT_PIPE = -6   /* an mbarrier wait inside a GEMM pipeline ran out */
+  PSDEV_ERR_TIMEOUT_PIPE = -6,  /* an mbarrier wait inside a GEMM pipeline ran out */
+  /* -7: PSDEV_ERR_TOO_LARGE of the no-alloc GEMM (src/kernels/pull_gemm_noalloc.h) */
+  PSDEV_ERR_BOUNDS = -8         /* a buffer does not fit into the heap (host check), or, in the
+                                   checks build, a kernel computed an index outside it */
 };
 
 /* The ranks of one job as seen from this process. */
@@ -71,6 +74,8 @@ typedef struct {
   int32_t world;
   void* peer_base[PSDEV_MAX_RANKS]; /* heap base of every rank in this address space */
   void* mc_base;                    /* NVLS multicast alias of the heap, or NULL       */
+  uint64_t heap_bytes;              /* size of every rank's arena; 0 = unknown (no extent
+                                       checks)                                          */
 } psdev_world_t;
 
 /* Hyper-parameters of the server handle; unused fields are ignored. */

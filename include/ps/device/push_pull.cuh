@@ -52,7 +52,24 @@ struct DenseArgs {
   int nseg;                 // 0: single range [begin, end)
   const long long* segs_in; // multi-slice launch: nseg x (begin, end, priority), device memory
   unsigned long long timeout_ns;
+  // extents, used by the checks build (-DPSDEV_CHECKS): arena size (0 = unknown), elements of
+  // the table, elements of this rank's master/state arrays
+  unsigned long long heap_bytes;
+  long long n_total, local_len;
 };
+
+#ifdef PSDEV_CHECKS
+// Checks build: may the vector of VEC elements at table index i (state index si) be touched?
+template <typename GT, typename OT, int VEC>
+__device__ __forceinline__ bool dense_index_ok(const DenseArgs& a, long long i, long long si) {
+  if (i < 0 || i + VEC > a.n_total || si < 0 || si + VEC > a.local_len) return false;
+  if (a.heap_bytes) {
+    if (a.grad_off + (unsigned long long)(i + VEC) * sizeof(GT) > a.heap_bytes) return false;
+    if (a.weight_off + (unsigned long long)(i + VEC) * sizeof(OT) > a.heap_bytes) return false;
+  }
+  return true;
+}
+#endif
 
 // ---- server handles ---------------------------------------------------------------
 // apply(w, g, s1, s2, o): g is the scaled sum over workers; w, s1, s2 are updated in place.
@@ -325,6 +342,14 @@ __global__ void __launch_bounds__(kDenseThreads)
       for (int u = 0; u < U; ++u) {
         const long long i = i0 + (long long)u * kDenseThreads * VEC;
         live[u] = (i < hi) && (i >= seg_begin);
+#ifdef PSDEV_CHECKS
+        // an index outside the table, the owner's state arrays or the arena is recorded in
+        // the channel's status word and skipped, never dereferenced
+        if (live[u] && !dense_index_ok<GT, OT, VEC>(a, i, st_base + i)) {
+          atomicMin(&ctrl_of(a.base[R])->status[a.channel], (int)PSDEV_ERR_BOUNDS);
+          live[u] = false;
+        }
+#endif
       }
       float w[U][VEC], m[U][VEC], v[U][VEC];
       if constexpr (REDUCE) {

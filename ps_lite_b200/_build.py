@@ -58,21 +58,23 @@ def _headers_stamp() -> str:
     return h.hexdigest()[:16]
 
 
-def _compile_one(src: Path, stamp: str, verbose: bool) -> Path:
-    flags = NVCC_FLAGS if src.suffix == ".cu" else CXX_FLAGS
+def _compile_one(src: Path, stamp: str, verbose: bool, extra: tuple = (),
+                 obj_dir: Path = OBJ_DIR) -> Path:
+    flags = [*(NVCC_FLAGS if src.suffix == ".cu" else CXX_FLAGS), *extra]
     flag_text = " ".join(flags).replace(str(ROOT), "")
     tag = hashlib.sha1(src.read_bytes() + stamp.encode() + flag_text.encode()).hexdigest()[:12]
-    obj = OBJ_DIR / f"{src.stem}.{tag}.o"
+    obj_dir.mkdir(parents=True, exist_ok=True)
+    obj = obj_dir / f"{src.stem}.{tag}.o"
     if obj.exists():
         return obj
-    for old in OBJ_DIR.glob(f"{src.stem}.*.o"):
+    for old in obj_dir.glob(f"{src.stem}.*.o"):
         old.unlink()
     if src.suffix == ".cu":
-        cmd = [NVCC, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [NVCC, *flags, "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd[1:1] = ["-Xptxas", "-v"]
     else:
-        cmd = [CXX, *CXX_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [CXX, *flags, "-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"compile failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
@@ -110,18 +112,26 @@ def _build_lock():
             fcntl.flock(fh, fcntl.LOCK_UN)
 
 
-def build_device(verbose: bool = False) -> Path:
-    """Compile every CUDA source for sm_100a and link libpsb200_device.so."""
+def build_device(verbose: bool = False, checks: bool = False) -> Path:
+    """Compile every CUDA source for sm_100a and link libpsb200_device.so.
+
+    ``checks=True`` builds the checks variant instead (``-DPSDEV_CHECKS``,
+    libpsb200_device_checks.so): the dense kernel verifies every index against the table, the
+    owner's state arrays and the arena before it touches memory, records
+    ``PSDEV_ERR_BOUNDS`` in the channel status and skips the access instead of performing it.
+    ``PSB200_DEVICE_CHECKS=1`` makes the package load that variant."""
     with _build_lock():
-        return _build_device(verbose)
+        return _build_device(verbose, checks)
 
 
-def _build_device(verbose: bool) -> Path:
+def _build_device(verbose: bool, checks: bool = False) -> Path:
     srcs = _sources("src/kernels", "src/device", exts=(".cu",))
     stamp = _headers_stamp()
+    extra = ("-DPSDEV_CHECKS=1",) if checks else ()
+    obj_dir = ROOT / "build" / "obj_checks" if checks else OBJ_DIR
     with ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as ex:
-        objs = list(ex.map(lambda s: _compile_one(s, stamp, verbose), srcs))
-    out = LIB_DIR / "libpsb200_device.so"
+        objs = list(ex.map(lambda s: _compile_one(s, stamp, verbose, extra, obj_dir), srcs))
+    out = LIB_DIR / ("libpsb200_device_checks.so" if checks else "libpsb200_device.so")
     _link(objs, out, cuda=True, extra=[])
     return out
 

@@ -22,13 +22,15 @@ OP_PUSH, OP_PULL, OP_PUSHPULL, OP_PUBLISH = 1, 2, 3, 4
 ERR_NAMES = {
     0: "ok", -1: "bad argument", -2: "timeout waiting for peers to enter",
     -3: "timeout waiting for peers to leave", -4: "unsupported", -5: "out of heap memory",
-    -6: "timeout inside a GEMM pipeline",
+    -6: "timeout inside a GEMM pipeline", -7: "output too wide for the static scratch",
+    -8: "buffer or index outside the heap",
 }
 
 
 class World(C.Structure):
     _fields_ = [("rank", C.c_int32), ("world", C.c_int32),
-                ("peer_base", C.c_void_p * MAX_RANKS), ("mc_base", C.c_void_p)]
+                ("peer_base", C.c_void_p * MAX_RANKS), ("mc_base", C.c_void_p),
+                ("heap_bytes", C.c_uint64)]
 
 
 class Opt(C.Structure):
@@ -127,9 +129,11 @@ def device_lib() -> C.CDLL:
     with _lock:
         if _device_lib is None:
             from . import _build
-            path = _build.LIB_DIR / "libpsb200_device.so"
+            checks = os.environ.get("PSB200_DEVICE_CHECKS") == "1"
+            path = _build.LIB_DIR / ("libpsb200_device_checks.so" if checks
+                                     else "libpsb200_device.so")
             if os.environ.get("PSB200_NO_BUILD") != "1" or not path.exists():
-                path = _build.build_device()
+                path = _build.build_device(checks=checks)
             lib = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
             _declare(lib)
             _device_lib = lib

@@ -216,6 +216,7 @@ class SymmetricHeap:
         for p in range(self.world):
             w.peer_base[p] = self.bases[p]
         w.mc_base = self.mc_base or None
+        w.heap_bytes = self.nbytes
         return w
 
     # -- channel state -----------------------------------------------------------------------

@@ -2,6 +2,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 
 #include "ps/device/push_pull.cuh"
 
@@ -121,6 +122,19 @@ static int dense_op_impl(const psdev_world_t* w, const psdev_table_t* t, int op,
     return PSDEV_ERR_ARG;
   if ((op & PSDEV_OP_PUSH) && !opt) return PSDEV_ERR_ARG;
   if (!t->master) return PSDEV_ERR_ARG;
+  if (w->heap_bytes) {
+    // every buffer of the table must lie inside the arena, behind the control region
+    const uint64_t gsz = t->grad_dtype == PSDEV_F32 ? 4 : (t->grad_dtype == PSDEV_BF16 ? 2 : 1);
+    const uint64_t osz = t->out_dtype == PSDEV_F32 ? 4 : 2;
+    const uint64_t n = static_cast<uint64_t>(t->n);
+    auto inside = [&](uint64_t off, uint64_t bytes) {
+      return off >= PSDEV_CTRL_BYTES && off <= w->heap_bytes && bytes <= w->heap_bytes - off;
+    };
+    if (!inside(t->grad_off, n * gsz) || !inside(t->weight_off, n * osz)) return PSDEV_ERR_BOUNDS;
+    if (t->grad_dtype == PSDEV_I8 &&
+        !inside(t->gscale_off, (n + kInt8Group - 1) / kInt8Group * sizeof(float)))
+      return PSDEV_ERR_BOUNDS;
+  }
   const int W = w->world, R = w->rank;
   DenseArgs a{};
   for (int p = 0; p < W; ++p) {
@@ -149,6 +163,22 @@ static int dense_op_impl(const psdev_world_t* w, const psdev_table_t* t, int op,
     a.mc_base = nullptr;
   }
   a.timeout_ns = timeout_ns;
+  a.heap_bytes = w->heap_bytes;
+  a.n_total = t->n;
+  {
+    // blocks owned by this rank: j = R, R + W, ... below ceil(n / blk)
+    const int64_t nblocks = (t->n + t->blk - 1) / t->blk;
+    const int64_t owned = nblocks > R ? (nblocks - R + W - 1) / W : 0;
+    a.local_len = owned * t->blk;
+  }
+#ifdef PSDEV_CHECKS
+  // Test hook of the checks build: pretend that the table is shorter than it is, so that the
+  // kernel's own index check has something to refuse while every address stays valid.
+  if (const char* shrink = getenv("PSDEV_CHECKS_TEST_SHRINK")) {
+    const long long by = atoll(shrink);
+    if (by > 0 && by < a.n_total) a.n_total -= by;
+  }
+#endif
   a.segs_in = reinterpret_cast<const long long*>(segs);
   a.nseg = nseg;
   a.sched = static_cast<const SchedEntry*>(sched);

@@ -1393,6 +1393,9 @@ extern "C" int psdev_pull_gemm_bf16(const psdev_world_t* w, const psdev_table_t*
   if (!w || !t || w->world < 1 || w->world > PSDEV_MAX_RANKS) return PSDEV_ERR_ARG;
   if (t->out_dtype != PSDEV_BF16) return PSDEV_ERR_UNSUPPORTED;
   if (w_elem_off < 0 || (w_elem_off & 7) || w_elem_off + N * K > t->n) return PSDEV_ERR_ARG;
+  if (w->heap_bytes && (t->weight_off < PSDEV_CTRL_BYTES || t->weight_off > w->heap_bytes ||
+                        static_cast<uint64_t>(t->n) * 2 > w->heap_bytes - t->weight_off))
+    return PSDEV_ERR_BOUNDS;  // the weight buffer must lie inside the arena
   gemm::Args a{};
   a.M = M; a.N = N; a.K = K;
   a.c = static_cast<__nv_bfloat16*>(c);
