@@ -235,6 +235,18 @@ static int fill(SparseArgs* a, const psdev_world_t* w, const psdev_sparse_t* t, 
   a->capacity = t->capacity;
   a->overflow = t->overflow;
   if (t->capacity && ((t->capacity & (t->capacity - 1)) || !t->overflow)) return PSDEV_ERR_ARG;
+  if (w->heap_bytes) {
+    // what can be said without the buffers' capacities: the n staged pairs, their answers and
+    // the W+1 cut points lie inside the arena, behind the control region
+    const uint64_t un = n > 0 ? static_cast<uint64_t>(n) : 0;
+    auto inside = [&](uint64_t off, uint64_t bytes) {
+      return off >= PSDEV_CTRL_BYTES && off <= w->heap_bytes && bytes <= w->heap_bytes - off;
+    };
+    if (!inside(t->keys_off, un * 8) || !inside(t->grads_off, un * 4) ||
+        !inside(t->out_off, un * 4) || !inside(t->pos_off, (w->world + 1) * 8ull) ||
+        !inside(t->acc_off, 0) || (t->capacity && !inside(t->hkeys_off, t->capacity * 8)))
+      return PSDEV_ERR_BOUNDS;
+  }
   return 0;
 }
 

@@ -36,3 +36,33 @@ def test_buffers_outside_the_arena_are_refused():
         rc = lib.psdev_dense_op(C.byref(w), C.byref(t), _lib.OP_PUSHPULL, 0, n, C.byref(opt), 0, 0,
                                 10**9, 0, None)
         assert rc == -8, why
+
+
+def test_sparse_descriptor_is_checked_against_the_arena():
+    """A layout made the way SparseTable makes it passes the extent check (the call then fails
+    later for want of a GPU, or succeeds on a GPU box: anything but -8); one that leaves the
+    arena is refused."""
+    lib = _lib.device_lib()
+    world, max_keys, slots = 2, 1 << 16, 1 << 18
+    heap = 1 << 26
+    sub = lib.psdev_suballoc_new(heap)
+    offs = [lib.psdev_suballoc_alloc(sub, nbytes, 256) for nbytes in
+            (8 * max_keys, 4 * max_keys, 4 * max_keys, 8 * (world + 2), 4 * slots)]
+    lib.psdev_suballoc_delete(sub)
+    assert all(o >= 65536 for o in offs)
+
+    def table(keys_off):
+        t = _lib.Sparse()
+        t.range = 1 << 20
+        t.keys_off, t.grads_off, t.out_off, t.pos_off, t.acc_off = keys_off, *offs[1:]
+        t.w = 0x20000000                         # never dereferenced on this path
+        t.kind = 0
+        return t
+    w = _world(heap)
+    good, bad = table(offs[0]), table(heap - 64)
+    rc_bad = lib.psdev_sparse_scatter(C.byref(w), C.byref(bad), max_keys, 1, None)
+    assert rc_bad == -8
+    import torch
+    if not torch.cuda.is_available():            # with a GPU the good call would really launch
+        rc_good = lib.psdev_sparse_scatter(C.byref(w), C.byref(good), max_keys, 1, None)
+        assert rc_good != -8 and rc_good != -1
