@@ -18,6 +18,7 @@
 #include <netinet/tcp.h>
 #include <sys/epoll.h>
 #include <sys/eventfd.h>
+#include <sys/file.h>
 #include <sys/socket.h>
 #include <limits.h>
 #include <sys/uio.h>
@@ -224,6 +225,8 @@ class TcpVan : public Van {
     listen_fd_ = -1;
     if (!unix_path_.empty()) ::unlink(unix_path_.c_str());
     unix_path_.clear();
+    if (unix_lock_fd_ >= 0) ::close(unix_lock_fd_);  // gives the name back
+    unix_lock_fd_ = -1;
     ::close(wakefd_);
     ::close(epfd_);
     wakefd_ = epfd_ = -1;
@@ -357,12 +360,24 @@ class TcpVan : public Van {
       addr.sun_family = AF_UNIX;
       const std::string path = UnixPath(port);
       strncpy(addr.sun_path, path.c_str(), sizeof(addr.sun_path) - 1);
+      // A port number is only a name here, and two processes can be handed the same one.  The
+      // owner of a name holds a lock on "<path>.lock" for as long as it lives (the kernel drops
+      // it when the process dies, so a stale socket file of a crashed run is not in the way);
+      // whoever cannot get the lock tries another number instead of unlinking a live socket.
+      const int lock_fd = ::open((path + ".lock").c_str(), O_CREAT | O_RDWR | O_CLOEXEC, 0600);
+      if (lock_fd < 0 || flock(lock_fd, LOCK_EX | LOCK_NB) != 0) {
+        if (lock_fd >= 0) ::close(lock_fd);
+        ::close(fd);
+        return -1;
+      }
       ::unlink(path.c_str());
       if (bind(fd, reinterpret_cast<struct sockaddr*>(&addr), sizeof(addr)) != 0) {
+        ::close(lock_fd);
         ::close(fd);
         return -1;
       }
       unix_path_ = path;
+      unix_lock_fd_ = lock_fd;
     } else {
       fd = socket(AF_INET, SOCK_STREAM | SOCK_CLOEXEC, 0);
       if (fd < 0) return -1;
@@ -625,6 +640,7 @@ class TcpVan : public Van {
   }
 
   bool local_ = false;
+  int unix_lock_fd_ = -1;  // lock that marks this process as the owner of its Unix socket name
   std::shared_ptr<RecvPool> recv_pool_ = std::make_shared<RecvPool>();
   int epfd_ = -1, wakefd_ = -1, listen_fd_ = -1;
   std::string unix_path_;
