@@ -20,6 +20,7 @@
 #include <sys/eventfd.h>
 #include <sys/file.h>
 #include <sys/socket.h>
+#include <sys/stat.h>
 #include <limits.h>
 #include <sys/uio.h>
 #include <sys/un.h>
@@ -223,7 +224,10 @@ class TcpVan : public Van {
     }
     if (listen_fd_ >= 0) ::close(listen_fd_);
     listen_fd_ = -1;
-    if (!unix_path_.empty()) ::unlink(unix_path_.c_str());
+    if (!unix_path_.empty()) {
+      ::unlink(unix_path_.c_str());
+      if (unix_lock_fd_ >= 0) ::unlink((unix_path_ + ".lock").c_str());
+    }
     unix_path_.clear();
     if (unix_lock_fd_ >= 0) ::close(unix_lock_fd_);  // gives the name back
     unix_lock_fd_ = -1;
@@ -364,8 +368,13 @@ class TcpVan : public Van {
       // owner of a name holds a lock on "<path>.lock" for as long as it lives (the kernel drops
       // it when the process dies, so a stale socket file of a crashed run is not in the way);
       // whoever cannot get the lock tries another number instead of unlinking a live socket.
-      const int lock_fd = ::open((path + ".lock").c_str(), O_CREAT | O_RDWR | O_CLOEXEC, 0600);
-      if (lock_fd < 0 || flock(lock_fd, LOCK_EX | LOCK_NB) != 0) {
+      const std::string lock_path = path + ".lock";
+      const int lock_fd = ::open(lock_path.c_str(), O_CREAT | O_RDWR | O_CLOEXEC, 0600);
+      struct stat held {}, named {};
+      // the lock file is removed by its owner at Stop: a lock on a file that is no longer the
+      // one behind the name does not count
+      if (lock_fd < 0 || flock(lock_fd, LOCK_EX | LOCK_NB) != 0 || fstat(lock_fd, &held) != 0 ||
+          stat(lock_path.c_str(), &named) != 0 || held.st_ino != named.st_ino) {
         if (lock_fd >= 0) ::close(lock_fd);
         ::close(fd);
         return -1;
