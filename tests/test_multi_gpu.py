@@ -46,3 +46,19 @@ def test_fused_pull_gemm_sparse_and_training_across_gpus(cuda_device):
     nproc = 8 if n >= 8 else (4 if n >= 4 else 2)
     r = _torchrun("mp_fused_check.py", nproc)
     assert r.returncode == 0 and "MP_FUSED_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(os.environ.get("PSB200_TEST_VMM_MULTI") != "1",
+                    reason="set PSB200_TEST_VMM_MULTI=1: the import of cuMem arenas on a peer GPU "
+                           "has not yet been run on a multi-GPU box")
+def test_dense_push_pull_across_gpus_on_vmm_arenas(cuda_device):
+    """Same check with the arenas of src/device/vmm_heap.cu: descriptors exchanged over Unix
+    sockets, every rank maps every peer's physical allocation."""
+    import torch
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    nproc = 8 if n >= 8 else (4 if n >= 4 else 2)
+    r = _torchrun("mp_dense_check.py", nproc,
+                  extra_env={"PSB200_NVLS": "0", "PSB200_HEAP": "vmm"})
+    assert r.returncode == 0 and "MP_DENSE_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
