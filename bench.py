@@ -39,6 +39,8 @@ def parse_args():
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--slice-mb", type=float, default=32.0,
+                    help="slice size of the end-to-end staging pipeline (MiB)")
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--trainer", default="ps", choices=["ps", "ddp"],
                     help="model workloads: this package's server-side optimizer, or the "
@@ -76,7 +78,7 @@ def run_pushpull(args):
     n = max(8 * world, n // (8 * world) * (8 * world))
     nbytes = n * isz
     ctx = kvstore.init(heap_bytes=2 * nbytes + (64 << 20), device=dev)
-    kv = kvstore.KVStore(ctx)
+    kv = kvstore.KVStore(ctx, slice_bytes=int(args.slice_mb * (1 << 20)))
     # sum over workers + SGD lr 0.01; contiguous key ranges, one per server
     opt = ServerOptimizer("sgd", lr=0.01, scale=1.0)
     table = kv.declare(0, n, grad_dtype=gdt, out_dtype=gdt, optimizer=opt, num_ctas=args.ctas)
@@ -134,6 +136,7 @@ def run_pushpull(args):
         e2e = {"value": round(world * 2.0 * nbytes / (ms2 * 1e-3) / 1e9, 3), "unit": "GB/s",
                "ms_per_step": round(ms2, 4), "steps": k2,
                "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
+               "slice_mib": args.slice_mb,
                "api": "KVStore.push_pull(pinned host tensor, out=pinned host tensor); wait(ts)"}
     # the sampler ran through both timed regions (device-timed and end-to-end)
     clocks = sampler.stop() if rank == 0 else None
