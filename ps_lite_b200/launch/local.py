@@ -145,6 +145,9 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--role-as-arg", action="store_true",
                     help="append the role name to the command line of each process")
     ap.add_argument("--timeout", type=float, default=3600.0)
+    ap.add_argument("--repeat", type=int, default=1,
+                    help="run the job this many times, stop at the first failure (a race "
+                         "shaker, like tests/repeat.sh of the reference)")
     ap.add_argument("command", nargs=argparse.REMAINDER)
     args = ap.parse_args(argv)
     if not args.command:
@@ -152,8 +155,14 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     if not args.joint and (args.num_workers <= 0 or args.num_servers <= 0):
         ap.error("give -n and -s, or --joint")
     env = dict(kv.split("=", 1) for kv in args.env)
-    rc, _ = run(args.command, args.num_workers, args.num_servers, args.joint, env,
-                args.timeout, args.role_as_arg)
+    rc = 0
+    for i in range(max(1, args.repeat)):
+        rc, _ = run(args.command, args.num_workers, args.num_servers, args.joint, env,
+                    args.timeout, args.role_as_arg)
+        if rc != 0:
+            if args.repeat > 1:
+                print(f"run {i + 1} of {args.repeat} failed with exit code {rc}", file=sys.stderr)
+            break
     return rc
 
 

@@ -199,6 +199,22 @@ def test_keepalive_restarts_on_exit_code_254(tmp_path):
     assert "worker0" in lines and "worker1" in lines and "server1" not in lines
 
 
+def test_repeat_stops_at_the_first_failure(tmp_path):
+    """--repeat runs the job again and again (a race shaker) and stops when a run fails."""
+    from ps_lite_b200.launch import local
+    marker = tmp_path / "runs"
+    script = tmp_path / "third_time_unlucky.py"
+    script.write_text(
+        "import os, sys\n"
+        "if os.environ['DMLC_ROLE'] != 'worker':\n"
+        "    sys.exit(0)\n"
+        f"with open(r'{marker}', 'a') as f:\n"
+        "    f.write('x')\n"
+        f"sys.exit(3 if len(open(r'{marker}').read()) == 3 else 0)\n")
+    rc = local.main(["--repeat", "10", "-n", "1", "-s", "1", sys.executable, str(script)])
+    assert rc == 3 and marker.read_text() == "xxx"
+
+
 def test_p3_scheduler_order():
     from ps_lite_b200.parallel.optimizer import P3Scheduler
     s = P3Scheduler(slice_elems=16)
