@@ -8,7 +8,7 @@ for the libzmq shared library that ships inside pyzmq) and ``meta.pb.h`` (stand-
 protoc output of src/meta.proto) -- and compiles ``libps.a`` with the reference's own flags
 (Makefile:21) plus the benchmark driver ``baseline/ref_bench.cc``.
 
-    python baseline/build_ref.py [--reference /root/reference]
+    python baseline/build_ref.py [--reference <checkout of the reference>]
 """
 from __future__ import annotations
 
@@ -78,6 +78,6 @@ def build(reference: str) -> str:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("PS_REFERENCE_SRC", "/root/reference"))
     a = ap.parse_args()
     print(build(a.reference))

@@ -12,7 +12,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BIN = os.path.join(ROOT, "build", "tests")
-REF_TESTS = "/root/reference/tests"
+REF_TESTS = os.path.join(os.environ.get("PS_REFERENCE_SRC", "/root/reference"), "tests")
 
 
 @pytest.fixture(scope="session")
