@@ -98,7 +98,7 @@ def test_two_customers_in_one_worker_process(core_lib):
 def test_public_headers_compile_with_older_standards(std):
     """Programs written for the reference are built with -std=c++11 (its Makefile:21): the
     public headers must not need anything newer."""
-    for prog in ("kv_config1", "kv_features"):
+    for prog in ("kv_config1", "kv_features", "checkpoint"):
         r = subprocess.run(["g++", f"-std={std}", "-O0", "-fsyntax-only", "-I",
                             os.path.join(ROOT, "include"),
                             os.path.join(ROOT, "tests", "cpp", prog + ".cc")],
@@ -130,6 +130,15 @@ def test_key32_build(tmp_path):
     assert r.returncode == 0 and "UNIT_OK" in r.stdout, r.stderr[-3000:]
     rc, text = _job([os.path.join(out, "kv_config1")], num_workers=2, num_servers=2)
     assert rc == 0 and text.count("CONFIG1_OK") == 2, text[-3000:]
+
+
+@pytest.mark.parametrize("layout", [dict(num_workers=2, num_servers=2), dict(num_joint=2)],
+                         ids=["separate", "joint"])
+def test_checkpoint_commands(core_lib, tmp_path, layout):
+    """Servers save and reload their shard on a group request (include/ps/kv_checkpoint.h)."""
+    rc, out = _job([_prog("checkpoint", core_lib), str(tmp_path)], **layout)
+    assert rc == 0 and out.count("CHECKPOINT_OK") == 2, out[-3000:]
+    assert sorted(os.listdir(tmp_path)) == ["server-0.kv", "server-1.kv"]
 
 
 def test_shm_pool_unit(core_lib):
