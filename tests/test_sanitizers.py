@@ -18,7 +18,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.skipif(os.environ.get("PS_RUN_SANITIZERS") != "1",
                                 reason="set PS_RUN_SANITIZERS=1 to run the sanitizer builds")
 PROGRAMS = ["unit_core", "loop_kv", "shm_frames", "kv_config1", "kv_features", "multi_customer",
-            "recovery"]
+            "recovery", "checkpoint"]
 MARKS = {"thread": "WARNING: ThreadSanitizer", "address": "ERROR: AddressSanitizer",
          "undefined": "runtime error:"}
 
@@ -71,15 +71,17 @@ def test_single_process_programs(san, prog, token):
     ("kv_config1", [], {}, dict(num_joint=2), "CONFIG1_OK", 2),
     ("kv_features", [], {}, dict(num_workers=3, num_servers=2), "FEATURES_OK", 3),
     ("kv_features", [], {}, dict(num_joint=3), "FEATURES_OK", 3),
+    ("checkpoint", ["<tmp>"], {}, dict(num_workers=2, num_servers=2), "CHECKPOINT_OK", 2),
     ("shm_frames", ["job"], {"DMLC_LOCAL": "1"}, dict(num_workers=2, num_servers=2),
      "SHM_JOB_OK", 2),
     ("shm_frames", ["job"], {"DMLC_LOCAL": "1", "PS_RESEND": "1", "PS_RESEND_TIMEOUT": "300",
                              "PS_DROP_MSG": "10"}, dict(num_workers=2, num_servers=2),
      "SHM_JOB_OK", 2),
 ])
-def test_multi_process_programs(san, prog, args, env, layout, token, count):
+def test_multi_process_programs(san, prog, args, env, layout, token, count, tmp_path):
     from ps_lite_b200.launch.local import LocalJob
     kind, out = san
+    args = [str(tmp_path) if a == "<tmp>" else a for a in args]
     job = LocalJob([os.path.join(out, prog), *args], capture=True, env=env, **layout)
     job.start()
     rc = job.wait(600)
