@@ -6,6 +6,7 @@ PyTorch statement of FTRL.
 
     python benchmarks/sparse_lr.py                       # one GPU
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/sparse_lr.py
+    python benchmarks/sparse_lr.py --cpu-oracle [--workers 8]   # timed CPU baseline, no GPU needed
 """
 import argparse
 import json
@@ -35,13 +36,54 @@ def zipf_keys(n, key_space, s, gen, dev):
     return torch.sort(keys[idx]).values
 
 
+def cpu_oracle(args):
+    """The same step as plain PyTorch on the host CPUs: the requests of `workers` workers are
+    merged (sort + sum of duplicate keys, the server's view), FTRL runs on the touched
+    coordinates of direct-indexed fp32 state, and every worker reads its keys back."""
+    import time
+    dev = torch.device("cpu")
+    key_space, n, W = 1 << args.log2_key_space, 1 << args.log2_keys, args.workers
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1234)
+    batches = [[(zipf_keys(n, key_space, 1.1, gen, dev), torch.randn(n, generator=gen) * 0.1)
+                for _ in range(W)] for _ in range(2)]
+    z = torch.zeros(key_space)
+    nn_ = torch.zeros(key_space)
+    w = torch.zeros(key_space)
+
+    def step(reqs):
+        uk, inv = torch.unique(torch.cat([k for k, _ in reqs]), return_inverse=True)
+        G = torch.zeros(uk.numel()).index_add_(0, inv, torch.cat([g for _, g in reqs]))
+        zs, ns, ws = z[uk], nn_[uk], w[uk]
+        ftrl_update(zs, ns, ws, G)
+        z[uk], nn_[uk], w[uk] = zs, ns, ws
+        return [w[k] for k, _ in reqs]
+
+    for i in range(min(args.warmup, 2)):
+        step(batches[i % 2])
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for i in range(steps):
+        step(batches[i % 2])
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    print(json.dumps({"metric": "sparse_lr_keys_per_s", "impl": "cpu oracle (PyTorch, host CPUs)",
+                      "value": round(W * n / (ms * 1e-3)), "unit": "keys/s", "workers": W,
+                      "ms_per_step": round(ms, 2), "keys_per_worker_per_step": n,
+                      "key_space": key_space, "threads": torch.get_num_threads(),
+                      "handle": "FTRL-proximal"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--log2-key-space", type=int, default=30)
     ap.add_argument("--log2-keys", type=int, default=20)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--cpu-oracle", action="store_true")
+    ap.add_argument("--workers", type=int, default=1, help="workers merged by the CPU oracle")
     args = ap.parse_args()
+    if args.cpu_oracle:
+        return cpu_oracle(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
