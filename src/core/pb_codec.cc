@@ -84,7 +84,10 @@ bool DecodeControl(const char* buf, size_t len, Control* c) {
     uint64_t v;
     if (f == 1 && wt == kVarint) {
       if (!r.varint(&v)) return false;
-      c->cmd = static_cast<Control::Command>(static_cast<int32_t>(v));
+      // a command outside the enumeration makes the message undecodable, not undefined
+      const int32_t cmd = static_cast<int32_t>(v);
+      if (cmd < 0 || cmd > static_cast<int32_t>(Control::HEARTBEAT)) return false;
+      c->cmd = static_cast<Control::Command>(cmd);
     } else if (f == 2 && wt == kBytes) {
       const char* p;
       size_t n;
@@ -149,7 +152,10 @@ bool DecodeNode(const char* buf, size_t len, Node* n) {
       if (!r.varint(&v)) return false;
       const int32_t x = static_cast<int32_t>(v);
       switch (f) {
-        case 1: n->role = static_cast<Node::Role>(x); break;
+        case 1:
+          if (x < 0 || x > static_cast<int32_t>(Node::JOINT)) return false;
+          n->role = static_cast<Node::Role>(x);
+          break;
         case 2: n->id = x; break;
         case 4: n->port = x; break;
         case 5: n->is_recovery = (v != 0); break;

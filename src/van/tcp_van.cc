@@ -30,6 +30,7 @@
 #include <cstring>
 #include <deque>
 #include <map>
+#include <new>
 #include <random>
 
 #include "ps/internal/pb_codec.h"
@@ -42,6 +43,8 @@ namespace {
 
 constexpr uint32_t kMagic = 0x32425350u;  // "PSB2"
 constexpr uint32_t kMaxFrames = 64;
+constexpr uint32_t kMaxMetaBytes = 64u << 20;      // a meta block is a few hundred bytes
+constexpr uint64_t kMaxFrameBytes = 1ull << 40;    // no single array is a terabyte
 
 struct FrameHeader {
   uint32_t magic;
@@ -169,6 +172,7 @@ struct InConn {
   ShmRef shm_ref{};           // body of a shared-memory frame
   bool frame_is_shm = false;
   std::deque<int> fds;        // descriptors received and not yet claimed by a frame
+  bool bad = false;           // a frame was refused (absurd length): close the connection
 };
 
 struct OutConn {
@@ -465,9 +469,14 @@ class TcpVan : public Van {
   // Returns false on a protocol error.
   bool Advance(InConn* c) {
     for (;;) {
+      if (c->bad) return false;
       switch (c->phase) {
         case InConn::kHeader:
-          if (c->hdr.magic != kMagic || c->hdr.n_data > kMaxFrames) return false;
+          // a peer that is not one of ours (or a corrupted stream) must not make this process
+          // allocate without bound
+          if (c->hdr.magic != kMagic || c->hdr.n_data > kMaxFrames ||
+              c->hdr.meta_len > kMaxMetaBytes)
+            return false;
           c->lens.assign(c->hdr.n_data, 0);
           c->msg = Message();
           c->frame = 0;
@@ -546,7 +555,19 @@ class TcpVan : public Van {
     }
     c->frame_is_shm = false;
     const size_t len = c->lens[c->frame];
-    c->frame_buf = recv_pool_->Get(len, &c->frame_cap);
+    c->frame_buf = nullptr;
+    if (len <= kMaxFrameBytes) {
+      try {
+        c->frame_buf = recv_pool_->Get(len, &c->frame_cap);
+      } catch (const std::bad_alloc&) {
+      }
+    }
+    if (!c->frame_buf) {
+      // refuse the stream: Advance returns a protocol error on its next turn
+      c->bad = true;
+      Arm(c, InConn::kData, reinterpret_cast<char*>(&c->shm_ref), 0);
+      return true;
+    }
     Arm(c, InConn::kData, c->frame_buf, len);
     return true;
   }

@@ -141,6 +141,50 @@ def test_checkpoint_commands(core_lib, tmp_path, layout):
     assert sorted(os.listdir(tmp_path)) == ["server-0.kv", "server-1.kv"]
 
 
+def test_garbage_on_the_wire_does_not_hurt_a_node(core_lib):
+    """Strangers talk to the scheduler's port while a job starts: random bytes, a frame header
+    with an absurd meta length, a data frame of 2^62 bytes.  The connections are dropped, the
+    node neither crashes nor allocates what it was told to, and the job completes."""
+    import socket
+    import struct
+    import threading
+    import time
+    from ps_lite_b200.launch.local import LocalJob
+    job = LocalJob([_prog("kv_config1", core_lib)], num_workers=2, num_servers=2, capture=True)
+    job._spawn("scheduler", 0)
+    magic = 0x32425350
+
+    def stranger(payload):
+        deadline = time.time() + 20
+        while time.time() < deadline:
+            try:
+                with socket.create_connection(("127.0.0.1", job.port), timeout=2) as s:
+                    s.sendall(payload)
+                    time.sleep(0.2)
+                return
+            except OSError:
+                time.sleep(0.05)
+
+    payloads = [
+        os.urandom(4096),
+        struct.pack("<IiiII", magic, 9, 1, 0xFFFFFFF0, 0),                       # meta of 4 GB
+        struct.pack("<IiiII", magic, 9, 1, 4, 1) + struct.pack("<Q", 1 << 62) + b"abcd",
+        struct.pack("<IiiII", magic, 9, 1, 4, 65),                               # too many frames
+    ]
+    threads = [threading.Thread(target=stranger, args=(p,)) for p in payloads]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for i in range(2):
+        job._spawn("server", i)
+    for i in range(2):
+        job._spawn("worker", i)
+    rc = job.wait(90)
+    out = job.output()
+    assert rc == 0 and out.count("CONFIG1_OK") == 2, out[-3000:]
+
+
 def test_shm_pool_unit(core_lib):
     """Shared-memory array pool: recycling, views that outlive their array, own segments echoed."""
     r = subprocess.run([_prog("shm_frames", core_lib)], capture_output=True, text=True, timeout=60)
