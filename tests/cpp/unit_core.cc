@@ -262,6 +262,53 @@ static void TestCodec() {
   }
 }
 
+// Mutated encodings (flipped, inserted, removed bytes, truncations) must either decode into
+// something that can be printed and encoded again, or be refused; never anything undefined.
+static void TestCodecFuzz() {
+  std::mt19937_64 rng(42);
+  Meta m;
+  m.head = 7; m.app_id = 1; m.customer_id = 2; m.timestamp = 99; m.request = true; m.push = true;
+  m.body = "hello world";
+  m.data_type = {UINT64, FLOAT, INT32};
+  m.priority = 5;
+  m.data_size = 123;
+  m.control.cmd = Control::ADD_NODE;
+  m.control.barrier_group = 7;
+  m.control.msg_sig = 0x1234567890ull;
+  for (int i = 0; i < 3; ++i) {
+    Node n;
+    n.role = Node::WORKER; n.id = 9 + 2 * i; n.hostname = "10.0.0.1"; n.port = 1000 + i;
+    n.customer_id = i;
+    m.control.node.push_back(n);
+  }
+  std::string good;
+  pb::EncodeMeta(m, &good);
+  size_t accepted = 0;
+  for (int it = 0; it < 200000; ++it) {
+    std::string s = good;
+    const int edits = 1 + static_cast<int>(rng() % 4);
+    for (int k = 0; k < edits; ++k) {
+      switch (rng() % 4) {
+        case 0: s[rng() % s.size()] = static_cast<char>(rng()); break;
+        case 1: s.resize(rng() % (s.size() + 1)); break;
+        case 2: s.insert(rng() % s.size(), 1, static_cast<char>(rng())); break;
+        default: s.erase(rng() % s.size(), 1); break;
+      }
+      if (s.empty()) s = "x";
+    }
+    Meta out;
+    if (pb::DecodeMeta(s.data(), s.size(), &out)) {
+      ++accepted;
+      std::string again;
+      pb::EncodeMeta(out, &again);
+      Message msg;
+      msg.meta = out;
+      CHECK(!msg.DebugString().empty());
+    }
+  }
+  CHECK_GT(accepted, (size_t)0);
+}
+
 static void TestMisc() {
   CHECK_EQ(Postoffice::WorkerRankToID(3), 15);
   CHECK_EQ(Postoffice::ServerRankToID(3), 14);
@@ -325,6 +372,7 @@ int main() {
   TestEnv();
   TestQueues();
   TestCodec();
+  TestCodecFuzz();
   TestMisc();
   printf("UNIT_OK\n");
   return 0;
