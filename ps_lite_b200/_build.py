@@ -48,9 +48,11 @@ def _sources(*dirs: str, exts=(".cu", ".cc")) -> list[Path]:
     return out
 
 
-def _headers_stamp() -> str:
+def _headers_stamp(dirs=("include", "src")) -> str:
+    """Hash of every header under `dirs`: part of each object's name, so that a changed header
+    recompiles what may include it."""
     h = hashlib.sha1()
-    for d in ("include", "src"):
+    for d in dirs:
         for f in sorted((ROOT / d).rglob("*")):
             if f.suffix in (".h", ".cuh", ".hpp", ".inl"):
                 h.update(str(f.relative_to(ROOT)).encode())
@@ -126,7 +128,9 @@ def build_device(verbose: bool = False, checks: bool = False) -> Path:
 
 def _build_device(verbose: bool, checks: bool = False) -> Path:
     srcs = _sources("src/kernels", "src/device", exts=(".cu",))
-    stamp = _headers_stamp()
+    # device sources include nothing outside these directories: a change to a host-only
+    # header does not rebuild the kernels
+    stamp = _headers_stamp(("include/ps/device", "src/kernels", "src/device"))
     extra = ("-DPSDEV_CHECKS=1",) if checks else ()
     obj_dir = ROOT / "build" / "obj_checks" if checks else OBJ_DIR
     with ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as ex:
