@@ -9,6 +9,7 @@
 // WaitRequest reports it instead of blocking forever.
 #ifndef PS_INTERNAL_CUSTOMER_H_
 #define PS_INTERNAL_CUSTOMER_H_
+#include <deque>
 #include <chrono>
 #include <atomic>
 #include <condition_variable>
@@ -77,8 +78,13 @@ class Customer {
 
   std::mutex tracker_mu_;
   std::condition_variable tracker_cond_;
-  // tracker_[ts] = (responses expected, responses received)
-  std::vector<std::pair<int, int>> tracker_;
+  // tracker_[ts - tracker_base_] = (responses expected, responses received).  Requests below
+  // tracker_base_ have completed and been forgotten: the table keeps a window of recent
+  // requests instead of growing for the life of the process (the reference's never shrinks,
+  // src/customer.cc:25-47); timestamps keep counting up.
+  std::deque<std::pair<int, int>> tracker_;
+  int tracker_base_ = 0;
+  static constexpr size_t kTrackerWindow = 4096;
   DISALLOW_COPY_AND_ASSIGN(Customer);
 };
 

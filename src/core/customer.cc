@@ -1,6 +1,7 @@
 #include "ps/internal/customer.h"
 
 #include <chrono>
+#include <climits>
 
 #include "ps/internal/postoffice.h"
 
@@ -36,7 +37,7 @@ int Customer::NewRequest(int recver) {
   const int expected = static_cast<int>(Postoffice::Get()->GetNodeIDs(recver).size());
   std::lock_guard<std::mutex> lk(tracker_mu_);
   tracker_.emplace_back(expected, 0);
-  return static_cast<int>(tracker_.size()) - 1;
+  return tracker_base_ + static_cast<int>(tracker_.size()) - 1;
 }
 
 void Customer::WaitRequest(int timestamp) { WaitRequestFor(timestamp, -1); }
@@ -44,9 +45,11 @@ void Customer::WaitRequest(int timestamp) { WaitRequestFor(timestamp, -1); }
 bool Customer::WaitRequestFor(int timestamp, int timeout_ms) {
   std::unique_lock<std::mutex> lk(tracker_mu_);
   CHECK_GE(timestamp, 0);
-  CHECK_LT(static_cast<size_t>(timestamp), tracker_.size()) << "unknown timestamp";
+  CHECK_LT(static_cast<size_t>(timestamp), tracker_base_ + tracker_.size()) << "unknown timestamp";
   auto done = [this, timestamp] {
-    return tracker_[timestamp].first <= tracker_[timestamp].second;
+    if (timestamp < tracker_base_) return true;  // completed long ago
+    const auto& e = tracker_[timestamp - tracker_base_];
+    return e.first <= e.second;
   };
   if (timeout_ms < 0) {
     tracker_cond_.wait(lk, done);
@@ -57,13 +60,19 @@ bool Customer::WaitRequestFor(int timestamp, int timeout_ms) {
 
 int Customer::NumResponse(int timestamp) {
   std::lock_guard<std::mutex> lk(tracker_mu_);
-  return tracker_[timestamp].second;
+  if (timestamp < tracker_base_) return INT_MAX;  // forgotten: complete, and more than anyone expects
+  return tracker_[timestamp - tracker_base_].second;
 }
 
 void Customer::AddResponse(int timestamp, int num) {
   {
     std::lock_guard<std::mutex> lk(tracker_mu_);
-    tracker_[timestamp].second += num;
+    if (timestamp >= tracker_base_) tracker_[timestamp - tracker_base_].second += num;
+    // forget completed requests beyond the window of recent ones
+    while (tracker_.size() > kTrackerWindow && tracker_.front().first <= tracker_.front().second) {
+      tracker_.pop_front();
+      ++tracker_base_;
+    }
   }
   tracker_cond_.notify_all();
 }

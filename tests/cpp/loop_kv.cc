@@ -27,6 +27,15 @@ int main() {
       std::vector<float> outs;
       kv.Wait(kv.PushPull(keys, vals, &outs));
       for (int i = 0; i < 8; ++i) CHECK_LT(std::fabs(outs[i] - 6 * vals[i]), 1e-6f);
+      // many requests: the tracker forgets completed ones beyond a window, timestamps keep
+      // counting, and waiting for a forgotten request returns at once
+      std::vector<int> stamps;
+      for (int i = 0; i < 10000; ++i) stamps.push_back(kv.Push(keys, vals));
+      CHECK_EQ(stamps.back() - stamps.front(), 9999);
+      kv.Wait(stamps.back());
+      for (int ts : {stamps[0], stamps[5000], stamps[9999]}) kv.Wait(ts);
+      kv.Wait(kv.Pull(keys, &got));
+      for (int i = 0; i < 8; ++i) CHECK_LT(std::fabs(got[i] - 10006 * vals[i]), 1e-3f * 10006);
       const auto& ranges = Postoffice::Get()->GetServerKeyRanges();
       CHECK_EQ(ranges.size(), (size_t)1);
       CHECK_EQ(ranges[0].begin(), (uint64_t)0);
