@@ -60,7 +60,8 @@ bool Customer::WaitRequestFor(int timestamp, int timeout_ms) {
 
 int Customer::NumResponse(int timestamp) {
   std::lock_guard<std::mutex> lk(tracker_mu_);
-  if (timestamp < tracker_base_) return INT_MAX;  // forgotten: complete, and more than anyone expects
+  // forgotten: complete, and more than anyone expects
+  if (timestamp < tracker_base_) return INT_MAX;
   return tracker_[timestamp - tracker_base_].second;
 }
 
