@@ -61,6 +61,7 @@ def lib() -> C.CDLL:
             L.ps_capi_dead_nodes.argtypes = [i, ip, i]
             L.ps_capi_server_key_range.argtypes = [i, u64p, u64p]
             L.ps_capi_traffic.argtypes = [u64p, u64p]
+            L.ps_capi_shm_stats.argtypes = [C.POINTER(C.c_uint64 * 6)]
             L.ps_capi_worker_new.restype = vp
             L.ps_capi_worker_new.argtypes = [i, i]
             L.ps_capi_worker_delete.argtypes = [vp]
@@ -135,6 +136,15 @@ def traffic() -> tuple[int, int]:
     s, r = C.c_uint64(), C.c_uint64()
     _ck(lib().ps_capi_traffic(C.byref(s), C.byref(r)))
     return s.value, r.value
+
+
+def shm_stats() -> dict:
+    """Counters of the shared-memory array pool (large arrays between processes of one host)."""
+    out = (C.c_uint64 * 6)()
+    _ck(lib().ps_capi_shm_stats(C.byref(out)))
+    names = ("segments_created", "segments_reused", "bytes_live", "bytes_pooled",
+             "segments_received", "segments_received_already_mapped")
+    return dict(zip(names, (int(v) for v in out)))
 
 
 def _u64(a): return np.ascontiguousarray(a, dtype=np.uint64)

@@ -21,4 +21,5 @@ def snapshot(heap=None, host: bool = False) -> dict:
         from .. import host as h
         sent, recv = h.traffic()
         out["van_bytes_sent"], out["van_bytes_received"] = sent, recv
+        out["shared_memory_arrays"] = h.shm_stats()
     return out

@@ -1,3 +1,4 @@
+#include "ps/internal/shm_pool.h"
 #include "capi/ps_c_api.h"
 
 #include <cstring>
@@ -93,6 +94,17 @@ int ps_capi_traffic(uint64_t* sent, uint64_t* received) {
     *received = v->recv_bytes();
     return 0;
   });
+}
+
+int ps_capi_shm_stats(uint64_t out[6]) {
+  const shm::Stats s = shm::GetStats();
+  out[0] = s.segments_created;
+  out[1] = s.segments_reused;
+  out[2] = s.bytes_live;
+  out[3] = s.bytes_pooled;
+  out[4] = s.imports;
+  out[5] = s.import_hits;
+  return 0;
 }
 
 // ---- worker ----

@@ -38,6 +38,10 @@ int ps_capi_dead_nodes(int timeout_s, int* ids, int cap);
 int ps_capi_server_key_range(int rank, uint64_t* begin, uint64_t* end);
 /* Bytes sent / received by the van so far. */
 int ps_capi_traffic(uint64_t* sent, uint64_t* received);
+/* Counters of the shared-memory array pool (ps/internal/shm_pool.h), in this order: segments
+ * created, segments recycled, bytes backing live arrays, bytes idle in the pool, segments
+ * received from peers, of which already mapped.  Works before Start. */
+int ps_capi_shm_stats(uint64_t out[6]);
 
 /* ---- KVWorker<float> ---- */
 void* ps_capi_worker_new(int app_id, int customer_id);
