@@ -94,8 +94,16 @@ def _link(objs: list[Path], out: Path, cuda: bool, extra: list[str]) -> None:
         cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a",
                "-o", str(out), *map(str, objs), "-lcudart", *extra]
     else:
-        cmd = [CXX, "-shared", "-pthread", "-o", str(out), *map(str, objs), *extra]
+        # Always the shared libstdc++: some toolchains link the static one by default, and a
+        # second copy of the C++ runtime inside this library clashes with the one that the
+        # programs linking it, and torch in the same Python process, already use.
+        cmd = [CXX, "-shared", "-pthread", "-nostdlib++", "-o", str(out), *map(str, objs),
+               "-l:libstdc++.so.6", "-lm", *extra]
     r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0 and not cuda:
+        # a compiler without -nostdlib++ or a system without that soname: default link
+        cmd = [CXX, "-shared", "-pthread", "-o", str(out), *map(str, objs), *extra]
+        r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
     manifest.write_text(want)

@@ -53,7 +53,7 @@ def lib() -> C.CDLL:
         if _lib is None:
             from . import _build
             path = _build.build_core()
-            L = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
+            L = C.CDLL(str(path))   # local scope: nothing else resolves against this library
             vp, i, sz = C.c_void_p, C.c_int, C.c_size_t
             u64p, fp, ip = C.POINTER(C.c_uint64), C.POINTER(C.c_float), C.POINTER(C.c_int)
             L.ps_capi_last_error.restype = C.c_char_p

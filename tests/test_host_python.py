@@ -215,6 +215,20 @@ def test_repeat_stops_at_the_first_failure(tmp_path):
     assert rc == 3 and marker.read_text() == "xxx"
 
 
+def test_core_library_then_torch_in_one_process():
+    """The host runtime library must not bring a second C++ runtime into the process: loading
+    it first and importing torch afterwards used to crash where the compiler links libstdc++
+    statically by default."""
+    import subprocess
+    code = ("from ps_lite_b200 import host\n"
+            "host.lib(); host.shm_stats()\n"
+            "import torch\n"
+            "print('LOADED', torch.__version__)\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
+                       cwd=ROOT)
+    assert r.returncode == 0 and "LOADED" in r.stdout, (r.stdout + r.stderr)[-2000:]
+
+
 def test_p3_scheduler_order():
     from ps_lite_b200.parallel.optimizer import P3Scheduler
     s = P3Scheduler(slice_elems=16)
