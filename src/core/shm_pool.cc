@@ -59,11 +59,11 @@ size_t EnvSize(const char* name, size_t dflt) {
 }
 
 size_t PoolCap() {
-  static const size_t v = EnvSize("PS_SHM_POOL_MB", 1024) << 20;
+  static const size_t v = EnvSize("PS_SHM_POOL_MB", 512) << 20;
   return v;
 }
 size_t ImportCap() {
-  static const size_t v = EnvSize("PS_SHM_IMPORT_CACHE_MB", 1024) << 20;
+  static const size_t v = EnvSize("PS_SHM_IMPORT_CACHE_MB", 512) << 20;
   return v;
 }
 
