@@ -78,6 +78,8 @@ def build(reference: str) -> str:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("PS_REFERENCE_SRC", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("PS_REFERENCE_SRC"), required=not
+                    os.environ.get("PS_REFERENCE_SRC"),
+                    help="directory of the unmodified reference sources (or PS_REFERENCE_SRC)")
     a = ap.parse_args()
     print(build(a.reference))

@@ -34,8 +34,11 @@ def main(args) -> None:
     if not os.path.exists(EXE):
         try:
             sys.path.insert(0, ROOT)
-            from baseline import build_ref
-            build_ref.build(os.environ.get("PS_REFERENCE_SRC", "/root/reference"))
+            from baseline import build_ref, reference_source
+            src = reference_source()
+            if src is None:
+                raise FileNotFoundError("set PS_REFERENCE_SRC to the reference sources")
+            build_ref.build(src)
         except Exception as exc:
             _unavailable(f"reference build not present and cannot be built here: {exc}")
             return

@@ -72,8 +72,10 @@ def build_kv_app_benchmark():
     ref_root = os.path.join(ROOT, "baseline", "_ref")
     src = os.path.join(ref_root, "ps-lite", "tests", "test_kv_app_benchmark.cc")
     if not os.path.exists(src):
-        src = os.path.join(os.environ.get("PS_REFERENCE_SRC", "/root/reference"), "tests",
-                           "test_kv_app_benchmark.cc")
+        from baseline import reference_source
+        if reference_source() is None:
+            raise FileNotFoundError("set PS_REFERENCE_SRC to the reference sources")
+        src = os.path.join(reference_source(), "tests", "test_kv_app_benchmark.cc")
     libs = _build.build_all()
     libdir = os.path.dirname(libs["core"])
     out_dir = os.path.join(ROOT, "build", "hostbench")

@@ -6,21 +6,13 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "ps/device/ctrl_layout.h"
 #include "ps/device/psdev.h"
 
 namespace psdev {
 
-// Control region: first PSDEV_CTRL_BYTES of every heap.  flag_in[c][p] / flag_out[c][p]
-// are written by rank p (remotely) and read by the owner of the heap (locally).
-struct Ctrl {
-  unsigned long long flag_in[PSDEV_NUM_CHANNELS][PSDEV_MAX_RANKS];
-  unsigned long long flag_out[PSDEV_NUM_CHANNELS][PSDEV_MAX_RANKS];
-  unsigned long long epoch[PSDEV_NUM_CHANNELS];
-  unsigned int done[PSDEV_NUM_CHANNELS];
-  int status[PSDEV_NUM_CHANNELS];
-  // who was late when a wait ran out: bit p set = rank p
-  unsigned int late_mask[PSDEV_NUM_CHANNELS];
-};
+// Control region: first PSDEV_CTRL_BYTES of every heap (layout in ctrl_layout.h).
+using Ctrl = psdev_ctrl_t;
 static_assert(sizeof(Ctrl) <= PSDEV_CTRL_BYTES, "control region too small");
 
 __device__ __forceinline__ Ctrl* ctrl_of(void* base) { return reinterpret_cast<Ctrl*>(base); }

@@ -124,11 +124,31 @@ int psdev_enable_peer(int peer_device);
  * device; *mapped_bytes is the rounded size that peers pass to psdev_vmm_import, *fd belongs
  * to the caller (send it to the peers over a Unix socket, then close it); the control region
  * is cleared.  psdev_vmm_import maps a peer's arena from its descriptor (which stays the
- * caller's).  psdev_vmm_release unmaps either kind.  No NVSwitch multicast binding is made. */
+ * caller's).  psdev_vmm_release unmaps either kind. */
 int psdev_vmm_supported(void);
 int psdev_vmm_create(size_t bytes, void** base, int* fd, size_t* mapped_bytes);
+int psdev_vmm_create_aligned(size_t bytes, size_t align, void** base, int* fd,
+                             size_t* mapped_bytes);
 int psdev_vmm_import(int fd, size_t mapped_bytes, void** base);
 int psdev_vmm_release(void* base);
+
+/* NVSwitch multicast object over the arenas of all ranks (NVLS): loads through the alias can
+ * reduce over, and stores replicate into, every rank's arena (multimem.* instructions).  The
+ * ranks go through these steps together, with a host barrier between them:
+ *   rank 0: psdev_mc_create (exports a descriptor), others: psdev_mc_import;
+ *   all: psdev_mc_add_device; barrier; all: psdev_mc_bind(arena); barrier;
+ *   all: psdev_mc_map -> alias for psdev_world_t.mc_base.
+ * Arenas must come from psdev_vmm_create_aligned with align = psdev_mc_granularity and have
+ * the object's size.  psdev_mc_release (after a barrier that follows the last kernel using
+ * the alias) unmaps, unbinds and drops the object. */
+int psdev_mc_supported(void);
+int psdev_mc_granularity(int num_devices, size_t bytes, size_t* gran);
+int psdev_mc_create(size_t bytes, int num_devices, int* fd, void** mc);
+int psdev_mc_import(int fd, size_t bytes, void** mc);
+int psdev_mc_add_device(void* mc);
+int psdev_mc_bind(void* mc, void* arena_base);
+int psdev_mc_map(void* mc, void** mc_base);
+int psdev_mc_release(void* mc);
 
 /* first-fit sub-allocator over [PSDEV_CTRL_BYTES, bytes): pure host bookkeeping,
  * deterministic, so every rank that issues the same calls gets the same offsets */
@@ -141,6 +161,9 @@ size_t psdev_suballoc_in_use(void* sa);
 /* ---- channel state ------------------------------------------------------- */
 /* Reads (synchronously) the status word and epoch of a channel of the local heap. */
 int psdev_channel_status(void* local_base, int channel, int32_t* status, uint64_t* epoch);
+/* Same, with the copies issued on `stream` (then synchronised) instead of the default stream. */
+int psdev_channel_status_on(void* local_base, int channel, void* stream, int32_t* status,
+                            uint64_t* epoch);
 /* Clears status (not the epoch) of a channel after an error was handled. */
 int psdev_channel_clear(void* local_base, int channel);
 
@@ -213,8 +236,30 @@ int64_t psdev_pull_plan_chunk(int64_t w_elem_off, int64_t nk, int blk, int world
 /* Reads and clears the error word of the GEMM kernels on the current device (synchronous). */
 int psdev_gemm_status(int32_t* status);
 
-/* Peer bandwidth probe: copies `bytes` from `src` to `dst` with 16 B accesses. */
-int psdev_copy_probe(void* dst, const void* src, size_t bytes, int num_ctas, void* stream);
+/* Copy kernel of the link-bandwidth benchmark (benchmarks/link_bandwidth.py): `bytes` from
+ * `src` to `dst` with 16-byte loads and stores; either side may be a peer's arena. */
+int psdev_link_copy(void* dst, const void* src, size_t bytes, int num_ctas, void* stream);
+
+/* CUDA-runtime shims for the host runtime's device plane (src/device/runtime.cu). */
+int psdev_rt_device_count(int* n);
+int psdev_rt_set_device(int device);
+int psdev_rt_get_device(int* device);
+int psdev_rt_malloc(void** p, size_t bytes); /* zero-filled */
+int psdev_rt_free(void* p);
+int psdev_rt_memset_async(void* p, int value, size_t bytes, void* stream);
+int psdev_rt_stream_create(void** stream, int priority);
+int psdev_rt_stream_destroy(void* stream);
+int psdev_rt_stream_sync(void* stream);
+int psdev_rt_event_create(void** event);
+int psdev_rt_event_destroy(void* event);
+int psdev_rt_event_record(void* event, void* stream);
+int psdev_rt_event_sync(void* event);
+int psdev_rt_stream_wait_event(void* stream, void* event);
+int psdev_rt_memcpy_async(void* dst, const void* src, size_t bytes, void* stream);
+int psdev_rt_is_device_pointer(const void* p);
+int psdev_rt_is_pinned_host(const void* p);
+int psdev_rt_host_alloc(void** p, size_t bytes);
+int psdev_rt_host_free(void* p);
 
 #ifdef __cplusplus
 }

@@ -11,6 +11,21 @@ namespace ps {
 
 enum AssignOp { ASSIGN, PLUS, MINUS, TIMES, DIVIDE, AND, OR, XOR };
 
+namespace detail {
+// Bitwise operators exist for integral types only; the choice is made by overload on a tag so
+// that the header needs nothing newer than C++11.
+template <typename T>
+inline void BitwiseAssign(const T& src, AssignOp op, T* dst, std::true_type) {
+  if (op == AND) *dst &= src;
+  else if (op == OR) *dst |= src;
+  else *dst ^= src;
+}
+template <typename T>
+inline void BitwiseAssign(const T&, AssignOp, T*, std::false_type) {
+  LOG(FATAL) << "bitwise assignment on a non-integral type";
+}
+}  // namespace detail
+
 // Applies `op` to one element.  Bitwise operators are defined for integral types only.
 template <typename T>
 inline void AssignFunc(const T& src, AssignOp op, T* dst) {
@@ -23,13 +38,7 @@ inline void AssignFunc(const T& src, AssignOp op, T* dst) {
     case AND:
     case OR:
     case XOR:
-      if constexpr (std::is_integral<T>::value) {
-        if (op == AND) *dst &= src;
-        else if (op == OR) *dst |= src;
-        else *dst ^= src;
-      } else {
-        LOG(FATAL) << "bitwise assignment on a non-integral type";
-      }
+      detail::BitwiseAssign(src, op, dst, typename std::is_integral<T>::type());
       break;
   }
 }

@@ -14,7 +14,9 @@
 #include <atomic>
 #include <condition_variable>
 #include <functional>
+#include <map>
 #include <memory>
+#include <string>
 #include <mutex>
 #include <thread>
 #include <utility>
@@ -56,6 +58,10 @@ class Customer {
   // Credits `num` responses (used for recipients that were skipped, and by the handler
   // thread after each response message).
   void AddResponse(int timestamp, int num = 1);
+  // Marks request `timestamp` as failed with `why` and completes it: WaitRequest throws
+  // ps::Error for it instead of returning.  Used by the device plane when a kernel gave up
+  // waiting for a peer; message traffic never fails a request this way.
+  void FailRequest(int timestamp, const std::string& why);
   // Hands a received message to this customer (called by the van's receive thread).
   void Accept(const Message& recved) { recv_queue_.Push(recved); }
   // False during the first milliseconds of a customer's life (PS_HANDLE_GRACE_MS, default 20).
@@ -83,6 +89,7 @@ class Customer {
   // requests instead of growing for the life of the process (the reference's never shrinks,
   // src/customer.cc:25-47); timestamps keep counting up.
   std::deque<std::pair<int, int>> tracker_;
+  std::map<int, std::string> failed_;  // timestamp -> reason, erased when waited for
   int tracker_base_ = 0;
   static constexpr size_t kTrackerWindow = 4096;
   DISALLOW_COPY_AND_ASSIGN(Customer);

@@ -61,12 +61,16 @@ inline std::string* CheckFailText(const A& a, const B& b, const char* expr) {
   return new std::string(os.str());
 }
 
-// Holder that is "true" when the check failed (so the macro can use if/else).
+// Holder that is "true" when the check passed (so the macro can use if/else with a
+// declaration as the condition, which C++11 has).
 struct CheckResult {
   std::string* text;
   explicit CheckResult(std::string* t) : text(t) {}
+  CheckResult(CheckResult&& o) : text(o.text) { o.text = nullptr; }
+  CheckResult(const CheckResult&) = delete;
+  CheckResult& operator=(const CheckResult&) = delete;
   ~CheckResult() { delete text; }
-  explicit operator bool() const { return text != nullptr; }
+  explicit operator bool() const { return text == nullptr; }
 };
 
 #define PS_DEFINE_CHECK_OP(name, op)                                            \
@@ -107,8 +111,8 @@ using Error = ::ps::Error;
   } else      \
     PS_LOG_FATAL.stream() << "Check failed: " #x << ' '
 #define PS_CHECK_OP(name, op, a, b)                                                   \
-  if (::ps::log::CheckResult _ps_cr = ::ps::log::Check##name((a), (b), #a " " #op " " #b); \
-      !_ps_cr) {                                                                      \
+  if (::ps::log::CheckResult _ps_cr =                                                 \
+          ::ps::log::Check##name((a), (b), #a " " #op " " #b)) {                      \
   } else                                                                              \
     PS_LOG_FATAL.stream() << *_ps_cr.text
 #define CHECK_EQ(a, b) PS_CHECK_OP(EQ, ==, a, b)

@@ -8,6 +8,7 @@
 #ifndef PS_INTERNAL_POSTOFFICE_H_
 #define PS_INTERNAL_POSTOFFICE_H_
 #include <algorithm>
+#include <atomic>
 #include <condition_variable>
 #include <functional>
 #include <map>
@@ -17,6 +18,7 @@
 #include <vector>
 
 #include "ps/internal/customer.h"
+#include "ps/internal/device_route.h"
 #include "ps/internal/env.h"
 #include "ps/internal/van.h"
 #include "ps/range.h"
@@ -76,6 +78,13 @@ class Postoffice {
   int verbose() const { return verbose_; }
   bool is_recovery() const { return van_->my_node().is_recovery; }
 
+  // The device plane, when one is attached (see ps/internal/device_route.h); KVWorker asks
+  // it first whether it serves the keys of a request.
+  DeviceRoute* device_route() const { return device_route_.load(std::memory_order_acquire); }
+  void set_device_route(DeviceRoute* route) {
+    device_route_.store(route, std::memory_order_release);
+  }
+
   // Blocks until every node of `node_group` (which must include this node) entered.
   void Barrier(int customer_id, int node_group);
   // Called by the van for control responses that concern the Postoffice (barrier release).
@@ -93,8 +102,10 @@ class Postoffice {
   Postoffice();
   ~Postoffice() { delete van_; }
   void InitEnvironment();
+  void BarrierImpl(int customer_id, int node_group, bool process_wide);
 
   Van* van_ = nullptr;
+  std::atomic<DeviceRoute*> device_route_{nullptr};
   mutable std::mutex mu_;
   // Held by the van while it looks a customer up and hands it a message, and by
   // RemoveCustomer: once a customer has been removed, no delivery to it is under way.
@@ -112,8 +123,11 @@ class Postoffice {
   // released by the scheduler.
   struct Round {
     bool in_flight = false;
+    bool process_wide = false;  // opened by Start/Finalize on behalf of every customer
     int pending = 0;
-    uint64_t generation = 0;
+    uint64_t generation = 0;    // rounds released so far
+    uint64_t floor = 0;         // rounds that count as passed by every customer
+    std::unordered_map<int, uint64_t> passed;  // customer id -> rounds it has passed
   };
   std::unordered_map<int, Round> rounds_;
   int started_customers_ = 0;

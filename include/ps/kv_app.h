@@ -70,6 +70,14 @@ class KVWorker : public SimpleApp {
            std::vector<int>* lens = nullptr, int cmd = 0, const Callback& cb = nullptr,
            int priority = 0) {
     SArray<Key> skeys(keys);
+    if (DeviceRoute* route = DeviceRouteFor(skeys)) {
+      CHECK_NOTNULL(vals);
+      if (vals->empty()) vals->resize(route->PullBytes(obj_->app_id(), skeys) / sizeof(Val));
+      if (lens && lens->empty()) lens->resize(keys.size());
+      return SubmitToDevice(route, false, true, cmd, skeys, nullptr, 0, vals->data(),
+                            vals->size() * sizeof(Val), SArray<int>(),
+                            lens ? lens->data() : nullptr, lens ? lens->size() : 0, cb, priority);
+    }
     const int ts = AddPullCB(skeys, vals, lens, cmd, cb);
     KVPairs<Val> kvs;
     kvs.keys = skeys;
@@ -109,6 +117,12 @@ class KVWorker : public SimpleApp {
   // contents unchanged until the request has completed.
   int ZPush(const SArray<Key>& keys, const SArray<Val>& vals, const SArray<int>& lens = {},
             int cmd = 0, const Callback& cb = nullptr, int priority = 0) {
+    if (DeviceRoute* route = DeviceRouteFor(keys)) {
+      // the arrays are captured by the completion routine: they stay alive until then
+      return SubmitToDevice(route, true, false, cmd, keys, vals.data(),
+                            vals.size() * sizeof(Val), nullptr, 0, lens, nullptr, 0,
+                            [keys, vals, lens, cb]() { if (cb) cb(); }, priority);
+    }
     const int ts = obj_->NewRequest(kServerGroup);
     AddCallback(ts, cb);
     KVPairs<Val> kvs;
@@ -122,6 +136,15 @@ class KVWorker : public SimpleApp {
 
   int ZPull(const SArray<Key>& keys, SArray<Val>* vals, SArray<int>* lens = nullptr,
             int cmd = 0, const Callback& cb = nullptr, int priority = 0) {
+    if (DeviceRoute* route = DeviceRouteFor(keys)) {
+      CHECK_NOTNULL(vals);
+      if (vals->empty()) vals->resize(route->PullBytes(obj_->app_id(), keys) / sizeof(Val));
+      if (lens && lens->empty()) lens->resize(keys.size());
+      return SubmitToDevice(route, false, true, cmd, keys, nullptr, 0, vals->data(),
+                            vals->size() * sizeof(Val), SArray<int>(),
+                            lens ? lens->data() : nullptr, lens ? lens->size() : 0,
+                            [keys, cb]() { if (cb) cb(); }, priority);
+    }
     const int ts = AddPullCB(keys, vals, lens, cmd, cb);
     KVPairs<Val> kvs;
     kvs.keys = keys;
@@ -133,6 +156,14 @@ class KVWorker : public SimpleApp {
   int ZPushPull(const SArray<Key>& keys, const SArray<Val>& vals, SArray<Val>* outs,
                 SArray<int>* lens = nullptr, int cmd = 0, const Callback& cb = nullptr,
                 int priority = 0) {
+    if (DeviceRoute* route = DeviceRouteFor(keys)) {
+      CHECK_NOTNULL(outs);
+      if (outs->empty()) outs->resize(vals.size());
+      return SubmitToDevice(route, true, true, cmd, keys, vals.data(),
+                            vals.size() * sizeof(Val), outs->data(), outs->size() * sizeof(Val),
+                            lens ? *lens : SArray<int>(), nullptr, 0,
+                            [keys, vals, cb]() { if (cb) cb(); }, priority);
+    }
     const int ts = AddPullCB(keys, outs, lens, cmd, cb);
     KVPairs<Val> kvs;
     kvs.keys = keys;
@@ -154,6 +185,44 @@ class KVWorker : public SimpleApp {
   }
 
  private:
+  // The device plane, if it is attached and serves `keys` (a tensor registered for this app).
+  DeviceRoute* DeviceRouteFor(const SArray<Key>& keys) {
+    DeviceRoute* route = Postoffice::Get()->device_route();
+    if (route && keys.size() && route->Claims(obj_->app_id(), keys)) return route;
+    return nullptr;
+  }
+
+  // Hands a request to the device plane.  The tracker entry is the usual one (one response
+  // expected per server); the plane credits all of them when its kernels have completed,
+  // after the callback has run, so Wait(ts) has the reference's meaning.
+  int SubmitToDevice(DeviceRoute* route, bool push, bool pull, int cmd, const SArray<Key>& keys,
+                     const void* vals, size_t vals_bytes, void* outs, size_t outs_bytes,
+                     const SArray<int>& lens, int* lens_out, size_t lens_out_n,
+                     const Callback& cb, int priority) {
+    const int ts = obj_->NewRequest(kServerGroup);
+    DeviceRequest req;
+    req.app_id = obj_->app_id();
+    req.timestamp = ts;
+    req.push = push;
+    req.pull = pull;
+    req.cmd = cmd;
+    req.priority = priority;
+    req.keys = keys;
+    req.lens = lens;
+    req.vals = vals;
+    req.vals_bytes = vals_bytes;
+    req.outs = outs;
+    req.outs_bytes = outs_bytes;
+    req.lens_out = lens_out;
+    req.lens_out_n = lens_out_n;
+    req.val_size = sizeof(Val);
+    req.customer = obj_;
+    req.responses = Postoffice::Get()->num_servers();
+    req.on_done = cb;
+    route->Submit(req);
+    return ts;
+  }
+
   // One pulled slice, kept in the slot of the server that sent it.
   struct PullSlot {
     bool filled = false;

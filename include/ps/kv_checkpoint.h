@@ -62,9 +62,19 @@ class CheckpointableHandle {
       res.keys = req_data.keys;
       res.vals.resize(n * k);
     }
+    // A pull that comes before the first push finds no width yet: it is answered with one
+    // zero per key and stores nothing, so that the first push is free to fix the width.  A
+    // slot whose length differs from the width (a file written by an older layout) is
+    // brought to the width before it is touched.
+    const bool may_insert = req_meta.push || st.width != 0;
     for (size_t i = 0; i < n; ++i) {
-      std::vector<Val>& slot = st.store[req_data.keys[static_cast<int>(i)]];
-      if (slot.empty()) slot.assign(k, Val());
+      const Key key = req_data.keys[static_cast<int>(i)];
+      if (!may_insert) {
+        auto it = st.store.find(key);
+        if (it == st.store.end()) continue;  // res.vals is zero-filled already
+      }
+      std::vector<Val>& slot = st.store[key];
+      if (slot.size() != k) slot.resize(k, Val());
       if (req_meta.push)
         for (size_t j = 0; j < k; ++j) slot[j] += req_data.vals[static_cast<int>(i * k + j)];
       if (req_meta.pull)

@@ -35,6 +35,8 @@ struct SimpleBox {
 extern "C" {
 
 const char* ps_capi_last_error(void) { return g_err.c_str(); }
+// for the other translation units of the C ABI
+void ps_capi_set_error(const char* text) { g_err = text ? text : ""; }
 
 int ps_capi_setenv(const char* key, const char* value) {
   return Guard([&] {

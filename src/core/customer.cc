@@ -51,11 +51,35 @@ bool Customer::WaitRequestFor(int timestamp, int timeout_ms) {
     const auto& e = tracker_[timestamp - tracker_base_];
     return e.first <= e.second;
   };
+  bool finished = true;
   if (timeout_ms < 0) {
     tracker_cond_.wait(lk, done);
-    return true;
+  } else {
+    finished = tracker_cond_.wait_for(lk, std::chrono::milliseconds(timeout_ms), done);
   }
-  return tracker_cond_.wait_for(lk, std::chrono::milliseconds(timeout_ms), done);
+  if (finished) {
+    auto it = failed_.find(timestamp);
+    if (it != failed_.end()) {
+      const std::string why = it->second;
+      failed_.erase(it);
+      lk.unlock();
+      LOG(FATAL) << "request " << timestamp << " failed: " << why;
+    }
+  }
+  return finished;
+}
+
+void Customer::FailRequest(int timestamp, const std::string& why) {
+  {
+    std::lock_guard<std::mutex> lk(tracker_mu_);
+    failed_[timestamp] = why;
+    if (failed_.size() > kTrackerWindow) failed_.erase(failed_.begin());
+    if (timestamp >= tracker_base_) {
+      auto& e = tracker_[timestamp - tracker_base_];
+      e.second = e.first;
+    }
+  }
+  tracker_cond_.notify_all();
 }
 
 int Customer::NumResponse(int timestamp) {

@@ -86,7 +86,7 @@ void Postoffice::Start(int customer_id, const char* argv0, const bool do_barrier
       }
     }
     if (leader) {
-      Barrier(customer_id, kWorkerGroup + kServerGroup + kScheduler);
+      BarrierImpl(customer_id, kWorkerGroup + kServerGroup + kScheduler, true);
       std::lock_guard<std::mutex> lk(barrier_mu_);
       start_barrier_done_ = true;
       barrier_cond_.notify_all();
@@ -109,7 +109,7 @@ void Postoffice::Finalize(const int customer_id, const bool do_barrier) {
     last = (finalizing_customers_ >= started_customers_);
   }
   if (last) {
-    if (do_barrier) Barrier(customer_id, kWorkerGroup + kServerGroup + kScheduler);
+    if (do_barrier) BarrierImpl(customer_id, kWorkerGroup + kServerGroup + kScheduler, true);
     std::lock_guard<std::mutex> lk(barrier_mu_);
     ++finalize_generation_;
     barrier_cond_.notify_all();
@@ -191,6 +191,10 @@ Customer* Postoffice::GetCustomer(int app_id, int customer_id, int timeout, int 
 }
 
 void Postoffice::Barrier(int customer_id, int node_group) {
+  BarrierImpl(customer_id, node_group, /*process_wide=*/false);
+}
+
+void Postoffice::BarrierImpl(int customer_id, int node_group, bool process_wide) {
   const std::vector<int>& members = GetNodeIDs(node_group);
   if (members.size() <= 1) return;
   std::vector<int> mine;
@@ -200,11 +204,24 @@ void Postoffice::Barrier(int customer_id, int node_group) {
 
   std::unique_lock<std::mutex> lk(barrier_mu_);
   Round& r = rounds_[node_group];
+  if (!process_wide) {
+    // Every customer's k-th call belongs to the k-th round of the group.  A round that a
+    // sibling customer of this process opened may already have been released when this
+    // customer calls: it then takes that round instead of opening another one, which would
+    // leave a half-counted round at the scheduler.
+    uint64_t& passed = r.passed[customer_id];
+    if (passed < r.floor) passed = r.floor;
+    if (passed < r.generation) {
+      ++passed;
+      return;
+    }
+  }
   const uint64_t gen = r.generation;
   if (!r.in_flight) {
     // first caller of this round: announce every id this process hosts in the group;
     // customers that call while the round is open simply join it
     r.in_flight = true;
+    r.process_wide = process_wide;
     r.pending = static_cast<int>(mine.size());
     lk.unlock();
     for (int id : mine) {
@@ -220,8 +237,15 @@ void Postoffice::Barrier(int customer_id, int node_group) {
       van_->Send(req);
     }
     lk.lock();
+  } else if (process_wide) {
+    r.process_wide = true;
   }
   barrier_cond_.wait(lk, [this, node_group, gen] { return rounds_[node_group].generation != gen; });
+  if (!process_wide) {
+    Round& rr = rounds_[node_group];
+    uint64_t& passed = rr.passed[customer_id];
+    if (passed < gen + 1) passed = gen + 1;
+  }
 }
 
 void Postoffice::Manage(const Message& recv) {
@@ -232,6 +256,9 @@ void Postoffice::Manage(const Message& recv) {
     if (r.in_flight && --r.pending <= 0) {
       r.in_flight = false;
       ++r.generation;
+      // a round entered once for the whole process (Start, Finalize) counts for every customer
+      if (r.process_wide) r.floor = r.generation;
+      r.process_wide = false;
       barrier_cond_.notify_all();
     }
   }

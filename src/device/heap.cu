@@ -149,6 +149,25 @@ extern "C" int psdev_channel_status(void* local_base, int channel, int32_t* stat
   return 0;
 }
 
+// Same read on a stream of the caller's (a non-blocking one: the plain form above copies on the
+// default stream, which waits for every blocking stream of the process).
+extern "C" int psdev_channel_status_on(void* local_base, int channel, void* stream,
+                                       int32_t* status, uint64_t* epoch) {
+  if (!local_base || channel < 0 || channel >= PSDEV_NUM_CHANNELS) return PSDEV_ERR_ARG;
+  auto* c = static_cast<psdev::Ctrl*>(local_base);
+  cudaStream_t s = (cudaStream_t)stream;
+  cudaError_t e;
+  if (status) {
+    e = cudaMemcpyAsync(status, &c->status[channel], sizeof(int32_t), cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return (int)e;
+  }
+  if (epoch) {
+    e = cudaMemcpyAsync(epoch, &c->epoch[channel], sizeof(uint64_t), cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return (int)cudaStreamSynchronize(s);
+}
+
 extern "C" int psdev_channel_clear(void* local_base, int channel) {
   if (!local_base || channel < 0 || channel >= PSDEV_NUM_CHANNELS) return PSDEV_ERR_ARG;
   auto* c = static_cast<psdev::Ctrl*>(local_base);

@@ -227,7 +227,7 @@ __global__ void barrier_kernel(const __grid_constant__ BarrierArgs a) {
   channel_leave(a.base, a.rank, a.world, a.channel, e, a.timeout_ns, &s_last);
 }
 
-__global__ void copy_probe_kernel(uint4* dst, const uint4* src, size_t n16) {
+__global__ void link_copy_kernel(uint4* dst, const uint4* src, size_t n16) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n16;
        i += (size_t)gridDim.x * blockDim.x)
     st_v4(dst + i, ld_sys_v4(src + i));
@@ -250,10 +250,10 @@ extern "C" int psdev_device_barrier(const psdev_world_t* w, int channel, uint64_
   return (int)cudaGetLastError();
 }
 
-extern "C" int psdev_copy_probe(void* dst, const void* src, size_t bytes, int num_ctas,
+extern "C" int psdev_link_copy(void* dst, const void* src, size_t bytes, int num_ctas,
                                 void* stream) {
   if ((bytes & 15) || ((uintptr_t)dst & 15) || ((uintptr_t)src & 15)) return PSDEV_ERR_ARG;
-  copy_probe_kernel<<<num_ctas > 0 ? num_ctas : 296, 512, 0, (cudaStream_t)stream>>>(
+  link_copy_kernel<<<num_ctas > 0 ? num_ctas : 296, 512, 0, (cudaStream_t)stream>>>(
       (uint4*)dst, (const uint4*)src, bytes / 16);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return (int)cudaGetLastError();

@@ -1,0 +1,1130 @@
+// nvl_van: the device plane of the host runtime (declaration and overview: ps/device/plane.h).
+//
+// What happens here, in the order of a job's life:
+//   * Start: bind the CUDA library at run time, create this rank's arena, exchange arena
+//     handles with the other workers over the control plane, map the peers, optionally build
+//     the multicast alias, attach to the Postoffice as its DeviceRoute.
+//   * Submit: a KVWorker request on a registered tensor becomes copies and kernel launches on
+//     CUDA streams (a slice pipeline when values live in host memory), followed by an event.
+//   * Completing: a thread waits for those events in submission order, reads the channel's
+//     status word, runs the request's callback and credits the Customer tracker -- the role
+//     the Customer's receive thread plays for responses that arrive as messages
+//     (reference: src/customer.cc:49-64, include/ps/kv_app.h:616-640).
+//   * Stop: drain, barrier, unbind, unmap.
+#include <dlfcn.h>
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/socket.h>
+#include <sys/un.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <chrono>
+#include <cmath>
+#include <condition_variable>
+#include <cstring>
+#include <deque>
+#include <map>
+#include <mutex>
+#include <random>
+#include <sstream>
+#include <thread>
+
+#include "ps/device/ctrl_layout.h"
+#include "ps/device/plane.h"
+#include "ps/internal/postoffice.h"
+#include "ps/simple_app.h"
+#include "van/nvl_host_sim.h"
+
+namespace ps {
+namespace device {
+namespace {
+
+constexpr int kPlaneApp = 0x6e766c;  // app id of the plane's own simple-app endpoint ("nvl")
+constexpr int kHeadGather = 1;
+
+// ---- run-time binding of the CUDA library -----------------------------------------------------
+struct Rt {
+  int (*set_device)(int) = nullptr;
+  int (*malloc_)(void**, size_t) = nullptr;
+  int (*free_)(void*) = nullptr;
+  int (*stream_create)(void**, int) = nullptr;
+  int (*stream_destroy)(void*) = nullptr;
+  int (*stream_sync)(void*) = nullptr;
+  int (*event_create)(void**) = nullptr;
+  int (*event_destroy)(void*) = nullptr;
+  int (*event_record)(void*, void*) = nullptr;
+  int (*event_sync)(void*) = nullptr;
+  int (*stream_wait_event)(void*, void*) = nullptr;
+  int (*memcpy_async)(void*, const void*, size_t, void*) = nullptr;
+  int (*is_device_pointer)(const void*) = nullptr;
+  int (*heap_create)(size_t, void**, unsigned char*) = nullptr;
+  int (*heap_open)(const unsigned char*, void**) = nullptr;
+  int (*heap_close)(void*) = nullptr;
+  int (*heap_destroy)(void*) = nullptr;
+  int (*vmm_supported)() = nullptr;
+  int (*vmm_create_aligned)(size_t, size_t, void**, int*, size_t*) = nullptr;
+  int (*vmm_import)(int, size_t, void**) = nullptr;
+  int (*vmm_release)(void*) = nullptr;
+  int (*mc_supported)() = nullptr;
+  int (*mc_granularity)(int, size_t, size_t*) = nullptr;
+  int (*mc_create)(size_t, int, int*, void**) = nullptr;
+  int (*mc_import)(int, size_t, void**) = nullptr;
+  int (*mc_add_device)(void*) = nullptr;
+  int (*mc_bind)(void*, void*) = nullptr;
+  int (*mc_map)(void*, void**) = nullptr;
+  int (*mc_release)(void*) = nullptr;
+  int (*channel_status_on)(void*, int, void*, int32_t*, uint64_t*) = nullptr;
+  int (*channel_clear)(void*, int) = nullptr;
+  int (*dense_op)(const psdev_world_t*, const psdev_table_t*, int, int64_t, int64_t,
+                  const psdev_opt_t*, int, int, uint64_t, int, void*) = nullptr;
+  uint64_t (*launch_count)() = nullptr;
+};
+
+template <typename Fn>
+void Bind(void* lib, const char* name, Fn* out) {
+  void* p = dlsym(lib, name);
+  CHECK(p) << "the device library lacks " << name;
+  *out = reinterpret_cast<Fn>(p);
+}
+
+std::string DirOfThisLibrary() {
+  Dl_info info;
+  if (dladdr(reinterpret_cast<void*>(&DirOfThisLibrary), &info) && info.dli_fname) {
+    std::string path(info.dli_fname);
+    const size_t cut = path.rfind('/');
+    if (cut != std::string::npos) return path.substr(0, cut);
+  }
+  return ".";
+}
+
+void* LoadRt(const std::string& configured, Rt* rt) {
+  std::string path = configured;
+  if (path.empty()) {
+    const char* env = getenv("PSB200_DEVICE_LIB");
+    path = env ? env : DirOfThisLibrary() + "/libpsb200_device.so";
+  }
+  void* lib = dlopen(path.c_str(), RTLD_NOW | RTLD_GLOBAL);
+  CHECK(lib) << "cannot load the device library " << path << ": " << dlerror();
+  Bind(lib, "psdev_rt_set_device", &rt->set_device);
+  Bind(lib, "psdev_rt_malloc", &rt->malloc_);
+  Bind(lib, "psdev_rt_free", &rt->free_);
+  Bind(lib, "psdev_rt_stream_create", &rt->stream_create);
+  Bind(lib, "psdev_rt_stream_destroy", &rt->stream_destroy);
+  Bind(lib, "psdev_rt_stream_sync", &rt->stream_sync);
+  Bind(lib, "psdev_rt_event_create", &rt->event_create);
+  Bind(lib, "psdev_rt_event_destroy", &rt->event_destroy);
+  Bind(lib, "psdev_rt_event_record", &rt->event_record);
+  Bind(lib, "psdev_rt_event_sync", &rt->event_sync);
+  Bind(lib, "psdev_rt_stream_wait_event", &rt->stream_wait_event);
+  Bind(lib, "psdev_rt_memcpy_async", &rt->memcpy_async);
+  Bind(lib, "psdev_rt_is_device_pointer", &rt->is_device_pointer);
+  Bind(lib, "psdev_heap_create", &rt->heap_create);
+  Bind(lib, "psdev_heap_open", &rt->heap_open);
+  Bind(lib, "psdev_heap_close", &rt->heap_close);
+  Bind(lib, "psdev_heap_destroy", &rt->heap_destroy);
+  Bind(lib, "psdev_vmm_supported", &rt->vmm_supported);
+  Bind(lib, "psdev_vmm_create_aligned", &rt->vmm_create_aligned);
+  Bind(lib, "psdev_vmm_import", &rt->vmm_import);
+  Bind(lib, "psdev_vmm_release", &rt->vmm_release);
+  Bind(lib, "psdev_mc_supported", &rt->mc_supported);
+  Bind(lib, "psdev_mc_granularity", &rt->mc_granularity);
+  Bind(lib, "psdev_mc_create", &rt->mc_create);
+  Bind(lib, "psdev_mc_import", &rt->mc_import);
+  Bind(lib, "psdev_mc_add_device", &rt->mc_add_device);
+  Bind(lib, "psdev_mc_bind", &rt->mc_bind);
+  Bind(lib, "psdev_mc_map", &rt->mc_map);
+  Bind(lib, "psdev_mc_release", &rt->mc_release);
+  Bind(lib, "psdev_channel_status_on", &rt->channel_status_on);
+  Bind(lib, "psdev_channel_clear", &rt->channel_clear);
+  Bind(lib, "psdev_dense_op", &rt->dense_op);
+  Bind(lib, "psdev_launch_count", &rt->launch_count);
+  return lib;
+}
+
+// ---- CPU stand-in of the same table: arenas are shared memory, work is done at once ---------
+std::atomic<uint64_t> g_sim_launches{0};
+int SimOk1(void*) { return 0; }
+int SimSetDevice(int) { return 0; }
+int SimMalloc(void** p, size_t bytes) {
+  *p = calloc(1, bytes ? bytes : 1);
+  return *p ? 0 : PSDEV_ERR_NOMEM;
+}
+int SimFree(void* p) {
+  free(p);
+  return 0;
+}
+int SimStreamCreate(void** s, int) {
+  *s = nullptr;
+  return 0;
+}
+int SimEventCreate(void** e) {
+  *e = nullptr;
+  return 0;
+}
+int SimEventRecord(void*, void*) { return 0; }
+int SimMemcpy(void* dst, const void* src, size_t bytes, void*) {
+  memmove(dst, src, bytes);
+  return 0;
+}
+int SimChannelStatusOn(void* base, int channel, void*, int32_t* st, uint64_t* ep) {
+  return sim::ChannelStatus(base, channel, st, ep);
+}
+int SimDenseOp(const psdev_world_t* w, const psdev_table_t* t, int op, int64_t b, int64_t e,
+               const psdev_opt_t* o, int channel, int, uint64_t tmo, int sync, void*) {
+  g_sim_launches.fetch_add(1, std::memory_order_relaxed);
+  return sim::DenseOp(w, t, op, b, e, o, channel, tmo, sync);
+}
+uint64_t SimLaunchCount() { return g_sim_launches.load(std::memory_order_relaxed); }
+
+void FillSimRt(Rt* rt) {
+  rt->set_device = SimSetDevice;
+  rt->malloc_ = SimMalloc;
+  rt->free_ = SimFree;
+  rt->stream_create = SimStreamCreate;
+  rt->stream_destroy = SimOk1;
+  rt->stream_sync = SimOk1;
+  rt->event_create = SimEventCreate;
+  rt->event_destroy = SimOk1;
+  rt->event_record = SimEventRecord;
+  rt->event_sync = SimOk1;
+  rt->stream_wait_event = SimEventRecord;
+  rt->memcpy_async = SimMemcpy;
+  rt->channel_status_on = SimChannelStatusOn;
+  rt->channel_clear = sim::ChannelClear;
+  rt->dense_op = SimDenseOp;
+  rt->launch_count = SimLaunchCount;
+}
+
+// ---- first-fit sub-allocator of the arena (host bookkeeping only) ---------------------------
+class SubAlloc {
+ public:
+  explicit SubAlloc(size_t bytes) : bytes_(bytes) { free_[PSDEV_CTRL_BYTES] = bytes - PSDEV_CTRL_BYTES; }
+  int64_t Alloc(size_t bytes, size_t align) {
+    if (align < 16) align = 16;
+    bytes = (bytes + 255) & ~size_t(255);
+    if (bytes == 0) bytes = 256;
+    for (auto it = free_.begin(); it != free_.end(); ++it) {
+      const size_t lo = it->first, len = it->second;
+      const size_t at = (lo + align - 1) / align * align;
+      if (at + bytes > lo + len) continue;
+      free_.erase(it);
+      if (at > lo) free_[lo] = at - lo;
+      if (at + bytes < lo + len) free_[at + bytes] = lo + len - (at + bytes);
+      used_[at] = bytes;
+      in_use_ += bytes;
+      return static_cast<int64_t>(at);
+    }
+    return -1;
+  }
+  bool Free(int64_t off) {
+    auto it = used_.find(static_cast<size_t>(off));
+    if (it == used_.end()) return false;
+    size_t lo = it->first, len = it->second;
+    in_use_ -= len;
+    used_.erase(it);
+    auto next = free_.lower_bound(lo);
+    if (next != free_.end() && lo + len == next->first) {
+      len += next->second;
+      next = free_.erase(next);
+    }
+    if (next != free_.begin()) {
+      auto prev = std::prev(next);
+      if (prev->first + prev->second == lo) {
+        lo = prev->first;
+        len += prev->second;
+        free_.erase(prev);
+      }
+    }
+    free_[lo] = len;
+    return true;
+  }
+  size_t in_use() const { return in_use_; }
+
+ private:
+  size_t bytes_;
+  std::map<size_t, size_t> free_, used_;
+  size_t in_use_ = 0;
+};
+
+// ---- descriptors between the processes of one host -------------------------------------------
+// Each rank binds a datagram socket in the abstract namespace; the names go round through
+// `gather` (the control plane); every rank then sends its descriptors to every peer as
+// SCM_RIGHTS data.  Returns, for every rank, the descriptors it sent (own entry: duplicates).
+std::vector<std::vector<int>> ExchangeFds(int rank, int world, const std::vector<int>& mine,
+                                          const std::function<std::vector<std::string>(
+                                              const std::string&)>& gather) {
+  std::vector<std::vector<int>> got(world);
+  for (int fd : mine) got[rank].push_back(dup(fd));
+  if (world == 1) return got;
+  std::random_device rd;
+  std::ostringstream name;
+  name << "psb200-nvl-" << getpid() << "-" << rd() << "-" << rank;
+  const std::string mine_name = name.str();
+  const int srv = socket(AF_UNIX, SOCK_DGRAM | SOCK_CLOEXEC, 0);
+  CHECK_GE(srv, 0) << "socket: " << strerror(errno);
+  auto addr_of = [](const std::string& n, sockaddr_un* a) {
+    memset(a, 0, sizeof(*a));
+    a->sun_family = AF_UNIX;
+    CHECK_LT(n.size() + 1, sizeof(a->sun_path));
+    memcpy(a->sun_path + 1, n.data(), n.size());  // leading NUL: abstract namespace
+    return static_cast<socklen_t>(offsetof(sockaddr_un, sun_path) + 1 + n.size());
+  };
+  sockaddr_un me;
+  const socklen_t me_len = addr_of(mine_name, &me);
+  CHECK_EQ(bind(srv, reinterpret_cast<sockaddr*>(&me), me_len), 0) << strerror(errno);
+  timeval tv{60, 0};
+  setsockopt(srv, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
+  const std::vector<std::string> names = gather(mine_name);  // everyone is bound after this
+  CHECK_EQ(names.size(), static_cast<size_t>(world));
+  const int out = socket(AF_UNIX, SOCK_DGRAM | SOCK_CLOEXEC, 0);
+  CHECK_GE(out, 0);
+  const size_t nfd = mine.size();
+  CHECK(nfd >= 1 && nfd <= 8);
+  for (int p = 0; p < world; ++p) {
+    if (p == rank) continue;
+    sockaddr_un to;
+    const socklen_t to_len = addr_of(names[p], &to);
+    int32_t hdr[2] = {rank, static_cast<int32_t>(nfd)};
+    iovec iov{hdr, sizeof(hdr)};
+    alignas(cmsghdr) char ctl[CMSG_SPACE(sizeof(int) * 8)];
+    memset(ctl, 0, sizeof(ctl));
+    msghdr msg{};
+    msg.msg_name = &to;
+    msg.msg_namelen = to_len;
+    msg.msg_iov = &iov;
+    msg.msg_iovlen = 1;
+    msg.msg_control = ctl;
+    msg.msg_controllen = CMSG_SPACE(sizeof(int) * nfd);
+    cmsghdr* c = CMSG_FIRSTHDR(&msg);
+    c->cmsg_level = SOL_SOCKET;
+    c->cmsg_type = SCM_RIGHTS;
+    c->cmsg_len = CMSG_LEN(sizeof(int) * nfd);
+    memcpy(CMSG_DATA(c), mine.data(), sizeof(int) * nfd);
+    CHECK_GE(sendmsg(out, &msg, 0), 0) << "sendmsg to rank " << p << ": " << strerror(errno);
+  }
+  close(out);
+  for (int k = 0; k < world - 1; ++k) {
+    int32_t hdr[2] = {-1, 0};
+    iovec iov{hdr, sizeof(hdr)};
+    alignas(cmsghdr) char ctl[CMSG_SPACE(sizeof(int) * 8)];
+    msghdr msg{};
+    msg.msg_iov = &iov;
+    msg.msg_iovlen = 1;
+    msg.msg_control = ctl;
+    msg.msg_controllen = sizeof(ctl);
+    const ssize_t n = recvmsg(srv, &msg, MSG_CMSG_CLOEXEC);
+    CHECK_EQ(n, static_cast<ssize_t>(sizeof(hdr))) << "descriptor exchange: " << strerror(errno);
+    const int src = hdr[0];
+    CHECK(src >= 0 && src < world && src != rank && got[src].empty())
+        << "unexpected descriptor message from rank " << src;
+    cmsghdr* c = CMSG_FIRSTHDR(&msg);
+    CHECK(c && c->cmsg_level == SOL_SOCKET && c->cmsg_type == SCM_RIGHTS);
+    const size_t cnt = (c->cmsg_len - CMSG_LEN(0)) / sizeof(int);
+    CHECK_EQ(cnt, static_cast<size_t>(hdr[1]));
+    got[src].resize(cnt);
+    memcpy(got[src].data(), CMSG_DATA(c), cnt * sizeof(int));
+  }
+  close(srv);
+  return got;
+}
+
+// ---- all-gather among the workers over simple-app messages ---------------------------------
+class Exchange : public SimpleApp {
+ public:
+  Exchange() : SimpleApp(kPlaneApp, kPlaneApp) {
+    set_request_handle([this](const SimpleData& req, SimpleApp* app) {
+      if (req.head == kHeadGather && req.body.size() >= 4) {
+        uint32_t round;
+        memcpy(&round, req.body.data(), 4);
+        const int from = Postoffice::IDtoRank(req.sender);
+        {
+          std::lock_guard<std::mutex> lk(mu_);
+          rounds_[round][from] = req.body.substr(4);
+        }
+        cv_.notify_all();
+      }
+      app->Response(req);
+    });
+  }
+
+  std::vector<std::string> AllGather(const std::string& mine, int world) {
+    uint32_t round;
+    {
+      std::lock_guard<std::mutex> lk(mu_);
+      round = next_round_++;
+    }
+    std::string body(4, '\0');
+    memcpy(&body[0], &round, 4);
+    body += mine;
+    Wait(Request(kHeadGather, body, kWorkerGroup));
+    std::unique_lock<std::mutex> lk(mu_);
+    const bool ok = cv_.wait_for(lk, std::chrono::seconds(120), [&] {
+      return rounds_[round].size() == static_cast<size_t>(world);
+    });
+    CHECK(ok) << "all-gather round " << round << " got " << rounds_[round].size() << " of "
+              << world << " contributions";
+    std::vector<std::string> out(world);
+    for (auto& kv : rounds_[round]) {
+      CHECK(kv.first >= 0 && kv.first < world);
+      out[kv.first] = std::move(kv.second);
+    }
+    rounds_.erase(round);
+    return out;
+  }
+
+ private:
+  std::mutex mu_;
+  std::condition_variable cv_;
+  uint32_t next_round_ = 0;
+  std::map<uint32_t, std::map<int, std::string>> rounds_;
+};
+
+size_t DtypeSize(int dt) { return dt == PSDEV_F32 ? 4 : (dt == PSDEV_BF16 ? 2 : 1); }
+
+thread_local void* tls_stream = nullptr;
+
+}  // namespace
+
+// ================================================================================================
+struct Plane::Impl {
+  PlaneOptions opts;
+  bool started = false;
+  bool sim = false;
+  std::string backend_name;
+  Rt rt;
+  void* lib = nullptr;
+  int rank = 0, world = 1;
+  psdev_world_t ws{};
+  size_t arena_bytes = 0;
+  void* mc = nullptr;
+  std::unique_ptr<Exchange> exchange;
+  std::unique_ptr<SubAlloc> sub;
+  mutable std::mutex mu;  // tables, allocator, channel counter
+  std::map<std::pair<int, uint64_t>, std::unique_ptr<DenseInfo>> dense;
+  int next_channel = 0;
+
+  void* s_h2d = nullptr;
+  void* s_compute = nullptr;
+  void* s_d2h = nullptr;
+  void* s_status = nullptr;
+  std::vector<void*> event_pool;
+  std::mutex ev_mu;
+  // requests on one tensor are serialised against each other: the last event of the previous
+  // one (keyed by DenseInfo*)
+  std::map<const DenseInfo*, void*> last_done;
+
+  struct Pending {
+    void* event = nullptr;
+    std::vector<void*> events_to_recycle;
+    int channel = 0;
+    int timestamp = 0;
+    int responses = 1;
+    Customer* customer = nullptr;
+    std::function<void()> on_done;
+    int* lens_out = nullptr;
+    std::vector<int> lens;
+    const DenseInfo* tensor = nullptr;
+  };
+  std::mutex q_mu;
+  std::condition_variable q_cv, idle_cv;
+  std::deque<Pending> queue;
+  bool stop = false;
+  int in_flight = 0;
+  std::thread completer;
+
+  void* NewEvent() {
+    {
+      std::lock_guard<std::mutex> lk(ev_mu);
+      if (!event_pool.empty()) {
+        void* e = event_pool.back();
+        event_pool.pop_back();
+        return e;
+      }
+    }
+    void* e = nullptr;
+    CHECK_EQ(rt.event_create(&e), 0);
+    return e;
+  }
+  void RecycleEvent(void* e) {
+    if (sim) return;
+    std::lock_guard<std::mutex> lk(ev_mu);
+    event_pool.push_back(e);
+  }
+
+  void Completing() {
+    rt.set_device(opts.device);
+    for (;;) {
+      Pending p;
+      {
+        std::unique_lock<std::mutex> lk(q_mu);
+        q_cv.wait(lk, [&] { return stop || !queue.empty(); });
+        if (queue.empty()) return;
+        p = std::move(queue.front());
+        queue.pop_front();
+      }
+      int rc = rt.event_sync(p.event);
+      int32_t status = 0;
+      if (rc == 0)
+        rc = rt.channel_status_on(ws.peer_base[rank], p.channel, s_status, &status, nullptr);
+      if (p.lens_out)
+        for (size_t i = 0; i < p.lens.size(); ++i) p.lens_out[i] = p.lens[i];
+      if (p.on_done) p.on_done();  // before the request counts as complete, like the reference
+      if (p.customer) {
+        if (rc != 0 || status != 0) {
+          std::ostringstream why;
+          why << "device plane: ";
+          if (rc != 0) why << "CUDA error " << rc;
+          else why << "status " << status << " on channel " << p.channel
+                   << (status == PSDEV_ERR_TIMEOUT_ENTRY || status == PSDEV_ERR_TIMEOUT_EXIT
+                           ? " (a peer did not arrive within the deadline)"
+                           : "");
+          p.customer->FailRequest(p.timestamp, why.str());
+        } else {
+          p.customer->AddResponse(p.timestamp, p.responses);
+        }
+      }
+      {
+        // the event stops being the ordering point of its tensor before it is reused
+        std::lock_guard<std::mutex> lk(mu);
+        auto it = last_done.find(p.tensor);
+        if (it != last_done.end() && it->second == p.event) last_done.erase(it);
+      }
+      RecycleEvent(p.event);
+      for (void* e : p.events_to_recycle) RecycleEvent(e);
+      {
+        std::lock_guard<std::mutex> lk(q_mu);
+        --in_flight;
+      }
+      idle_cv.notify_all();
+    }
+  }
+
+  void Drain() {
+    std::unique_lock<std::mutex> lk(q_mu);
+    idle_cv.wait(lk, [&] { return in_flight == 0; });
+  }
+};
+
+Plane::Plane() : impl_(new Impl) {}
+Plane::~Plane() {}
+
+Plane* Plane::Get() {
+  static Plane* p = new Plane;  // outlives static destruction, like the Postoffice
+  return p;
+}
+
+bool Plane::started() const { return impl_->started; }
+int Plane::rank() const { return impl_->rank; }
+int Plane::world() const { return impl_->world; }
+const psdev_world_t& Plane::world_struct() const { return impl_->ws; }
+const PlaneOptions& Plane::options() const { return impl_->opts; }
+const std::string& Plane::backend() const { return impl_->backend_name; }
+uint64_t Plane::launches() const { return impl_->rt.launch_count ? impl_->rt.launch_count() : 0; }
+void Plane::SetStream(void* stream) { tls_stream = stream; }
+
+std::vector<std::string> Plane::AllGather(const std::string& mine) {
+  Impl& m = *impl_;
+  CHECK(m.exchange) << "the device plane is not started";
+  if (m.world == 1) return {mine};
+  return m.exchange->AllGather(mine, m.world);
+}
+
+void Plane::Barrier() {
+  if (impl_->world > 1) Postoffice::Get()->Barrier(kPlaneApp, kWorkerGroup);
+}
+
+void Plane::Start(const PlaneOptions& options) {
+  Impl& m = *impl_;
+  CHECK(!m.started) << "the device plane is already started";
+  Postoffice* po = Postoffice::Get();
+  CHECK(po->van() && po->is_worker())
+      << "start the device plane after ps::Start, on a worker or joint process";
+  m.opts = options;
+  m.sim = options.device < 0;
+  m.rank = po->my_rank();
+  m.world = po->num_workers();
+  CHECK(m.world >= 1 && m.world <= PSDEV_MAX_RANKS)
+      << "the device plane serves up to " << PSDEV_MAX_RANKS << " workers of one machine";
+  if (m.sim) {
+    FillSimRt(&m.rt);
+  } else {
+    m.lib = LoadRt(options.device_lib, &m.rt);
+    CHECK_EQ(m.rt.set_device(options.device), 0) << "cannot select CUDA device " << options.device;
+  }
+  m.exchange.reset(new Exchange);
+  // nobody sends before every endpoint exists
+  Barrier();
+
+  const int R = m.rank, W = m.world;
+  auto gather = [this](const std::string& s) { return AllGather(s); };
+  std::string backend = m.sim ? "sim" : options.backend;
+  if (backend == "auto") {
+    const char* env = getenv("PSB200_HEAP");
+    backend = env ? env : "auto";
+  }
+  if (backend == "auto") {
+    const std::string mine = m.rt.vmm_supported() ? "1" : "0";
+    bool all = true;
+    for (const auto& s : AllGather(mine)) all = all && s == "1";
+    backend = all ? "vmm" : "ipc";
+  }
+  CHECK(backend == "sim" || backend == "ipc" || backend == "vmm") << "unknown heap backend " << backend;
+  m.backend_name = backend;
+  m.ws = psdev_world_t{};
+  m.ws.rank = R;
+  m.ws.world = W;
+  size_t bytes = (options.heap_bytes + 255) & ~size_t(255);
+  CHECK_GE(bytes, size_t(2) * PSDEV_CTRL_BYTES);
+
+  if (backend == "sim") {
+    // shared memory, handed round as descriptors like the vmm arenas
+    const int fd = memfd_create("psb200-arena", MFD_CLOEXEC);
+    CHECK_GE(fd, 0) << strerror(errno);
+    CHECK_EQ(ftruncate(fd, static_cast<off_t>(bytes)), 0);
+    auto fds = ExchangeFds(R, W, {fd}, gather);
+    close(fd);
+    for (int p = 0; p < W; ++p) {
+      void* at = mmap(nullptr, bytes, PROT_READ | PROT_WRITE, MAP_SHARED, fds[p][0], 0);
+      CHECK(at != MAP_FAILED) << strerror(errno);
+      m.ws.peer_base[p] = at;
+      close(fds[p][0]);
+    }
+  } else if (backend == "ipc") {
+    void* base = nullptr;
+    unsigned char handle[PSDEV_IPC_HANDLE_BYTES];
+    CHECK_EQ(m.rt.heap_create(bytes, &base, handle), 0) << "arena of " << bytes << " bytes";
+    m.ws.peer_base[R] = base;
+    const auto handles = AllGather(std::string(reinterpret_cast<char*>(handle), sizeof(handle)));
+    for (int p = 0; p < W; ++p) {
+      if (p == R) continue;
+      CHECK_EQ(handles[p].size(), sizeof(handle));
+      void* at = nullptr;
+      const int rc = m.rt.heap_open(reinterpret_cast<const unsigned char*>(handles[p].data()), &at);
+      CHECK_EQ(rc, 0) << "cannot map the arena of rank " << p;
+      m.ws.peer_base[p] = at;
+    }
+  } else {
+    // multicast wanted?  every rank must be able, and the arena size must suit the object
+    bool want_mc = W > 1 && options.multicast != 0;
+    if (const char* env = getenv("PSB200_MULTICAST")) want_mc = want_mc && atoi(env) != 0;
+    size_t gran = 0;
+    if (want_mc) {
+      std::string mine = "0";
+      if (m.rt.mc_supported() && m.rt.mc_granularity(W, bytes, &gran) == 0 && gran)
+        mine = std::to_string(gran);
+      for (const auto& s : AllGather(mine)) want_mc = want_mc && s == mine && s != "0";
+      if (!want_mc && options.multicast == 1)
+        LOG(WARNING) << "NVSwitch multicast was requested but is not available on every rank";
+    }
+    void* base = nullptr;
+    int fd = -1;
+    size_t mapped = 0;
+    CHECK_EQ(m.rt.vmm_create_aligned(bytes, want_mc ? gran : 0, &base, &fd, &mapped), 0)
+        << "arena of " << bytes << " bytes";
+    m.ws.peer_base[R] = base;
+    const auto sizes = AllGather(std::to_string(mapped));
+    auto fds = ExchangeFds(R, W, {fd}, gather);
+    close(fd);
+    for (int p = 0; p < W; ++p) {
+      if (p != R) {
+        CHECK_EQ(sizes[p], std::to_string(mapped)) << "ranks disagree on the arena size";
+        void* at = nullptr;
+        CHECK_EQ(m.rt.vmm_import(fds[p][0], mapped, &at), 0)
+            << "cannot map the arena of rank " << p;
+        m.ws.peer_base[p] = at;
+      }
+      close(fds[p][0]);
+    }
+    bytes = mapped;
+    if (want_mc) {
+      // every step is agreed on by all ranks before the next one; any failure drops the
+      // alias everywhere and the job continues with plain peer accesses
+      auto agree = [&](bool ok) {
+        bool all = true;
+        for (const auto& s : AllGather(ok ? "1" : "0")) all = all && s == "1";
+        return all;
+      };
+      int mfd = -1;
+      bool ok = true;
+      if (R == 0) ok = m.rt.mc_create(mapped, W, &mfd, &m.mc) == 0;
+      ok = agree(ok);  // everyone learns whether rank 0 has an object to hand out
+      if (ok) {
+        // rank 0's descriptor goes to everyone (the others contribute a placeholder)
+        const int mine_fd = R == 0 ? mfd : open("/dev/null", O_RDONLY | O_CLOEXEC);
+        auto mfds = ExchangeFds(R, W, {mine_fd}, gather);
+        if (R != 0) ok = m.rt.mc_import(mfds[0][0], mapped, &m.mc) == 0;
+        for (auto& v : mfds)
+          for (int f : v) close(f);
+        close(mine_fd);
+      }
+      ok = agree(ok);
+      if (ok) ok = agree(m.rt.mc_add_device(m.mc) == 0);
+      if (ok) ok = agree(m.rt.mc_bind(m.mc, base) == 0);
+      void* alias = nullptr;
+      if (ok) ok = agree(m.rt.mc_map(m.mc, &alias) == 0);
+      if (ok) {
+        m.ws.mc_base = alias;
+      } else {
+        LOG(WARNING) << "NVSwitch multicast alias not available; using peer loads and stores";
+        if (m.mc) m.rt.mc_release(m.mc);
+        m.mc = nullptr;
+      }
+    }
+  }
+  m.arena_bytes = bytes;
+  m.ws.heap_bytes = bytes;
+  m.sub.reset(new SubAlloc(bytes));
+  m.next_channel = 0;
+  CHECK_EQ(m.rt.stream_create(&m.s_h2d, 0), 0);
+  CHECK_EQ(m.rt.stream_create(&m.s_compute, 1), 0);
+  CHECK_EQ(m.rt.stream_create(&m.s_d2h, 0), 0);
+  CHECK_EQ(m.rt.stream_create(&m.s_status, 0), 0);
+  m.stop = false;
+  m.in_flight = 0;
+  m.completer = std::thread(&Impl::Completing, &m);
+  m.started = true;
+  po->set_device_route(this);
+  // every rank has mapped every arena before anybody's kernel touches one
+  Barrier();
+  PS_VLOG(1) << "device plane up: rank " << R << "/" << W << ", backend " << backend
+             << (m.ws.mc_base ? " + multicast" : "") << ", arena " << bytes << " bytes";
+}
+
+void Plane::Stop() {
+  Impl& m = *impl_;
+  if (!m.started) return;
+  m.Drain();
+  if (!m.sim) {
+    m.rt.stream_sync(m.s_h2d);
+    m.rt.stream_sync(m.s_compute);
+    m.rt.stream_sync(m.s_d2h);
+  }
+  // nobody unmaps while a peer may still run a kernel that touches this arena
+  Barrier();
+  Postoffice::Get()->set_device_route(nullptr);
+  {
+    std::lock_guard<std::mutex> lk(m.q_mu);
+    m.stop = true;
+  }
+  m.q_cv.notify_all();
+  if (m.completer.joinable()) m.completer.join();
+  {
+    std::lock_guard<std::mutex> lk(m.mu);
+    for (auto& kv : m.dense) {
+      DenseInfo& d = *kv.second;
+      if (d.owns_state) {
+        m.rt.free_(d.table.master);
+        if (d.table.state1) m.rt.free_(d.table.state1);
+        if (d.table.state2) m.rt.free_(d.table.state2);
+      }
+    }
+    m.dense.clear();
+    m.last_done.clear();
+  }
+  if (m.mc) {
+    m.rt.mc_release(m.mc);
+    m.mc = nullptr;
+    Barrier();  // every rank has unbound before the arenas go away
+  }
+  for (int p = 0; p < m.world; ++p) {
+    void* at = m.ws.peer_base[p];
+    if (!at) continue;
+    if (m.backend_name == "sim") munmap(at, m.arena_bytes);
+    else if (m.backend_name == "vmm") m.rt.vmm_release(at);
+    else if (p != m.rank) m.rt.heap_close(at);
+  }
+  if (m.backend_name == "ipc") {
+    Barrier();  // peers have closed their mappings of this arena
+    m.rt.heap_destroy(m.ws.peer_base[m.rank]);
+  }
+  if (!m.sim) {
+    for (void* e : m.event_pool) m.rt.event_destroy(e);
+    m.rt.stream_destroy(m.s_h2d);
+    m.rt.stream_destroy(m.s_compute);
+    m.rt.stream_destroy(m.s_d2h);
+    m.rt.stream_destroy(m.s_status);
+  }
+  m.event_pool.clear();
+  m.exchange.reset();
+  m.sub.reset();
+  m.ws = psdev_world_t{};
+  m.started = false;
+}
+
+// ---- heap ---------------------------------------------------------------------------------------
+int64_t Plane::Alloc(size_t bytes, size_t align) {
+  std::lock_guard<std::mutex> lk(impl_->mu);
+  CHECK(impl_->sub) << "the device plane is not started";
+  return impl_->sub->Alloc(bytes, align);
+}
+void Plane::Free(int64_t offset) {
+  std::lock_guard<std::mutex> lk(impl_->mu);
+  if (impl_->sub) {
+    CHECK(impl_->sub->Free(offset)) << "not an allocation: offset " << offset;
+  }
+}
+void* Plane::Local(int64_t offset) const {
+  return static_cast<char*>(impl_->ws.peer_base[impl_->rank]) + offset;
+}
+size_t Plane::heap_in_use() const {
+  std::lock_guard<std::mutex> lk(impl_->mu);
+  return impl_->sub ? impl_->sub->in_use() : 0;
+}
+int Plane::NewChannel() {
+  std::lock_guard<std::mutex> lk(impl_->mu);
+  // the last channel is kept for device barriers
+  CHECK_LT(impl_->next_channel, PSDEV_NUM_CHANNELS - 1)
+      << "out of rendezvous channels: at most " << PSDEV_NUM_CHANNELS - 1 << " tensors";
+  return impl_->next_channel++;
+}
+
+// ---- dense tensors ------------------------------------------------------------------------------
+std::vector<Range> Plane::KeyRanges() const {
+  const uint64_t W = static_cast<uint64_t>(impl_->world);
+  const uint64_t width = kMaxKey / W;
+  std::vector<Range> r;
+  for (uint64_t i = 0; i < W; ++i) r.push_back(Range(width * i, width * (i + 1)));
+  return r;
+}
+
+std::vector<Key> Plane::DenseKeys(uint64_t tensor_id) const {
+  std::vector<Key> keys;
+  for (const Range& r : KeyRanges()) keys.push_back(static_cast<Key>(r.begin() + tensor_id));
+  return keys;
+}
+
+static int NumStates(int kind) {
+  return kind == PSDEV_OPT_MOMENTUM ? 1 : (kind == PSDEV_OPT_ADAM ? 2 : 0);
+}
+
+const DenseInfo& Plane::DeclareDense(int app_id, uint64_t tensor_id, int64_t n, int grad_dtype,
+                                     int out_dtype, const psdev_opt_t& opt) {
+  Impl& m = *impl_;
+  CHECK(m.started);
+  CHECK_GT(n, 0);
+  const int W = m.world;
+  const int64_t align = grad_dtype == PSDEV_I8 ? 256 : 8;
+  psdev_table_t t{};
+  t.n = (n + align - 1) / align * align;
+  t.blk = ((t.n + W - 1) / W + align - 1) / align * align;  // contiguous ranges, one per shard
+  const int64_t local_len = t.blk;  // one block per rank
+  t.grad_dtype = grad_dtype;
+  t.out_dtype = out_dtype;
+  const int64_t goff = Alloc(static_cast<size_t>(t.n) * DtypeSize(grad_dtype));
+  const int64_t woff = Alloc(static_cast<size_t>(t.n) * DtypeSize(out_dtype));
+  CHECK(goff >= 0 && woff >= 0) << "symmetric heap exhausted (tensor of " << n << " values)";
+  t.grad_off = static_cast<uint64_t>(goff);
+  t.weight_off = static_cast<uint64_t>(woff);
+  if (grad_dtype == PSDEV_I8) {
+    const int64_t soff = Alloc(static_cast<size_t>(t.n / 256) * 4);
+    CHECK_GE(soff, 0);
+    t.gscale_off = static_cast<uint64_t>(soff);
+  }
+  void* p = nullptr;
+  CHECK_EQ(m.rt.malloc_(&p, static_cast<size_t>(local_len) * 4), 0);
+  t.master = static_cast<float*>(p);
+  if (NumStates(opt.kind) >= 1) {
+    CHECK_EQ(m.rt.malloc_(&p, static_cast<size_t>(local_len) * 4), 0);
+    t.state1 = static_cast<float*>(p);
+  }
+  if (NumStates(opt.kind) >= 2) {
+    CHECK_EQ(m.rt.malloc_(&p, static_cast<size_t>(local_len) * 4), 0);
+    t.state2 = static_cast<float*>(p);
+  }
+  bool nvls = W >= 4;
+  if (const char* env = getenv("PSB200_NVLS")) nvls = atoi(env) != 0;
+  const DenseInfo& d = RegisterDense(app_id, tensor_id, n, t, opt, NewChannel(), nvls, 0);
+  const_cast<DenseInfo&>(d).owns_state = true;
+  return d;
+}
+
+const DenseInfo& Plane::RegisterDense(int app_id, uint64_t tensor_id, int64_t n_user,
+                                      const psdev_table_t& table, const psdev_opt_t& opt,
+                                      int channel, bool nvls, int num_ctas) {
+  Impl& m = *impl_;
+  CHECK(m.started);
+  std::unique_ptr<DenseInfo> d(new DenseInfo);
+  d->app_id = app_id;
+  d->tensor_id = tensor_id;
+  d->n = table.n;
+  d->n_user = n_user;
+  {
+    // key j names the j-th of W contiguous pieces of the tensor, whoever owns its blocks
+    const int64_t align = table.grad_dtype == PSDEV_I8 ? 256 : 8;
+    d->share = ((table.n + m.world - 1) / m.world + align - 1) / align * align;
+  }
+  d->channel = channel;
+  d->nvls = nvls && m.ws.mc_base != nullptr && m.world > 1;
+  d->num_ctas = num_ctas;
+  d->table = table;
+  d->opt = opt;
+  d->grad = Local(static_cast<int64_t>(table.grad_off));
+  d->weight = Local(static_cast<int64_t>(table.weight_off));
+  std::lock_guard<std::mutex> lk(m.mu);
+  auto key = std::make_pair(app_id, tensor_id);
+  CHECK(m.dense.find(key) == m.dense.end())
+      << "tensor " << tensor_id << " of app " << app_id << " is already registered";
+  DenseInfo* raw = d.get();
+  m.dense[key] = std::move(d);
+  return *raw;
+}
+
+void Plane::UnregisterDense(int app_id, uint64_t tensor_id) {
+  Impl& m = *impl_;
+  m.Drain();
+  std::lock_guard<std::mutex> lk(m.mu);
+  auto it = m.dense.find(std::make_pair(app_id, tensor_id));
+  if (it == m.dense.end()) return;
+  m.last_done.erase(it->second.get());
+  m.dense.erase(it);
+}
+
+const DenseInfo* Plane::FindDense(int app_id, uint64_t tensor_id) const {
+  std::lock_guard<std::mutex> lk(impl_->mu);
+  auto it = impl_->dense.find(std::make_pair(app_id, tensor_id));
+  return it == impl_->dense.end() ? nullptr : it->second.get();
+}
+
+void Plane::ClearStatus(int app_id, uint64_t tensor_id) {
+  const DenseInfo* d = FindDense(app_id, tensor_id);
+  CHECK(d) << "unknown tensor " << tensor_id;
+  impl_->Drain();
+  impl_->rt.set_device(impl_->opts.device);
+  CHECK_EQ(impl_->rt.channel_clear(impl_->ws.peer_base[impl_->rank], d->channel), 0);
+}
+
+void Plane::SetOptimizer(int app_id, uint64_t tensor_id, const psdev_opt_t& opt) {
+  std::lock_guard<std::mutex> lk(impl_->mu);
+  auto it = impl_->dense.find(std::make_pair(app_id, tensor_id));
+  CHECK(it != impl_->dense.end()) << "unknown tensor " << tensor_id;
+  it->second->opt = opt;
+}
+
+// ---- routing ------------------------------------------------------------------------------------
+namespace {
+// shard and tensor id named by a key
+inline void SplitKey(Key key, int world, int* shard, uint64_t* tensor_id) {
+  const uint64_t width = kMaxKey / static_cast<uint64_t>(world);
+  uint64_t s = static_cast<uint64_t>(key) / width;
+  if (s >= static_cast<uint64_t>(world)) s = world - 1;
+  *shard = static_cast<int>(s);
+  *tensor_id = static_cast<uint64_t>(key) - width * s;
+}
+}  // namespace
+
+bool Plane::Claims(int app_id, const SArray<Key>& keys) {
+  Impl& m = *impl_;
+  if (!m.started || keys.empty() || keys.mem_kind() != MemKind::kHost) return false;
+  int shard;
+  uint64_t id;
+  SplitKey(keys[0], m.world, &shard, &id);
+  return FindDense(app_id, id) != nullptr;
+}
+
+size_t Plane::PullBytes(int app_id, const SArray<Key>& keys) {
+  Impl& m = *impl_;
+  if (!m.started || keys.empty()) return 0;
+  int shard;
+  uint64_t id;
+  SplitKey(keys[0], m.world, &shard, &id);
+  const DenseInfo* d = FindDense(app_id, id);
+  if (!d) return 0;
+  size_t elems = 0;
+  for (size_t i = 0; i < keys.size(); ++i) {
+    uint64_t id_i;
+    SplitKey(keys[static_cast<int>(i)], m.world, &shard, &id_i);
+    const int64_t lo = std::min<int64_t>(shard * d->share, d->n_user);
+    const int64_t hi = std::min<int64_t>((shard + 1) * d->share, d->n_user);
+    elems += static_cast<size_t>(hi - lo);
+  }
+  return elems * DtypeSize(d->table.out_dtype);
+}
+
+void Plane::Submit(const DeviceRequest& req) {
+  Impl& m = *impl_;
+  CHECK(m.started);
+  m.rt.set_device(m.opts.device);
+  const int W = m.world;
+  int shard;
+  uint64_t id;
+  SplitKey(req.keys[0], W, &shard, &id);
+  DenseInfo* d = const_cast<DenseInfo*>(FindDense(req.app_id, id));
+  CHECK(d) << "no tensor registered under key " << req.keys[0];
+  const psdev_table_t& t = d->table;
+  const size_t gsz = DtypeSize(t.grad_dtype), osz = DtypeSize(t.out_dtype);
+
+  // keys -> runs of consecutive shards -> element ranges (in user elements: the last shard's
+  // share may be short)
+  struct Run { int64_t begin, end; };
+  std::vector<Run> runs;
+  std::vector<int> lens(req.keys.size());
+  int prev = -2;
+  for (size_t i = 0; i < req.keys.size(); ++i) {
+    uint64_t id_i;
+    SplitKey(req.keys[static_cast<int>(i)], W, &shard, &id_i);
+    CHECK_EQ(id_i, id) << "one request addresses one tensor (keys of tensors " << id << " and "
+                       << id_i << " were mixed)";
+    CHECK_GT(shard, prev == -2 ? -1 : prev) << "keys must be increasing";
+    const int64_t lo = std::min<int64_t>(shard * d->share, d->n_user);
+    const int64_t hi = std::min<int64_t>((shard + 1) * d->share, d->n_user);
+    lens[i] = static_cast<int>(hi - lo);
+    if (!req.lens.empty()) {
+      CHECK_EQ(req.lens[static_cast<int>(i)], lens[i])
+          << "length of key " << req.keys[static_cast<int>(i)] << " differs from its share";
+    }
+    if (shard == prev + 1 && !runs.empty()) runs.back().end = hi;
+    else runs.push_back(Run{lo, hi});
+    prev = shard;
+  }
+  size_t total = 0;
+  for (const Run& r : runs) total += static_cast<size_t>(r.end - r.begin);
+  if (req.push) {
+    CHECK(req.vals) << "push without values";
+    CHECK_EQ(req.vals_bytes, total * gsz)
+        << "pushed bytes do not match the keys' shares of tensor " << id << " ("
+        << total << " values of " << gsz << " bytes)";
+  }
+  if (req.pull && req.outs) {
+    CHECK_EQ(req.outs_bytes, total * osz) << "output size does not match the pulled values";
+  }
+  if (req.lens_out) { CHECK_EQ(req.lens_out_n, lens.size()); }
+
+  const bool in_dev = req.push && (m.sim ? true : m.rt.is_device_pointer(req.vals) != 0);
+  const bool out_dev = req.pull && req.outs && (m.sim ? true : m.rt.is_device_pointer(req.outs) != 0);
+  const bool host_in = req.push && !in_dev && !m.sim;
+  const bool host_out = req.pull && req.outs && !out_dev && !m.sim;
+  const bool staged = host_in || host_out;
+  int op = (req.push ? PSDEV_OP_PUSH : 0) | (req.pull ? PSDEV_OP_PULL : 0);
+  if (req.push && !req.pull && req.cmd == kCmdPublish) op |= PSDEV_OP_PUBLISH;
+
+  psdev_opt_t opt;
+  {
+    std::lock_guard<std::mutex> lk(m.mu);
+    if (req.push) ++d->step;
+    opt = d->opt;
+    if (opt.kind == PSDEV_OPT_ADAM) {
+      const double s = static_cast<double>(std::max<int64_t>(d->step, 1));
+      opt.bias1 = static_cast<float>(1.0 - std::pow(static_cast<double>(opt.beta1), s));
+      opt.bias2 = static_cast<float>(std::sqrt(1.0 - std::pow(static_cast<double>(opt.beta2), s)));
+    }
+  }
+  const int sync = 1 | (d->nvls ? 2 : 0);
+  // the kernel works on multiples of 8 values; the padding of the last shard belongs to it
+  auto pad8 = [&](int64_t e) { return e >= d->n_user ? t.n : e; };
+
+  Impl::Pending pend;
+  pend.channel = d->channel;
+  pend.timestamp = req.timestamp;
+  pend.responses = req.responses;
+  pend.customer = req.customer;
+  pend.on_done = req.on_done;
+  pend.lens_out = req.lens_out;
+  pend.tensor = d;
+  if (req.lens_out) pend.lens = lens;
+
+  void* prev_done = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(m.mu);
+    auto it = m.last_done.find(d);
+    if (it != m.last_done.end()) prev_done = it->second;
+  }
+  void* done = m.NewEvent();
+  const char* vals = static_cast<const char*>(req.vals);
+  char* outs = static_cast<char*>(req.outs);
+  char* grad = static_cast<char*>(d->grad);
+  char* weight = static_cast<char*>(d->weight);
+
+  if (!staged) {
+    // values already on the device: everything in order on one stream
+    void* s = tls_stream ? tls_stream : m.s_compute;
+    if (prev_done && !m.sim) m.rt.stream_wait_event(s, prev_done);
+    size_t eoff = 0;  // position in the request's value list, in elements
+    for (const Run& r : runs) {
+      const size_t cnt = static_cast<size_t>(r.end - r.begin);
+      if (req.push && vals + eoff * gsz != grad + r.begin * gsz) {
+        CHECK_EQ(m.rt.memcpy_async(grad + r.begin * gsz, vals + eoff * gsz, cnt * gsz, s), 0);
+      }
+      const int rc = m.rt.dense_op(&m.ws, &t, op, r.begin, pad8(r.end), &opt, d->channel,
+                                   d->num_ctas, m.opts.timeout_ns, sync, s);
+      CHECK_EQ(rc, 0) << "psdev_dense_op failed";
+      if (req.pull && outs && outs + eoff * osz != weight + r.begin * osz) {
+        CHECK_EQ(m.rt.memcpy_async(outs + eoff * osz, weight + r.begin * osz, cnt * osz, s), 0);
+      }
+      eoff += cnt;
+    }
+    m.rt.event_record(done, s);
+  } else {
+    // host-resident values: slices flow host -> device -> kernel -> host on three streams,
+    // so the copy of slice k+1 in, the kernel of slice k and the copy of slice k-1 out overlap
+    void* origin = tls_stream;  // work the caller has queued on its stream comes first
+    void* start = nullptr;
+    if (origin) {
+      start = m.NewEvent();
+      m.rt.event_record(start, origin);
+      pend.events_to_recycle.push_back(start);
+    }
+    for (void* s : {m.s_h2d, m.s_compute, m.s_d2h}) {
+      if (prev_done) m.rt.stream_wait_event(s, prev_done);
+      if (start) m.rt.stream_wait_event(s, start);
+    }
+    const int64_t step_g = std::max<int64_t>(8, static_cast<int64_t>(m.opts.slice_bytes / gsz) & ~int64_t(7));
+    size_t elem_off = 0;  // position in the request's value list
+    for (const Run& r : runs) {
+      for (int64_t b = r.begin; b < r.end; b += step_g) {
+        const int64_t e = std::min<int64_t>(b + step_g, r.end);
+        const size_t at = elem_off + static_cast<size_t>(b - r.begin);
+        const size_t cnt = static_cast<size_t>(e - b);
+        if (req.push) {
+          void* in_stream = host_in ? m.s_h2d : m.s_compute;
+          if (host_in || vals + at * gsz != grad + b * gsz) {
+            CHECK_EQ(m.rt.memcpy_async(grad + b * gsz, vals + at * gsz, cnt * gsz, in_stream), 0);
+          }
+          if (host_in) {
+            void* ev = m.NewEvent();
+            m.rt.event_record(ev, m.s_h2d);
+            m.rt.stream_wait_event(m.s_compute, ev);
+            pend.events_to_recycle.push_back(ev);
+          }
+        }
+        const int rc = m.rt.dense_op(&m.ws, &t, op, b, pad8(e), &opt, d->channel, d->num_ctas,
+                                     m.opts.timeout_ns, sync, m.s_compute);
+        CHECK_EQ(rc, 0) << "psdev_dense_op failed";
+        if (req.pull && outs) {
+          if (host_out) {
+            void* ev = m.NewEvent();
+            m.rt.event_record(ev, m.s_compute);
+            m.rt.stream_wait_event(m.s_d2h, ev);
+            pend.events_to_recycle.push_back(ev);
+            CHECK_EQ(m.rt.memcpy_async(outs + at * osz, weight + b * osz, cnt * osz, m.s_d2h), 0);
+          } else if (outs + at * osz != weight + b * osz) {
+            CHECK_EQ(m.rt.memcpy_async(outs + at * osz, weight + b * osz, cnt * osz, m.s_compute), 0);
+          }
+        }
+      }
+      elem_off += static_cast<size_t>(r.end - r.begin);
+    }
+    // the request is complete when the last kernel and the last copy out are
+    void* tail = m.NewEvent();
+    m.rt.event_record(tail, m.s_d2h);
+    m.rt.stream_wait_event(m.s_compute, tail);
+    pend.events_to_recycle.push_back(tail);
+    m.rt.event_record(done, m.s_compute);
+    if (origin) m.rt.stream_wait_event(origin, done);
+  }
+  pend.event = done;
+  {
+    std::lock_guard<std::mutex> lk(m.mu);
+    // `done` doubles as the ordering point for the next request on this tensor
+    m.last_done[d] = done;
+  }
+  {
+    std::lock_guard<std::mutex> lk(m.q_mu);
+    ++m.in_flight;
+    m.queue.push_back(std::move(pend));
+  }
+  m.q_cv.notify_one();
+}
+
+}  // namespace device
+}  // namespace ps

@@ -514,7 +514,8 @@ class TcpVan : public Van {
             if (c->fds.empty()) return false;
             const int fd = c->fds.front();
             c->fds.pop_front();
-            if (c->shm_ref.offset + len > c->shm_ref.seg_size) {
+            if (c->shm_ref.offset > c->shm_ref.seg_size ||
+                len > c->shm_ref.seg_size - c->shm_ref.offset) {
               ::close(fd);
               return false;
             }

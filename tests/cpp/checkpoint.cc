@@ -44,6 +44,13 @@ int main(int argc, char** argv) {
       keys[i] = kMaxKey / n * i + 5;
       for (int j = 0; j < k; ++j) vals[i * k + j] = static_cast<float>(i % 17 + j);
     }
+    // pulling the initial values before anything was pushed is a normal pattern: one zero per
+    // key comes back and the first wide push afterwards must find no narrow slot in its way
+    kv.Wait(kv.Pull(keys, &out));
+    CHECK_EQ(out.size(), static_cast<size_t>(n));
+    for (int i = 0; i < n; ++i) CHECK_EQ(out[i], 0.f);
+    out.clear();
+    Postoffice::Get()->Barrier(0, kWorkerGroup);
     kv.Wait(kv.Push(keys, vals));
     Postoffice::Get()->Barrier(0, kWorkerGroup);  // every worker's push is in
     if (MyRank() == 0) {

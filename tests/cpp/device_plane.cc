@@ -1,0 +1,165 @@
+// The device plane driven through the ordinary API: ps::Start, KVWorker push / pull /
+// push-pull with timestamps, callbacks and Wait, Finalize -- and nothing else (no collective
+// library).  Runs with the CPU stand-in of the plane (PlaneOptions::device = -1), in one
+// process under the loop van or as several joint processes, so the handle exchange over the
+// control plane, the key -> shard mapping, the routing in KVWorker and the completion through
+// the Customer tracker are checked where no GPU exists.  tests/cuda/device_plane_gpu.cu is the
+// same program on GPUs.
+// Reference behaviour checked: include/ps/kv_app.h:54-372 (timestamps, Wait, callback before
+// Wait returns, zero-copy Z* calls).
+#include <atomic>
+#include <cmath>
+#include <cstring>
+
+#include "ps/device/plane.h"
+#include "ps/ps.h"
+
+using namespace ps;
+using device::Plane;
+
+#ifndef PLANE_DEVICE
+#define PLANE_DEVICE -1
+#endif
+
+static psdev_opt_t Sgd(float lr) {
+  psdev_opt_t o{};
+  o.kind = PSDEV_OPT_SGD;
+  o.scale = 1.f;
+  o.lr = lr;
+  return o;
+}
+
+int main(int argc, char** argv) {
+  Start(0);
+  if (!IsWorker()) {  // scheduler (or a pure server): nothing to do on the device plane
+    Finalize(0, true);
+    return 0;
+  }
+  device::PlaneOptions po;
+  po.heap_bytes = 8u << 20;
+  po.device = PLANE_DEVICE < 0 ? -1 : MyRank();
+  po.timeout_ns = 3000000000ull;
+  Plane* plane = Plane::Get();
+  plane->Start(po);
+  const int W = plane->world(), R = plane->rank();
+  CHECK_EQ(W, NumWorkers());
+
+  // control-plane collectives
+  auto all = plane->AllGather("rank-" + std::to_string(R));
+  CHECK_EQ(all.size(), (size_t)W);
+  for (int r = 0; r < W; ++r) CHECK_EQ(all[r], "rank-" + std::to_string(r));
+
+  const int64_t n = 1000 + 8 * W + 3;  // not a multiple of anything convenient
+  const uint64_t kTensor = 7;
+  const device::DenseInfo& d =
+      plane->DeclareDense(0, kTensor, n, PSDEV_F32, PSDEV_F32, Sgd(0.5f));
+  const std::vector<Key> keys = plane->DenseKeys(kTensor);
+  CHECK_EQ(keys.size(), (size_t)W);
+  {
+    const auto& ranges = plane->KeyRanges();
+    for (int j = 0; j < W; ++j) CHECK_EQ(keys[j], ranges[j].begin() + kTensor);
+  }
+  KVWorker<float> kv(0, 0);
+
+  auto val_of = [](int rank, int64_t i) { return static_cast<float>((i % 13) - 6 + rank); };
+  std::vector<float> vals(n), expect(n, 0.f);
+  for (int64_t i = 0; i < n; ++i) vals[i] = val_of(R, i);
+  auto sum_of = [&](int64_t i) {
+    float s = 0.f;
+    for (int r = 0; r < W; ++r) s += val_of(r, i);
+    return s;
+  };
+
+  // 1. Push (copies), then Pull into empty vectors: sizes and per-key lengths come back
+  int last_ts = -1;
+  for (int rep = 0; rep < 3; ++rep) {
+    const int ts = kv.Push(keys, vals);
+    CHECK_GT(ts, last_ts);
+    last_ts = ts;
+    kv.Wait(ts);
+    for (int64_t i = 0; i < n; ++i) expect[i] -= 0.5f * sum_of(i);
+  }
+  std::vector<float> got;
+  std::vector<int> lens;
+  kv.Wait(kv.Pull(keys, &got, &lens));
+  CHECK_EQ(got.size(), (size_t)n);
+  CHECK_EQ(lens.size(), (size_t)W);
+  int64_t total = 0;
+  for (int j = 0; j < W; ++j) total += lens[j];
+  CHECK_EQ(total, n);
+  for (int64_t i = 0; i < n; ++i) CHECK_LT(std::fabs(got[i] - expect[i]), 1e-4f) << "at " << i;
+
+  // 2. ZPushPull with explicit lens and a callback that has run when Wait returns
+  std::atomic<int> called{0};
+  SArray<Key> skeys(keys);
+  SArray<float> svals(vals), souts(n, 0.f);
+  SArray<int> slens(lens);
+  kv.Wait(kv.ZPushPull(skeys, svals, &souts, &slens, 0, [&called]() { ++called; }));
+  CHECK_EQ(called.load(), 1);
+  for (int64_t i = 0; i < n; ++i) {
+    expect[i] -= 0.5f * sum_of(i);
+    CHECK_LT(std::fabs(souts[i] - expect[i]), 1e-4f) << "at " << i;
+  }
+
+  // 3. a subset of the keys touches only those shards' values
+  if (W > 1) {
+    const int j = W - 1;
+    const int64_t lo = j * d.share, hi = std::min<int64_t>(lo + d.share, n);
+    std::vector<float> part(vals.begin() + lo, vals.begin() + hi), part_out;
+    kv.Wait(kv.PushPull({keys[j]}, part, &part_out));
+    CHECK_EQ(part_out.size(), (size_t)(hi - lo));
+    for (int64_t i = lo; i < hi; ++i) {
+      expect[i] -= 0.5f * sum_of(i);
+      CHECK_LT(std::fabs(part_out[i - lo] - expect[i]), 1e-4f);
+    }
+    kv.Wait(kv.Pull(keys, &got));
+    for (int64_t i = 0; i < n; ++i) CHECK_LT(std::fabs(got[i] - expect[i]), 1e-4f) << "at " << i;
+  }
+
+  // 4. zero copy: values written straight into the tensor's gradient buffer in the arena and
+  // pulled straight into its weight buffer
+#if PLANE_DEVICE < 0
+  {
+    float* g = static_cast<float*>(d.grad);
+    for (int64_t i = 0; i < n; ++i) g[i] = 1.f;
+    SArray<float> dev_vals = SArray<float>::FromDevice(g, n);
+    SArray<float> dev_out = SArray<float>::FromDevice(static_cast<float*>(d.weight), n);
+    kv.Wait(kv.ZPushPull(skeys, dev_vals, &dev_out));
+    const float* w = static_cast<const float*>(d.weight);
+    for (int64_t i = 0; i < n; ++i) {
+      expect[i] -= 0.5f * W;
+      CHECK_LT(std::fabs(w[i] - expect[i]), 1e-4f);
+    }
+  }
+#endif
+
+  // 5. a peer that never issues the matching request: the wait runs out on the device side
+  // (a flag that nothing sets) and Wait reports it instead of hanging; afterwards the channel
+  // works again
+  if (W > 1) {
+    plane->Barrier();
+    if (R == 0) {
+      bool threw = false;
+      const int ts = kv.Push(keys, vals);
+      try {
+        kv.Wait(ts);
+      } catch (const Error& e) {
+        threw = strstr(e.what(), "did not arrive") != nullptr;
+      }
+      CHECK(threw) << "a request that no peer matched must fail, not hang or succeed";
+      plane->ClearStatus(0, kTensor);
+    }
+    plane->Barrier();
+    // rank 0's gradients of the failed round were applied nowhere
+    kv.Wait(kv.Push(keys, vals));
+    for (int64_t i = 0; i < n; ++i) expect[i] -= 0.5f * sum_of(i);
+    kv.Wait(kv.Pull(keys, &got));
+    for (int64_t i = 0; i < n; ++i) CHECK_LT(std::fabs(got[i] - expect[i]), 1e-4f) << "at " << i;
+  }
+
+  CHECK_GT(plane->launches(), (uint64_t)0);
+  LOG(INFO) << "DEVICE_PLANE_OK rank " << R << " of " << W << " backend " << plane->backend();
+  plane->Stop();
+  Finalize(0, true);
+  return 0;
+}

@@ -8,11 +8,17 @@ import os
 import subprocess
 import time
 
+import sys
+
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 BIN = os.path.join(ROOT, "build", "tests")
-REF_TESTS = os.path.join(os.environ.get("PS_REFERENCE_SRC", "/root/reference"), "tests")
+sys.path.insert(0, ROOT)
+from baseline import reference_source  # noqa: E402
+
+# the reference's own test programs: PS_REFERENCE_SRC, or the copy under baseline/_ref
+REF_TESTS = os.path.join(reference_source() or os.path.join(ROOT, "missing"), "tests")
 
 
 @pytest.fixture(scope="session")
@@ -94,12 +100,49 @@ def test_two_customers_in_one_worker_process(core_lib):
     assert rc == 0 and "CUSTOMER_OK 0" in out and "CUSTOMER_OK 1" in out, out[-3000:]
 
 
+def test_device_plane_single_process_loop_van(core_lib):
+    """Start -> Push/Pull/PushPull on a registered tensor -> Wait -> Finalize through KVWorker,
+    served by the device plane (CPU stand-in) in one process under the loop van."""
+    env = dict(os.environ, DMLC_PS_VAN_TYPE="loop")
+    r = subprocess.run([_prog("device_plane", core_lib)], capture_output=True, text=True,
+                       timeout=90, env=env)
+    assert r.returncode == 0 and "DEVICE_PLANE_OK rank 0 of 1" in r.stderr, r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("layout", [dict(num_joint=2), dict(num_joint=4),
+                                    dict(num_workers=3, num_servers=1),
+                                    dict(num_joint=2, env={"DMLC_LOCAL": "1"})],
+                         ids=["joint2", "joint4", "separate3", "joint2-ipc"])
+def test_device_plane_multi_process(core_lib, layout):
+    """The same program as several processes: arena handles travel over the control plane,
+    barriers are Postoffice barriers, requests complete the Customer tracker, and a request
+    that no peer matches fails with an error instead of hanging."""
+    n = layout.get("num_joint") or layout["num_workers"]
+    rc, out = _job([_prog("device_plane", core_lib)], **layout)
+    assert rc == 0 and out.count("DEVICE_PLANE_OK") == n, out[-3000:]
+
+
+def test_barrier_from_two_customers_of_two_processes(core_lib):
+    """Explicit Barrier calls from both customer threads of two worker processes, one thread
+    arriving late in one of them: every call passes exactly one round and nothing hangs."""
+    from ps_lite_b200.launch.local import LocalJob
+    job = LocalJob([_prog("multi_customer_barrier", core_lib)], num_workers=4, num_servers=1,
+                   capture=True)
+    job._spawn("scheduler", 0)
+    job._spawn("server", 0)
+    job._spawn("worker", 0)  # two processes, two customer threads each
+    job._spawn("worker", 1)
+    rc = job.wait(90)
+    out = job.output()
+    assert rc == 0 and out.count("BARRIER_ROUNDS_OK") == 2, out[-3000:]
+
+
 @pytest.mark.parametrize("std", ["c++11", "c++14"])
 def test_public_headers_compile_with_older_standards(std):
     """Programs written for the reference are built with -std=c++11 (its Makefile:21): the
     public headers must not need anything newer."""
-    for prog in ("kv_config1", "kv_features", "checkpoint"):
-        r = subprocess.run(["g++", f"-std={std}", "-O0", "-fsyntax-only", "-I",
+    for prog in ("kv_config1", "kv_features", "checkpoint", "helper_headers"):
+        r = subprocess.run(["g++", f"-std={std}", "-O0", "-pedantic-errors", "-fsyntax-only", "-I",
                             os.path.join(ROOT, "include"),
                             os.path.join(ROOT, "tests", "cpp", prog + ".cc")],
                            capture_output=True, text=True, timeout=300)
