@@ -26,6 +26,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 METRIC = "push_pull_goodput_GBps"
+T_START = time.time()
 
 
 def parse_args():
@@ -39,7 +40,11 @@ def parse_args():
     ap.add_argument("--dtype", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--ctas", type=int, default=0)
     ap.add_argument("--skip-e2e", action="store_true")
-    ap.add_argument("--slice-mb", type=float, default=32.0,
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the extra records (size sweep, sparse LR, model workloads)")
+    ap.add_argument("--extras-budget-s", type=float, default=240.0,
+                    help="the extra records stop being started once the run is this old")
+    ap.add_argument("--slice-mb", type=float, default=16.0,
                     help="slice size of the end-to-end staging pipeline (MiB)")
     ap.add_argument("--batch", type=int, default=0)
     ap.add_argument("--trainer", default="ps", choices=["ps", "ddp"],
@@ -48,68 +53,62 @@ def parse_args():
     return ap.parse_args()
 
 
-def _dist_init(args):
-    import torch
-    import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    return rank, world, local
-
-
 def run_pushpull(args):
     import torch
-    import torch.distributed as dist
 
-    import ps_lite_b200 as ps
-    from ps_lite_b200 import _lib, kvstore
+    from ps_lite_b200 import kvstore
+    from ps_lite_b200.launch import bootstrap
     from ps_lite_b200.parallel import ServerOptimizer
-    from ps_lite_b200.utils.timing import ClockSampler, max_over_ranks
+    from ps_lite_b200.utils.timing import ClockSampler
 
-    rank, world, local = _dist_init(args)
-    dev = torch.device("cuda", local)
     gdt = torch.float32 if args.dtype == "fp32" else torch.bfloat16
     isz = 4 if args.dtype == "fp32" else 2
+    world_hint = int(os.environ.get("WORLD_SIZE", os.environ.get("DMLC_NUM_WORKER", "1")))
     n = int(args.size_mb * (1 << 20)) // isz
-    n = max(8 * world, n // (8 * world) * (8 * world))
+    n = max(8 * world_hint, n // (8 * world_hint) * (8 * world_hint))
     nbytes = n * isz
-    ctx = kvstore.init(heap_bytes=2 * nbytes + (64 << 20), device=dev)
-    kv = kvstore.KVStore(ctx, slice_bytes=int(args.slice_mb * (1 << 20)))
+    # ps::Start from the launcher's environment, then the device plane: arena handles and
+    # barriers travel over the parameter server's own control plane (no collective library)
+    ctx = kvstore.init(heap_bytes=2 * nbytes + (64 << 20),
+                       slice_bytes=int(args.slice_mb * (1 << 20)))
+    rank, world, dev = ctx.rank, ctx.world, ctx.device
+    local = dev.index or 0
+    reporter = bootstrap.launcher_rank() == 0
+    kv = kvstore.KVStore(ctx)
     # sum over workers + SGD lr 0.01; contiguous key ranges, one per server
     opt = ServerOptimizer("sgd", lr=0.01, scale=1.0)
     table = kv.declare(0, n, grad_dtype=gdt, out_dtype=gdt, optimizer=opt, num_ctas=args.ctas)
     g = torch.Generator(device=dev)
     g.manual_seed(1234 + rank)
     table.grad.copy_(torch.randn(n, device=dev, generator=g).to(gdt))
-    lib = _lib.device_lib()
+    from ps_lite_b200 import host
+    L = host.lib()
 
-    # ---- device-timed: K fused push+pull rounds on resident gradients --------------------
+    # ---- device-timed: K fused push+pull rounds on resident gradients, each one a
+    # KVWorker::ZPushPull on the tensor's keys with values that already sit in the arena ------
     warmup = max(3, args.warmup)
     for _ in range(warmup):
-        table.push_pull()
+        kv.push_pull(0)
+    kv.wait_all()
     torch.cuda.synchronize()
     ctx.host_barrier()
     sampler = ClockSampler(local, period_ms=50)
-    if rank == 0:
+    if reporter:
         sampler.start()
         time.sleep(0.3)
     ctx.host_barrier()
     torch.cuda.synchronize()
-    launches0 = lib.psdev_launch_count()
+    launches0 = L.psnvl_launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        table.push_pull()
+        kv.push_pull(0)
     e1.record()
+    kv.wait_all()          # raises if a device-side wait ran out
     torch.cuda.synchronize()
-    launches = lib.psdev_launch_count() - launches0
+    launches = L.psnvl_launches() - launches0
     ctx.host_barrier()
-    ms = max_over_ranks(e0.elapsed_time(e1), dev)
-    table.check()
+    ms = ctx.max_over_ranks(e0.elapsed_time(e1))
     ms_per_step = ms / args.steps
     per_gpu = 2.0 * nbytes / (ms_per_step * 1e-3) / 1e9
     value = per_gpu * world
@@ -132,16 +131,22 @@ def run_pushpull(args):
         s1.record()
         torch.cuda.synchronize()
         ctx.host_barrier()
-        ms2 = max_over_ranks(s0.elapsed_time(s1), dev) / k2
+        ms2 = ctx.max_over_ranks(s0.elapsed_time(s1)) / k2
         e2e = {"value": round(world * 2.0 * nbytes / (ms2 * 1e-3) / 1e9, 3), "unit": "GB/s",
                "ms_per_step": round(ms2, 4), "steps": k2,
                "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
                "slice_mib": args.slice_mb,
-               "api": "KVStore.push_pull(pinned host tensor, out=pinned host tensor); wait(ts)"}
+               "api": "KVStore.push_pull(pinned host tensor, out=pinned host tensor); wait(ts) "
+                      "= KVWorker::ZPushPull + Wait through ps::Start and the device plane"}
     # the sampler ran through both timed regions (device-timed and end-to-end)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop() if reporter else None
 
-    if rank == 0:
+    extras = {}
+    if not args.no_extras:
+        from benchmarks import extras as extras_mod
+        extras = extras_mod.run(ctx, kv, args, time.time() - T_START)
+
+    if reporter:
         out = {
             "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 5),
@@ -154,13 +159,16 @@ def run_pushpull(args):
                        "parallelism": f"dp{world} workers x {world} key-range server shards",
                        "server_handle": "sum over workers + SGD lr=0.01 on fp32 master",
                        "per_gpu_goodput_GBps": round(per_gpu, 3),
+                       "value_is": "kernel goodput on device-resident gradients; e2e.value is "
+                                   "the same metric from pinned host memory and back",
+                       "control_plane": f"ps::Start ({ctx.launch_mode} launch), heap "
+                                        f"{ctx.heap.backend}, multicast {bool(ctx.heap.mc_base)}",
                        "l2": "inputs larger than L2 (gradient+weight+master per step > 126 MB)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
         }
+        out.update(extras)
         print(json.dumps(out), flush=True)
     kvstore.finalize()
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def run_reference(args):

@@ -37,13 +37,6 @@ def main():
         print(json.dumps({"impl": "nccl", "graph": True,
                           "unavailable": "NCCL collectives are not graph-captured here"}))
         return
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     dt = torch.float32 if args.dtype == "fp32" else torch.bfloat16
     isz = 4 if args.dtype == "fp32" else 2
     sizes = []
@@ -54,9 +47,25 @@ def main():
 
     from ps_lite_b200.utils.timing import max_over_ranks
     if args.impl == "ours":
+        # a parameter-server job: ps::Start + device plane, no collective library
         from ps_lite_b200 import kvstore
         from ps_lite_b200.parallel import ServerOptimizer
-        ctx = kvstore.init(heap_bytes=2 * sizes[-1] + (64 << 20), device=dev)
+        ctx = kvstore.init(heap_bytes=2 * sizes[-1] + (64 << 20))
+        rank, world, dev = ctx.rank, ctx.world, ctx.device
+    else:
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        rank = int(os.environ.get("RANK", "0"))
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if args.impl == "ours":
+            ctx.host_barrier()
+        elif world > 1:
+            dist.barrier()
 
     for nbytes in sizes:
         n = nbytes // isz
@@ -89,8 +98,7 @@ def main():
         for _ in range(args.warmup):
             step()
         torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
+        barrier()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if args.graph:
@@ -101,8 +109,7 @@ def main():
                     step()
             graph.replay()
             torch.cuda.synchronize()
-            if world > 1:
-                dist.barrier()
+            barrier()
             torch.cuda.synchronize()
             e0.record()
             graph.replay()
@@ -125,7 +132,7 @@ def main():
             ctx.heap.free(t.weight_off)
     if args.impl == "ours":
         kvstore.finalize()
-    if world > 1:
+    elif world > 1:
         dist.destroy_process_group()
 
 

@@ -1,4 +1,6 @@
-"""Pull fused with the consuming GEMM versus pull followed by the GEMM (run under torchrun).
+"""Pull fused with the consuming GEMM versus pull followed by the GEMM (run as a parameter-server job:
+``python -m ps_lite_b200.launch.local --joint N python benchmarks/pull_gemm_bench.py``, or under
+``torch.distributed.run``, whose environment is mapped onto such a job).
 
 Shape: the layer-0 QKV projection of BERT-large, X[16384,1024] * W[3072,1024]^T, W sharded
 block-cyclically over the ranks.  Each timed iteration is one server update of W and one use:
@@ -13,7 +15,6 @@ import os
 import sys
 
 import torch
-import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from ps_lite_b200 import kvstore  # noqa: E402
@@ -23,15 +24,9 @@ from ps_lite_b200.utils.timing import max_over_ranks  # noqa: E402
 
 
 def main():
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     M, N, K = (int(v) for v in os.environ.get("PULL_GEMM_SHAPE", "16384,3072,1024").split(","))
-    ctx = kvstore.init(heap_bytes=(64 << 20) + 8 * N * K, device=dev)
+    ctx = kvstore.init(heap_bytes=(64 << 20) + 8 * N * K)
+    rank, world, dev = ctx.rank, ctx.world, ctx.device
     t = DenseTable(ctx.heap, N * K, torch.bfloat16, torch.bfloat16, blk=4096,
                    optimizer=ServerOptimizer("sgd", lr=0.01), channel=ctx.new_channel())
     t.load_master(torch.randn(N * K, device=dev) * 0.02)
@@ -86,8 +81,6 @@ def main():
                           "w_bytes": N * K * 2,
                           "nvlink_bytes_in_per_gpu_pull": N * K * 2 * (world - 1) // world}), flush=True)
     kvstore.finalize()
-    if world > 1:
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

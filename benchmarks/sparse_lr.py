@@ -5,7 +5,7 @@ of the same keys.  Reports keys per second (whole job) and checks one step again
 PyTorch statement of FTRL.
 
     python benchmarks/sparse_lr.py                       # one GPU
-    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/sparse_lr.py
+    python -m ps_lite_b200.launch.local --joint 8 python benchmarks/sparse_lr.py   # 8 GPUs
     python benchmarks/sparse_lr.py --cpu-oracle [--workers 8]   # timed CPU baseline, no GPU needed
 """
 import argparse
@@ -13,8 +13,8 @@ import json
 import os
 import sys
 
+import numpy as np
 import torch
-import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from ps_lite_b200 import kvstore  # noqa: E402
@@ -84,16 +84,11 @@ def main():
     args = ap.parse_args()
     if args.cpu_oracle:
         return cpu_oracle(args)
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    world = int(os.environ.get("WORLD_SIZE", os.environ.get("DMLC_NUM_WORKER", "1")))
     key_space, n = 1 << args.log2_key_space, 1 << args.log2_keys
     per_rank = (key_space + world - 1) // world
-    ctx = kvstore.init(heap_bytes=4 * per_rank + 20 * n + (64 << 20), device=dev)
+    ctx = kvstore.init(heap_bytes=4 * per_rank + 20 * n + (64 << 20))
+    rank, world, dev = ctx.rank, ctx.world, ctx.device
     table = SparseTable(ctx.heap, key_space, n, kind="ftrl")
     gen = torch.Generator(device=dev)
     gen.manual_seed(1234 + rank)
@@ -102,11 +97,12 @@ def main():
 
     # correctness of one step on a fresh table (rank-local oracle needs every rank's request)
     keys0, g0 = batches[0]
-    all_k = [torch.empty_like(keys0) for _ in range(world)] if world > 1 else [keys0]
-    all_g = [torch.empty_like(g0) for _ in range(world)] if world > 1 else [g0]
-    if world > 1:
-        dist.all_gather(all_k, keys0)
-        dist.all_gather(all_g, g0)
+    all_k, all_g = [keys0], [g0]
+    if world > 1:  # every rank's first request, over the control plane
+        all_k = [torch.from_numpy(np.frombuffer(b, dtype=np.int64).copy()).to(dev)
+                 for b in ctx.allgather(keys0.cpu().numpy().tobytes())]
+        all_g = [torch.from_numpy(np.frombuffer(b, dtype=np.float32).copy()).to(dev)
+                 for b in ctx.allgather(g0.cpu().numpy().tobytes())]
     out = table.push_pull(keys0, g0).clone()
     torch.cuda.synchronize()
     cat_k, cat_g = torch.cat(all_k), torch.cat(all_g)
@@ -137,8 +133,6 @@ def main():
                           "timing": "device, CUDA events, max over ranks; includes staging the "
                                     "request into the heap, push, FTRL, pull"}), flush=True)
     kvstore.finalize()
-    if world > 1:
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -10,13 +10,15 @@ import torch.nn.functional as F
 
 
 def _setup(args):
-    import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
+    """Rank, world and device as the launcher gives them; only the library baseline (DDP over
+    NCCL) starts ``torch.distributed``."""
+    world = int(os.environ.get("WORLD_SIZE", os.environ.get("DMLC_NUM_WORKER", "1")))
     rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", os.environ.get("PSB200_LOCAL_INDEX", "0")))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    if world > 1:
+    if world > 1 and getattr(args, "trainer", "ps") == "ddp":
+        import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     return rank, world, dev
 
@@ -59,6 +61,7 @@ def run(args):
     if getattr(args, "trainer", "ps") == "ddp":
         return _run_ddp(args, model, fwd, make, rank, world, dev, metric, unit, per_step, nparam)
     ctx = kvstore.init(heap_bytes=nparam * 8 + (256 << 20), device=dev)
+    rank, world = ctx.rank, ctx.world
     fused = args.workload == "bert"
     dopt = DistributedOptimizer(model.parameters(), ctx.heap, sopt, grad_dtype=torch.bfloat16,
                                 num_ctas=args.ctas or 32,
@@ -115,9 +118,6 @@ def run(args):
             "loss_first_last": [losses[0], losses[-1]], "clocks": clocks,
             "gpu_launches": int(lib.psdev_launch_count() - l0)}), flush=True)
     kvstore.finalize()
-    if world > 1:
-        import torch.distributed as dist
-        dist.destroy_process_group()
 
 
 def _run_ddp(args, model, fwd, make, rank, world, dev, metric, unit, per_step, nparam):

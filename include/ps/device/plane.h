@@ -128,9 +128,14 @@ class Plane : public DeviceRoute {
   void ClearStatus(int app_id, uint64_t tensor_id);
   int NewChannel();
 
-  // Stream on which requests of the calling thread with device-resident values are ordered
-  // (nullptr: the plane's own compute stream).  Thread local.
+  // Stream on which requests of the calling thread are ordered: a request with device-resident
+  // values runs on it; a staged request starts after what the stream holds and the stream
+  // waits for its end.  A null handle names the legacy default stream.  Without a call (or
+  // after ClearStream) requests run on the plane's own streams.  Thread local.
   void SetStream(void* stream);
+  void ClearStream();
+  // Staging granularity for host-resident values of later requests (multiple of 64 bytes).
+  void SetSliceBytes(size_t bytes);
 
   // ---- DeviceRoute ---------------------------------------------------------------------------
   bool Claims(int app_id, const SArray<Key>& keys) override;

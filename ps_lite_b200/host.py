@@ -81,6 +81,32 @@ def lib() -> C.CDLL:
             L.ps_capi_encode_meta.restype = C.c_long
             L.ps_capi_encode_meta.argtypes = [C.POINTER(MetaStruct), C.c_char_p, sz]
             L.ps_capi_decode_meta.argtypes = [C.c_char_p, sz, C.POINTER(MetaStruct)]
+            # device plane (src/capi/ps_nvl_c_api.h)
+            from ._lib import Opt, Table, World
+            u64, i64 = C.c_uint64, C.c_int64
+            L.psnvl_start.argtypes = [u64, i, C.c_char_p, i, C.c_char_p, u64, u64]
+            L.psnvl_backend.restype = C.c_char_p
+            L.psnvl_world_struct.argtypes = [C.POINTER(World)]
+            L.psnvl_allgather.restype = C.c_long
+            L.psnvl_allgather.argtypes = [C.c_char_p, sz, C.c_char_p, sz, C.POINTER(sz)]
+            L.psnvl_alloc.restype = i64
+            L.psnvl_alloc.argtypes = [u64, u64]
+            L.psnvl_free.argtypes = [i64]
+            L.psnvl_heap_in_use.restype = u64
+            L.psnvl_register_dense.argtypes = [i, u64, i64, C.POINTER(Table), C.POINTER(Opt), i,
+                                               i, i]
+            L.psnvl_unregister_dense.argtypes = [i, u64]
+            L.psnvl_set_optimizer.argtypes = [i, u64, C.POINTER(Opt)]
+            L.psnvl_dense_keys.argtypes = [u64, u64p]
+            L.psnvl_set_stream.argtypes = [vp]
+            L.psnvl_set_slice_bytes.argtypes = [u64]
+            L.psnvl_clear_status.argtypes = [i, u64]
+            L.psnvl_launches.restype = u64
+            L.ps_capi_bworker_new.restype = vp
+            L.ps_capi_bworker_new.argtypes = [i, i]
+            L.ps_capi_bworker_delete.argtypes = [vp]
+            L.ps_capi_bworker_request.argtypes = [vp, i, i, u64p, sz, vp, sz, vp, sz, i, i]
+            L.ps_capi_bworker_wait.argtypes = [vp, i]
             _lib = L
         return _lib
 
@@ -99,12 +125,24 @@ def setenv(key: str, value) -> None:
     _ck(lib().ps_capi_setenv(key.encode(), str(value).encode()))
 
 
+_started = False
+
+
 def start(customer_id: int = 0, barrier: bool = True) -> None:
+    global _started
     _ck(lib().ps_capi_start(customer_id, int(barrier)))
+    _started = True
 
 
 def finalize(customer_id: int = 0, barrier: bool = True) -> None:
+    global _started
     _ck(lib().ps_capi_finalize(customer_id, int(barrier)))
+    if customer_id == 0:
+        _started = False
+
+
+def started() -> bool:
+    return _started
 
 
 def barrier(group: int = ALL, customer_id: int = 0) -> None:

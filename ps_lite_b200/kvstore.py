@@ -1,11 +1,18 @@
-"""Thin PyTorch binding: push / pull of torch tensors.
+"""Thin PyTorch binding: push / pull of torch tensors through the parameter server.
 
-The calls mirror ``KVWorker`` of the reference (include/ps/kv_app.h:54-372): ``push``,
-``pull`` and ``push_pull`` return an integer timestamp at once, ``wait(ts)`` blocks until
-that request has completed (``KVWorker::Wait``, :233), and the server-side update is
+``init`` is ``ps::Start`` for a GPU job: it starts the host runtime from the ``DMLC_*``
+environment (set by this package's launchers, derived from a ``torch.distributed.run`` launch,
+or a single process on the loop van), then starts the device plane (``Plane::Start``,
+include/ps/device/plane.h): arena handles travel over the control plane, barriers are
+``Postoffice::Barrier``; no collective library and no ``torch.distributed`` call is involved.
+
+:class:`KVStore` mirrors ``KVWorker`` of the reference (include/ps/kv_app.h:54-372):
+``push``, ``pull`` and ``push_pull`` return an integer timestamp at once, ``wait(ts)`` blocks
+until that request has completed (``KVWorker::Wait``, :233), and the server-side update is
 selected per key when the key is declared (the role of ``KVServer::set_request_handle``,
-:414-420).  Here a request is a kernel on a CUDA stream instead of messages to server
-processes, and completion is a CUDA event plus a device status word.
+:414-420).  The calls ARE ``KVWorker`` calls: a declared tensor is registered with the device
+plane under its key, and a request on it leaves ``KVWorker::ZPush/ZPull/ZPushPull`` as copies
+and kernels on CUDA streams whose completion credits the worker's request tracker.
 
 Tensors may live on the device or in (pinned) host memory.  Host tensors are streamed
 through the device in slices: host-to-device copy, fused push/pull kernel and
@@ -13,63 +20,122 @@ device-to-host copy of consecutive slices overlap on three streams.
 """
 from __future__ import annotations
 
+import ctypes as C
 import os
 from typing import Dict, Optional
 
+import numpy as np
 import torch
 
-from . import _lib
+from . import _lib, host
 from .parallel.dense import DenseTable, ServerOptimizer
 from .parallel.heap import SymmetricHeap
 
+APP_ID = 0
+
 
 class Context:
-    """Per-process state: rank, device, symmetric heap."""
+    """Per-process state: node rank, device, symmetric heap."""
 
     def __init__(self, heap_bytes: int = 1 << 30, device: Optional[torch.device] = None,
-                 group=None):
-        import torch.distributed as dist
-        self.group = group
-        if dist.is_available() and dist.is_initialized():
-            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
-        else:
-            self.rank, self.world = 0, 1
+                 backend: str = "auto", multicast: int = -1, slice_bytes: int = 0,
+                 timeout_s: Optional[float] = None):
+        from .launch import bootstrap
+        self.launch_mode = bootstrap.ensure_env()
+        self._own_start = not host.started()
+        if self._own_start:
+            host.start()
+        if host.is_scheduler() and not host.is_worker():
+            # a program run by every role, like the reference's tests: the scheduler has
+            # nothing to do on the device plane
+            host.finalize()
+            raise SystemExit(0)
         if device is None:
-            device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+            device = torch.device("cuda", int(os.environ.get("LOCAL_RANK",
+                                  os.environ.get("PSB200_LOCAL_INDEX", "0"))) %
+                                  max(1, torch.cuda.device_count()))
         self.device = torch.device(device)
         torch.cuda.set_device(self.device)
         # host staging buffers and copy threads next to the GPU (matters with several GPUs
         # per host: a pinned buffer on the far socket crosses the inter-socket link)
         from .utils.affinity import bind_to_gpu_cpus
         self.cpus = bind_to_gpu_cpus(self.device.index or 0)
-        self.heap = SymmetricHeap(heap_bytes, self.rank, self.world, group=group,
-                                  device=self.device)
-        self._next_channel = 0
-        if self.world > 1:
-            dist.barrier(group=group)
+        from . import _build
+        dev_lib = _lib.device_lib()   # builds if needed; the plane binds the same file
+        del dev_lib
+        checks = os.environ.get("PSB200_DEVICE_CHECKS") == "1"
+        path = _build.LIB_DIR / ("libpsb200_device_checks.so" if checks else "libpsb200_device.so")
+        if timeout_s is None:
+            from .parallel.dense import default_timeout_s
+            timeout_s = default_timeout_s()
+        L = host.lib()
+        host._ck(L.psnvl_start(int(heap_bytes), int(self.device.index or 0), backend.encode(),
+                               int(multicast), str(path).encode(), int(slice_bytes),
+                               int(timeout_s * 1e9)))
+        self.rank, self.world = int(L.psnvl_rank()), int(L.psnvl_world())
+        self.heap = SymmetricHeap(heap_bytes, device=self.device, backend="plane")
+        self.worker = L.ps_capi_bworker_new(APP_ID, 0)
+        if not self.worker:
+            raise host.PSError(L.ps_capi_last_error().decode())
 
     def new_channel(self) -> int:
-        c = self._next_channel
-        self._next_channel = (c + 1) % (_lib.NUM_CHANNELS - 1)  # last channel: barriers
-        return c
+        """A rendezvous channel for one more tensor; raises when all are taken."""
+        return host._ck(host.lib().psnvl_new_channel())
 
     def host_barrier(self) -> None:
-        if self.world > 1:
-            import torch.distributed as dist
-            dist.barrier(group=self.group)
+        """``Postoffice::Barrier`` over the workers."""
+        host._ck(host.lib().psnvl_barrier())
+
+    def allgather(self, payload: bytes) -> list:
+        """Byte strings of all workers in rank order, over the control plane."""
+        L = host.lib()
+        sizes = (C.c_size_t * self.world)()
+        cap = max(4096, (len(payload) + 64) * self.world * 2)
+        for _ in range(2):
+            buf = C.create_string_buffer(cap)
+            total = L.psnvl_allgather(payload, len(payload), buf, cap, sizes)
+            if total < 0:
+                raise host.PSError(L.ps_capi_last_error().decode())
+            if total <= cap:
+                out, at = [], 0
+                for r in range(self.world):
+                    out.append(buf.raw[at:at + sizes[r]])
+                    at += sizes[r]
+                return out
+            # cannot repeat a collective with a larger buffer: contributions are of one size
+            raise ValueError("all-gather contributions differ too much in size")
+        return []
+
+    def max_over_ranks(self, value: float) -> float:
+        import struct
+        if self.world == 1:
+            return float(value)
+        return max(struct.unpack("<d", b)[0] for b in self.allgather(struct.pack("<d", value)))
 
     def close(self) -> None:
+        L = host.lib()
+        if self.worker:
+            L.ps_capi_bworker_delete(self.worker)
+            self.worker = None
         self.heap.close()
+        torch.cuda.synchronize(self.device)
+        host._ck(L.psnvl_stop())
+        if self._own_start:
+            host.finalize()
 
 
 _ctx: Optional[Context] = None
 
 
-def init(heap_bytes: int = 1 << 30, device=None, group=None) -> Context:
-    """Create the process-wide context (``ps::Start`` for the device plane)."""
+def init(heap_bytes: int = 1 << 30, device=None, **kw) -> Context:
+    """Create the process-wide context (``ps::Start`` plus the device plane)."""
     global _ctx
     if _ctx is None:
-        _ctx = Context(heap_bytes, device, group)
+        _ctx = Context(heap_bytes, device, **kw)
+    return _ctx
+
+
+def context() -> Optional[Context]:
     return _ctx
 
 
@@ -77,7 +143,6 @@ def finalize() -> None:
     """Release the context (``ps::Finalize``)."""
     global _ctx
     if _ctx is not None:
-        _ctx.host_barrier()
         _ctx.close()
         _ctx = None
 
@@ -85,112 +150,113 @@ def finalize() -> None:
 class KVStore:
     """Dense key-value store over the device data plane."""
 
-    def __init__(self, ctx: Optional[Context] = None, slice_bytes: int = 32 << 20):
+    def __init__(self, ctx: Optional[Context] = None, slice_bytes: int = 0):
         self.ctx = ctx or init()
         self.tables: Dict[int, DenseTable] = {}
-        self._events: Dict[int, tuple] = {}
-        self._ts = 0
-        self.slice_bytes = int(slice_bytes)
-        dev = self.ctx.device
-        self._h2d = torch.cuda.Stream(dev)
-        self._d2h = torch.cuda.Stream(dev)
-        self._compute = torch.cuda.Stream(dev)
+        self._keys: Dict[int, np.ndarray] = {}
+        self._alive: Dict[int, tuple] = {}
+        if slice_bytes:
+            host._ck(host.lib().psnvl_set_slice_bytes(int(slice_bytes)))
 
     # -- declaration -----------------------------------------------------------------------
     def declare(self, key: int, numel: int, *, grad_dtype=torch.float32,
                 out_dtype=torch.float32, optimizer: Optional[ServerOptimizer] = None,
                 blk: Optional[int] = None, init: Optional[torch.Tensor] = None,
                 num_ctas: int = 0) -> DenseTable:
-        """Register a dense key of ``numel`` values; same call order on every rank."""
+        """Register tensor ``key`` of ``numel`` values; same call order on every rank.
+
+        ``key`` is the tensor's id inside every device shard's key range: the tensor is
+        addressed by the W keys ``range_j.begin + key`` (:meth:`keys_of`), key j naming the
+        j-th of W contiguous pieces.  ``blk`` chooses which rank serves which values: the
+        default gives rank j exactly piece j (the reference's contiguous server ranges,
+        src/postoffice.cc:169-180); a smaller ``blk`` spreads blocks round-robin."""
         if key in self.tables:
             raise KeyError(f"key {key} already declared")
         t = DenseTable(self.ctx.heap, numel, grad_dtype, out_dtype, blk=blk,
                        optimizer=optimizer, channel=self.ctx.new_channel(), num_ctas=num_ctas)
         if init is not None:
             t.load_master(init)
+        L = host.lib()
+        o = t.optimizer.to_struct(1)
+        host._ck(L.psnvl_register_dense(APP_ID, int(key), int(numel), C.byref(t._table),
+                                        C.byref(o), t.channel, int(t.nvls), t.num_ctas))
+        keys = np.zeros(self.ctx.world, dtype=np.uint64)
+        host._ck(L.psnvl_dense_keys(int(key), keys.ctypes.data_as(C.POINTER(C.c_uint64))))
         self.tables[key] = t
+        self._keys[key] = keys
         return t
 
-    # -- requests ----------------------------------------------------------------------------
-    def _new_ts(self, event: torch.cuda.Event, table: DenseTable) -> int:
-        self._ts += 1
-        self._events[self._ts] = (event, table)
-        return self._ts
+    def keys_of(self, key: int) -> np.ndarray:
+        """The uint64 keys of tensor ``key``, one per device shard."""
+        return self._keys[key].copy()
 
-    def _slices(self, t: DenseTable, itemsize: int):
-        step = max(8, (self.slice_bytes // itemsize) & ~7)
-        return [(b, min(b + step, t.n)) for b in range(0, t.n, step)]
-
-    def _request(self, key: int, op: int, value: Optional[torch.Tensor],
-                 out: Optional[torch.Tensor]) -> int:
+    def set_optimizer(self, key: int, optimizer: ServerOptimizer) -> None:
+        """Replace the hyper-parameters of the server handle of ``key`` (e.g. a new rate)."""
         t = self.tables[key]
-        cur = torch.cuda.current_stream(self.ctx.device)
-        host_in = value is not None and not value.is_cuda
-        host_out = out is not None and not out.is_cuda
-        if not host_in and not host_out:
-            # device path: one kernel on the caller's stream
-            if value is not None and value.data_ptr() != t.grad.data_ptr():
-                t.grad[: value.numel()].copy_(value.reshape(-1), non_blocking=True)
-            t._run(op, 0, None, True, cur, None, True)
-            if out is not None and out.data_ptr() != t.weight.data_ptr():
-                out.reshape(-1).copy_(t.weight[: out.numel()], non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record(cur)
-            return self._new_ts(ev, t)
-        # host path: slice pipeline over three streams
-        isz = t.grad.element_size() if op & _lib.OP_PUSH else t.weight.element_size()
-        for s in (self._h2d, self._compute, self._d2h):
-            s.wait_stream(cur)
-        vflat = value.reshape(-1) if value is not None else None
-        oflat = out.reshape(-1) if out is not None else None
-        first = True
-        for b, e in self._slices(t, isz):
-            if vflat is not None:
-                hi = min(e, vflat.numel())
-                if host_in:
-                    with torch.cuda.stream(self._h2d):
-                        if hi > b:
-                            t.grad[b:hi].copy_(vflat[b:hi], non_blocking=True)
-                    self._compute.wait_stream(self._h2d)
-                elif hi > b:
-                    with torch.cuda.stream(self._compute):
-                        t.grad[b:hi].copy_(vflat[b:hi], non_blocking=True)
-            t._run(op, b, e, True, self._compute, None, first)
-            first = False
-            if oflat is not None:
-                hi = min(e, oflat.numel())
-                if hi > b:
-                    if host_out:
-                        self._d2h.wait_stream(self._compute)
-                        with torch.cuda.stream(self._d2h):
-                            oflat[b:hi].copy_(t.weight[b:hi], non_blocking=True)
-                    else:
-                        with torch.cuda.stream(self._compute):
-                            oflat[b:hi].copy_(t.weight[b:hi], non_blocking=True)
-        ev = torch.cuda.Event()
-        self._compute.wait_stream(self._d2h)
-        ev.record(self._compute)
-        cur.wait_stream(self._compute)
-        return self._new_ts(ev, t)
+        t.optimizer = optimizer
+        o = optimizer.to_struct(1)
+        host._ck(host.lib().psnvl_set_optimizer(APP_ID, int(key), C.byref(o)))
 
-    def push(self, key: int, value: torch.Tensor) -> int:
-        """``ZPush``: contribute ``value`` (this worker's gradient) to ``key``."""
-        return self._request(key, _lib.OP_PUSH, value, None)
+    # -- requests ----------------------------------------------------------------------------
+    def _request(self, key: int, push: bool, pull: bool, value: Optional[torch.Tensor],
+                 out: Optional[torch.Tensor], cmd: int = 0, priority: int = 0) -> int:
+        t = self.tables[key]
+        L = host.lib()
+        keys = self._keys[key]
+        cur = torch.cuda.current_stream(self.ctx.device)
+        L.psnvl_set_stream(cur.cuda_stream)
+        vptr = vbytes = optr = obytes = 0
+        if push:
+            if value is None:
+                value = t.grad[: t.n_user]
+            if not value.is_contiguous() or value.numel() != t.n_user or value.dtype != t.grad_dtype:
+                raise ValueError("pushed values must be a contiguous tensor of the declared "
+                                 "length and gradient dtype")
+            vptr, vbytes = value.data_ptr(), value.numel() * value.element_size()
+        if pull:
+            if out is None:
+                out = t.weight[: t.n_user]
+            if not out.is_contiguous() or out.numel() != t.n_user or out.dtype != t.out_dtype:
+                raise ValueError("the output must be a contiguous tensor of the declared "
+                                 "length and weight dtype")
+            optr, obytes = out.data_ptr(), out.numel() * out.element_size()
+        ts = L.ps_capi_bworker_request(self.ctx.worker, int(push), int(pull),
+                                       keys.ctypes.data_as(C.POINTER(C.c_uint64)), keys.size,
+                                       vptr, vbytes, optr, obytes, int(cmd), int(priority))
+        if ts < 0:
+            raise host.PSError(L.ps_capi_last_error().decode())
+        self._alive[ts] = (value, out, t)   # zero-copy: kept until the request completed
+        return ts
+
+    def push(self, key: int, value: Optional[torch.Tensor] = None, publish: bool = False) -> int:
+        """``ZPush``: contribute ``value`` (this worker's gradient; default: the tensor's own
+        gradient buffer) to ``key``.  ``publish``: owners also leave the new values in their
+        own weight buffer, for a pull fused into a GEMM."""
+        return self._request(key, True, False, value, None, cmd=0x5055424c if publish else 0)
 
     def pull(self, key: int, out: Optional[torch.Tensor] = None) -> int:
         """``ZPull``: fetch the current value of ``key`` into ``out`` (or ``table.weight``)."""
-        return self._request(key, _lib.OP_PULL, None, out)
+        return self._request(key, False, True, None, out)
 
-    def push_pull(self, key: int, value: torch.Tensor, out: Optional[torch.Tensor] = None) -> int:
+    def push_pull(self, key: int, value: Optional[torch.Tensor] = None,
+                  out: Optional[torch.Tensor] = None) -> int:
         """``ZPushPull``: both, in one fused pass per slice."""
-        return self._request(key, _lib.OP_PUSHPULL, value, out)
+        return self._request(key, True, True, value, out)
 
     def wait(self, ts: int) -> None:
         """Block until request ``ts`` completed; raises if a device wait ran out."""
-        ev, table = self._events.pop(ts)
-        ev.synchronize()
-        table.check()
+        L = host.lib()
+        try:
+            if L.ps_capi_bworker_wait(self.ctx.worker, int(ts)) < 0:
+                raise host.PSError(L.ps_capi_last_error().decode())
+        finally:
+            self._alive.pop(ts, None)
 
     def wait_all(self) -> None:
-        for ts in sorted(self._events):
+        for ts in sorted(self._alive):
             self.wait(ts)
+
+    def clear_error(self, key: int) -> None:
+        """After a request on ``key`` failed because a peer did not arrive: make the tensor
+        usable again."""
+        host._ck(host.lib().psnvl_clear_status(APP_ID, int(key)))

@@ -7,9 +7,12 @@ copy of a tensor as ``peer_base[p] + offset``.
 
 This is the device counterpart of the reference's registered memory pool and address
 exchange for RDMA (src/ibverbs_van.h:86-214 ``SimpleMempool``; :632-724 rendezvous).
-Handles travel through ``torch.distributed`` (any backend) when a process group is
-given, or through a caller-supplied ``exchange`` callable (for example the control plane
-of the host runtime).
+A job's heap normally comes from the device plane of the host runtime (backend ``"plane"``,
+src/van/nvl_van.cc): the arenas were created, exchanged over the control plane and mapped by
+``Plane::Start``, and this object is a view of them.  The other backends build a heap
+without a job: one rank (tests, single-GPU use), ranks emulated on one GPU, or ranks of a
+``torch.distributed`` group whose handles travel through that group or through a
+caller-supplied ``exchange`` callable.
 """
 from __future__ import annotations
 
@@ -58,6 +61,10 @@ class SymmetricHeap:
         self.mc_base = 0        # NVSwitch multicast alias of the arena (0: none)
         self._symm = None       # torch symmetric-memory tensor and handle, when used
         self.backend = "ipc"
+        self._plane = False
+        if backend == "plane":
+            self._init_plane()
+            return
         if _bases is not None:  # view created by `emulated`
             self.bases = list(_bases)
             self._base = self.bases[self.rank]
@@ -99,6 +106,24 @@ class SymmetricHeap:
                     _lib.check(self.lib.psdev_heap_open(h, C.byref(ptr)), f"psdev_heap_open({p})")
                     self.bases[p] = ptr.value
                     self._opened.append(ptr.value)
+
+    def _init_plane(self) -> None:
+        """View of the arenas that the host runtime's device plane has set up."""
+        from .. import host
+        L = host.lib()
+        if not L.psnvl_started():
+            raise RuntimeError("the device plane is not started (kvstore.init does that)")
+        ws = _lib.World()
+        L.psnvl_world_struct(C.byref(ws))
+        self.lib.psdev_suballoc_delete(self._sub)
+        self._sub = None
+        self._plane, self._owner = True, False
+        self.rank, self.world = int(ws.rank), int(ws.world)
+        self.bases = [int(ws.peer_base[p] or 0) for p in range(self.world)]
+        self._base = self.bases[self.rank]
+        self.mc_base = int(ws.mc_base or 0)
+        self.nbytes = int(ws.heap_bytes)
+        self.backend = L.psnvl_backend().decode()
 
     def _init_vmm(self, group, exchange) -> None:
         """Arena from the virtual-memory-management API (src/device/vmm_heap.cu): the physical
@@ -188,16 +213,29 @@ class SymmetricHeap:
 
     # -- allocation ------------------------------------------------------------------------
     def alloc(self, nbytes: int, align: int = 256) -> int:
+        if self._plane:
+            from .. import host
+            off = host.lib().psnvl_alloc(int(nbytes), int(align))
+            if off < 0:
+                raise _lib.PsdevError(-5, f"symmetric heap alloc of {nbytes} bytes")
+            return int(off)
         off = self.lib.psdev_suballoc_alloc(self._sub, int(nbytes), int(align))
         if off < 0:
             raise _lib.PsdevError(int(off), f"symmetric heap alloc of {nbytes} bytes")
         return int(off)
 
     def free(self, offset: int) -> None:
+        if self._plane:
+            from .. import host
+            host._ck(host.lib().psnvl_free(int(offset)))
+            return
         _lib.check(self.lib.psdev_suballoc_free(self._sub, int(offset)), "suballoc_free")
 
     @property
     def in_use(self) -> int:
+        if self._plane:
+            from .. import host
+            return int(host.lib().psnvl_heap_in_use())
         return int(self.lib.psdev_suballoc_in_use(self._sub))
 
     def tensor(self, offset: int, numel: int, dtype: torch.dtype, rank: Optional[int] = None
@@ -244,6 +282,35 @@ class SymmetricHeap:
         w = self.world_struct()
         _lib.check(self.lib.psdev_device_barrier(C.byref(w), channel, int(timeout_s * 1e9),
                                                  s.cuda_stream), "device_barrier")
+
+    def broadcast(self, t: torch.Tensor, src: int = 0, chunk_bytes: int = 64 << 20) -> None:
+        """Overwrite ``t`` (contiguous, on this heap's device) on every rank with rank
+        ``src``'s values, moved through a scratch buffer of the heap: ``src`` copies a chunk
+        into its arena, a device barrier, the others read it from the peer arena with the
+        library's 16-byte copy kernel, another barrier.  Collective."""
+        if self.world == 1:
+            return
+        flat = t.reshape(-1).view(torch.uint8)
+        chunk = min((flat.numel() + 255) & ~255, int(chunk_bytes))
+        off = self.alloc(chunk)
+        mine = self.tensor(off, chunk, torch.uint8)
+        s = torch.cuda.current_stream(self.device)
+        try:
+            for b in range(0, flat.numel(), chunk):
+                e = min(b + chunk, flat.numel())
+                if self.rank == src:
+                    mine[: e - b].copy_(flat[b:e])
+                self.barrier()
+                if self.rank != src:
+                    n16 = (e - b + 15) & ~15
+                    tmp = torch.empty(n16, dtype=torch.uint8, device=self.device)
+                    _lib.check(self.lib.psdev_link_copy(tmp.data_ptr(), self.bases[src] + off,
+                                                        n16, 0, s.cuda_stream), "link_copy")
+                    flat[b:e].copy_(tmp[: e - b])
+                self.barrier()
+            torch.cuda.synchronize(self.device)
+        finally:
+            self.free(off)
 
     def close(self) -> None:
         if self._sub:

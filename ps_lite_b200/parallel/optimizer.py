@@ -98,9 +98,7 @@ class DistributedOptimizer:
         full = torch.zeros(self.total, dtype=torch.float32, device=heap.device)
         for p, o in zip(self.params, self.offsets):
             full[o:o + p.numel()] = p.detach().reshape(-1).float()
-        if heap.world > 1:
-            import torch.distributed as dist
-            dist.broadcast(full, 0)
+        heap.broadcast(full, 0)
         self.table.load_master(full)
         self.table.pull()
         torch.cuda.synchronize(heap.device)

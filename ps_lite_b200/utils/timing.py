@@ -76,7 +76,14 @@ def flush_l2(device) -> None:
     _flush_buf.zero_()
 
 
-def max_over_ranks(value: float, device) -> float:
+def max_over_ranks(value: float, device=None) -> float:
+    """Maximum of ``value`` over the workers of the job (gathered over the control plane of
+    the parameter server, or over ``torch.distributed`` in the baseline programs that use
+    that instead)."""
+    from .. import kvstore
+    ctx = kvstore.context()
+    if ctx is not None:
+        return ctx.max_over_ranks(value)
     import torch.distributed as dist
     if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
         t = torch.tensor([value], dtype=torch.float64, device=device)

@@ -121,6 +121,18 @@ int psnvl_set_stream(void* stream) {
   Plane::Get()->SetStream(stream);
   return 0;
 }
+int psnvl_set_slice_bytes(uint64_t bytes) {
+  return Guard([&] {
+    Plane::Get()->SetSliceBytes(bytes);
+    return 0;
+  });
+}
+int psnvl_clear_status(int app_id, uint64_t tensor_id) {
+  return Guard([&] {
+    Plane::Get()->ClearStatus(app_id, tensor_id);
+    return 0;
+  });
+}
 uint64_t psnvl_launches(void) { return Plane::Get()->launches(); }
 
 // ---- byte worker ----

@@ -44,8 +44,12 @@ int psnvl_unregister_dense(int app_id, uint64_t tensor_id);
 int psnvl_set_optimizer(int app_id, uint64_t tensor_id, const psdev_opt_t* opt);
 /* The W keys of a tensor (one per device shard), written to keys[0..world). */
 int psnvl_dense_keys(uint64_t tensor_id, uint64_t* keys);
-/* Stream of the calling thread's device-resident requests (NULL: the plane's own). */
+/* Stream that orders the calling thread's requests (NULL names the legacy default stream). */
 int psnvl_set_stream(void* stream);
+/* Staging granularity for host-resident values of later requests. */
+int psnvl_set_slice_bytes(uint64_t bytes);
+/* After a failed request on a tensor: clears the error word of its channel. */
+int psnvl_clear_status(int app_id, uint64_t tensor_id);
 uint64_t psnvl_launches(void);
 
 /* ---- KVWorker over raw bytes ---- */

@@ -75,7 +75,9 @@ int psdev_rt_is_pinned_host(const void* p) {
   }
   return a.type == cudaMemoryTypeHost;
 }
-int psdev_rt_host_alloc(void** p, size_t bytes) { return (int)cudaHostAlloc(p, bytes, cudaHostAllocDefault); }
+int psdev_rt_host_alloc(void** p, size_t bytes) {
+  return (int)cudaHostAlloc(p, bytes, cudaHostAllocDefault);
+}
 int psdev_rt_host_free(void* p) { return (int)cudaFreeHost(p); }
 
 }  // extern "C"

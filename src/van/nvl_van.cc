@@ -199,7 +199,9 @@ void FillSimRt(Rt* rt) {
 // ---- first-fit sub-allocator of the arena (host bookkeeping only) ---------------------------
 class SubAlloc {
  public:
-  explicit SubAlloc(size_t bytes) : bytes_(bytes) { free_[PSDEV_CTRL_BYTES] = bytes - PSDEV_CTRL_BYTES; }
+  explicit SubAlloc(size_t bytes) : bytes_(bytes) {
+    free_[PSDEV_CTRL_BYTES] = bytes - PSDEV_CTRL_BYTES;
+  }
   int64_t Alloc(size_t bytes, size_t align) {
     if (align < 16) align = 16;
     bytes = (bytes + 255) & ~size_t(255);
@@ -383,6 +385,7 @@ class Exchange : public SimpleApp {
 size_t DtypeSize(int dt) { return dt == PSDEV_F32 ? 4 : (dt == PSDEV_BF16 ? 2 : 1); }
 
 thread_local void* tls_stream = nullptr;
+thread_local bool tls_has_stream = false;
 
 }  // namespace
 
@@ -521,7 +524,19 @@ const psdev_world_t& Plane::world_struct() const { return impl_->ws; }
 const PlaneOptions& Plane::options() const { return impl_->opts; }
 const std::string& Plane::backend() const { return impl_->backend_name; }
 uint64_t Plane::launches() const { return impl_->rt.launch_count ? impl_->rt.launch_count() : 0; }
-void Plane::SetStream(void* stream) { tls_stream = stream; }
+void Plane::SetStream(void* stream) {
+  tls_stream = stream;
+  tls_has_stream = true;  // a null handle is a stream too: the legacy default stream
+}
+void Plane::ClearStream() {
+  tls_stream = nullptr;
+  tls_has_stream = false;
+}
+void Plane::SetSliceBytes(size_t bytes) {
+  CHECK_GE(bytes, size_t(64));
+  std::lock_guard<std::mutex> lk(impl_->mu);
+  impl_->opts.slice_bytes = bytes & ~size_t(63);
+}
 
 std::vector<std::string> Plane::AllGather(const std::string& mine) {
   Impl& m = *impl_;
@@ -569,7 +584,8 @@ void Plane::Start(const PlaneOptions& options) {
     for (const auto& s : AllGather(mine)) all = all && s == "1";
     backend = all ? "vmm" : "ipc";
   }
-  CHECK(backend == "sim" || backend == "ipc" || backend == "vmm") << "unknown heap backend " << backend;
+  CHECK(backend == "sim" || backend == "ipc" || backend == "vmm")
+      << "unknown heap backend " << backend;
   m.backend_name = backend;
   m.ws = psdev_world_t{};
   m.ws.rank = R;
@@ -991,7 +1007,8 @@ void Plane::Submit(const DeviceRequest& req) {
   if (req.lens_out) { CHECK_EQ(req.lens_out_n, lens.size()); }
 
   const bool in_dev = req.push && (m.sim ? true : m.rt.is_device_pointer(req.vals) != 0);
-  const bool out_dev = req.pull && req.outs && (m.sim ? true : m.rt.is_device_pointer(req.outs) != 0);
+  const bool out_dev =
+      req.pull && req.outs && (m.sim ? true : m.rt.is_device_pointer(req.outs) != 0);
   const bool host_in = req.push && !in_dev && !m.sim;
   const bool host_out = req.pull && req.outs && !out_dev && !m.sim;
   const bool staged = host_in || host_out;
@@ -1037,7 +1054,7 @@ void Plane::Submit(const DeviceRequest& req) {
 
   if (!staged) {
     // values already on the device: everything in order on one stream
-    void* s = tls_stream ? tls_stream : m.s_compute;
+    void* s = tls_has_stream ? tls_stream : m.s_compute;
     if (prev_done && !m.sim) m.rt.stream_wait_event(s, prev_done);
     size_t eoff = 0;  // position in the request's value list, in elements
     for (const Run& r : runs) {
@@ -1059,7 +1076,7 @@ void Plane::Submit(const DeviceRequest& req) {
     // so the copy of slice k+1 in, the kernel of slice k and the copy of slice k-1 out overlap
     void* origin = tls_stream;  // work the caller has queued on its stream comes first
     void* start = nullptr;
-    if (origin) {
+    if (tls_has_stream) {
       start = m.NewEvent();
       m.rt.event_record(start, origin);
       pend.events_to_recycle.push_back(start);
@@ -1068,7 +1085,8 @@ void Plane::Submit(const DeviceRequest& req) {
       if (prev_done) m.rt.stream_wait_event(s, prev_done);
       if (start) m.rt.stream_wait_event(s, start);
     }
-    const int64_t step_g = std::max<int64_t>(8, static_cast<int64_t>(m.opts.slice_bytes / gsz) & ~int64_t(7));
+    const int64_t step_g =
+        std::max<int64_t>(8, static_cast<int64_t>(m.opts.slice_bytes / gsz) & ~int64_t(7));
     size_t elem_off = 0;  // position in the request's value list
     for (const Run& r : runs) {
       for (int64_t b = r.begin; b < r.end; b += step_g) {
@@ -1098,7 +1116,8 @@ void Plane::Submit(const DeviceRequest& req) {
             pend.events_to_recycle.push_back(ev);
             CHECK_EQ(m.rt.memcpy_async(outs + at * osz, weight + b * osz, cnt * osz, m.s_d2h), 0);
           } else if (outs + at * osz != weight + b * osz) {
-            CHECK_EQ(m.rt.memcpy_async(outs + at * osz, weight + b * osz, cnt * osz, m.s_compute), 0);
+            CHECK_EQ(
+                m.rt.memcpy_async(outs + at * osz, weight + b * osz, cnt * osz, m.s_compute), 0);
           }
         }
       }
@@ -1110,7 +1129,7 @@ void Plane::Submit(const DeviceRequest& req) {
     m.rt.stream_wait_event(m.s_compute, tail);
     pend.events_to_recycle.push_back(tail);
     m.rt.event_record(done, m.s_compute);
-    if (origin) m.rt.stream_wait_event(origin, done);
+    if (tls_has_stream) m.rt.stream_wait_event(origin, done);
   }
   pend.event = done;
   {

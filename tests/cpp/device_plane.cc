@@ -3,8 +3,8 @@
 // library).  Runs with the CPU stand-in of the plane (PlaneOptions::device = -1), in one
 // process under the loop van or as several joint processes, so the handle exchange over the
 // control plane, the key -> shard mapping, the routing in KVWorker and the completion through
-// the Customer tracker are checked where no GPU exists.  tests/cuda/device_plane_gpu.cu is the
-// same program on GPUs.
+// the Customer tracker are checked where no GPU exists.  Built with -DPLANE_DEVICE=0 the same
+// program runs on GPUs (tests/test_kvstore_gpu.py, tests/test_multi_gpu.py).
 // Reference behaviour checked: include/ps/kv_app.h:54-372 (timestamps, Wait, callback before
 // Wait returns, zero-copy Z* calls).
 #include <atomic>

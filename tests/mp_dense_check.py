@@ -1,4 +1,6 @@
-"""Multi-GPU check of the fused dense kernel, run as one process per GPU under torchrun.
+"""Multi-GPU check of the fused dense kernel, run as one joint process per GPU under this
+package's launcher (``python -m ps_lite_b200.launch.local --joint N python tests/mp_dense_check.py``);
+the job is an ordinary parameter-server job: no collective library is involved.
 
 Every rank regenerates all ranks' gradients from their seeds, so each can compute the fp32
 PyTorch statement of the update locally and compare its pulled weights and owned master
@@ -8,7 +10,6 @@ import os
 import sys
 
 import torch
-import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
@@ -18,12 +19,8 @@ from ps_lite_b200.utils.oracle import dense_update  # noqa: E402
 
 
 def main():
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    local = int(os.environ.get("LOCAL_RANK", rank))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
-    ctx = kvstore.init(heap_bytes=256 << 20, device=dev)
+    ctx = kvstore.init(heap_bytes=256 << 20)
+    rank, world, dev = ctx.rank, ctx.world, ctx.device
     kv = kvstore.KVStore(ctx, slice_bytes=1 << 20)
     ok = True
     cases = [("momentum", torch.bfloat16, torch.bfloat16, 1_000_003, 4096),
@@ -46,14 +43,14 @@ def main():
                 g.manual_seed(1000 * step + r)
                 grads.append(torch.randn(t.n, device=dev, generator=g).to(gdt))
             if step % 2:   # fused
-                kv.wait(kv.push_pull(key, grads[rank]))
+                kv.wait(kv.push_pull(key, grads[rank][:n]))
             else:          # separate push and pull, host-staged in slices
-                hin = grads[rank].cpu().pin_memory()
-                hout = torch.empty(t.n, dtype=odt).pin_memory()
+                hin = grads[rank][:n].cpu().pin_memory()
+                hout = torch.empty(n, dtype=odt).pin_memory()
                 kv.wait(kv.push(key, hin))
                 kv.wait(kv.pull(key, hout))
                 torch.cuda.synchronize()
-                if not torch.equal(hout.to(dev), t.weight):
+                if not torch.equal(hout.to(dev), t.weight[:n]):
                     ok = False
                     print(f"rank {rank}: host copy of pulled weights differs", flush=True)
             dense_update(ref, grads, kind, lr=0.05, momentum=0.9, eps=1e-6, scale=1.0 / world,
@@ -69,14 +66,12 @@ def main():
                 print(f"rank {rank} case {kind} step {step}: {str(e)[:300]}", flush=True)
     ctx.heap.barrier()
     torch.cuda.synchronize()
-    flag = torch.tensor([1 if ok else 0], device=dev)
-    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    if rank == 0 and int(flag.item()) == 1:
-        print(f"MP_DENSE_OK heap={ctx.heap.backend} multicast={bool(ctx.heap.mc_base)} "
-              f"nvls_used={kv.tables[0].nvls}", flush=True)
+    all_ok = all(b == b"1" for b in ctx.allgather(b"1" if ok else b"0"))
+    if rank == 0 and all_ok:
+        print(f"MP_DENSE_OK world={world} heap={ctx.heap.backend} "
+              f"multicast={bool(ctx.heap.mc_base)} nvls_used={kv.tables[0].nvls}", flush=True)
     kvstore.finalize()
-    dist.destroy_process_group()
-    sys.exit(0 if int(flag.item()) == 1 else 1)
+    sys.exit(0 if all_ok else 1)
 
 
 if __name__ == "__main__":

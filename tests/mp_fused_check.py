@@ -1,4 +1,6 @@
-"""Multi-GPU checks run under torchrun: (1) push with publish followed by the pull fused with
+"""Multi-GPU checks run as joint processes of a parameter-server job (``python -m
+ps_lite_b200.launch.local --joint N python
+tests/mp_fused_check.py``): (1) push with publish followed by the pull fused with
 the tcgen05 GEMM, (2) sparse push/pull with FTRL across ranks, (3) a small model trained
 through the server-side optimizer on different data per rank equals single-process training
 on the averaged gradient.  Rank 0 prints MP_FUSED_OK when every rank agreed."""
@@ -7,7 +9,6 @@ import os
 import sys
 
 import torch
-import torch.distributed as dist
 import torch.nn as nn
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -26,12 +27,8 @@ def seeded(seed, n, dev, scale=1.0):
 
 
 def main():
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    local = int(os.environ.get("LOCAL_RANK", rank))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
-    ctx = kvstore.init(heap_bytes=512 << 20, device=dev)
+    ctx = kvstore.init(heap_bytes=512 << 20)
+    rank, world, dev = ctx.rank, ctx.world, ctx.device
     ok = True
 
     def expect(cond, what):
@@ -117,13 +114,11 @@ def main():
 
     ctx.heap.barrier()
     torch.cuda.synchronize()
-    flag = torch.tensor([1 if ok else 0], device=dev)
-    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    if rank == 0 and int(flag.item()) == 1:
-        print("MP_FUSED_OK", flush=True)
+    all_ok = all(b == b"1" for b in ctx.allgather(b"1" if ok else b"0"))
+    if rank == 0 and all_ok:
+        print(f"MP_FUSED_OK world={world} heap={ctx.heap.backend}", flush=True)
     kvstore.finalize()
-    dist.destroy_process_group()
-    sys.exit(0 if int(flag.item()) == 1 else 1)
+    sys.exit(0 if all_ok else 1)
 
 
 if __name__ == "__main__":
