@@ -220,9 +220,12 @@ __device__ __forceinline__ unsigned long long channel_enter(void* const* base, i
   const int tid = threadIdx.x;
   if (tid == 0) {
     *s_epoch = ld_volatile_u64(&my->epoch[channel]) + 1ull;
-    *s_err = 0;
+    // a channel whose last wait ran out stays out of service until the host has cleared its
+    // status: later launches return at once instead of waiting the deadline out again
+    *s_err = (*(volatile int*)&my->status[channel] != 0);
   }
   __syncthreads();
+  if (*s_err) return 0ull;
   const unsigned long long e = *s_epoch;
   if (blockIdx.x == 0 && tid < world) {
     __threadfence_system();

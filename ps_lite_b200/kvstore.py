@@ -125,6 +125,33 @@ class Context:
 
 
 _ctx: Optional[Context] = None
+_hook_installed = False
+
+
+def _install_exit_hook() -> None:
+    """An uncaught exception in a process that has joined a job ends the process at once, with
+    status 1, after the traceback: the orderly exit would wait in ``Finalize`` for peers that
+    may be waiting for this process, and the launcher is the one that cleans up a failed job
+    (``launch.local`` stops the other nodes; the reference's launcher restarts on code 254)."""
+    global _hook_installed
+    if _hook_installed:
+        return
+    _hook_installed = True
+    import sys
+    import traceback
+    prev = sys.excepthook
+
+    def hook(tp, val, tb):
+        try:
+            traceback.print_exception(tp, val, tb)
+            sys.stderr.flush()
+            sys.stdout.flush()
+        finally:
+            if _ctx is not None and tp is not KeyboardInterrupt:
+                os._exit(1)
+            prev(tp, val, tb)
+
+    sys.excepthook = hook
 
 
 def init(heap_bytes: int = 1 << 30, device=None, **kw) -> Context:
@@ -132,6 +159,7 @@ def init(heap_bytes: int = 1 << 30, device=None, **kw) -> Context:
     global _ctx
     if _ctx is None:
         _ctx = Context(heap_bytes, device, **kw)
+        _install_exit_hook()
     return _ctx
 
 

@@ -29,7 +29,8 @@ class LocalJob:
     def __init__(self, cmd: Sequence[str], num_workers: int = 0, num_servers: int = 0,
                  num_joint: int = 0, env: Optional[Dict[str, str]] = None,
                  port: Optional[int] = None, role_as_arg: bool = False,
-                 capture: bool = False, per_role_env: Optional[Dict[str, Dict[str, str]]] = None):
+                 capture: bool = False, per_role_env: Optional[Dict[str, Dict[str, str]]] = None,
+                 fail_fast: bool = False):
         self.cmd = list(cmd)
         self.num_joint = num_joint
         self.num_workers = num_joint or num_workers
@@ -43,6 +44,9 @@ class LocalJob:
         self.role_as_arg = role_as_arg
         self.capture = capture
         self.per_role_env = per_role_env or {}
+        # a process that fails ends the job: the others are stopped a few seconds later
+        # instead of waiting at a barrier for a node that will never come
+        self.fail_fast = fail_fast
         self.procs: List[dict] = []
         self._lock = threading.Lock()
 
@@ -95,6 +99,8 @@ class LocalJob:
                     pending.append(new)
                 elif rc != 0 and not rec.get("expected_dead") and rc_final == 0:
                     rc_final = rc
+                    if self.fail_fast:
+                        deadline = min(deadline, time.time() + 5.0)
             with self._lock:
                 for rec in self.procs:
                     if rec not in pending and rec["proc"].poll() is None:
@@ -126,10 +132,10 @@ class LocalJob:
 
 def run(cmd: Sequence[str], num_workers: int = 0, num_servers: int = 0, num_joint: int = 0,
         env: Optional[Dict[str, str]] = None, timeout: float = 120.0, role_as_arg: bool = False,
-        capture: bool = False):
+        capture: bool = False, fail_fast: bool = False):
     """Start a job, wait for it, return (exit code, LocalJob)."""
     job = LocalJob(cmd, num_workers, num_servers, num_joint, env, role_as_arg=role_as_arg,
-                   capture=capture)
+                   capture=capture, fail_fast=fail_fast)
     job.start()
     rc = job.wait(timeout)
     return rc, job
@@ -145,6 +151,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--role-as-arg", action="store_true",
                     help="append the role name to the command line of each process")
     ap.add_argument("--timeout", type=float, default=3600.0)
+    ap.add_argument("--keep-going", action="store_true",
+                    help="do not stop the other processes when one exits with an error")
     ap.add_argument("--repeat", type=int, default=1,
                     help="run the job this many times, stop at the first failure (a race "
                          "shaker, like tests/repeat.sh of the reference)")
@@ -158,7 +166,7 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     rc = 0
     for i in range(max(1, args.repeat)):
         rc, _ = run(args.command, args.num_workers, args.num_servers, args.joint, env,
-                    args.timeout, args.role_as_arg)
+                    args.timeout, args.role_as_arg, fail_fast=not args.keep_going)
         if rc != 0:
             if args.repeat > 1:
                 print(f"run {i + 1} of {args.repeat} failed with exit code {rc}", file=sys.stderr)

@@ -90,7 +90,9 @@ int DenseOp(const psdev_world_t* w, const psdev_table_t* t, int op, int64_t begi
   psdev_ctrl_t* my = CtrlOf(w->peer_base[R]);
   unsigned long long e = 1;
   bool ok = true;
-  if (sync & 1) {
+  if ((sync & 1) && __atomic_load_n(&my->status[channel], __ATOMIC_RELAXED) != 0) {
+    ok = false;  // out of service until the status has been cleared
+  } else if (sync & 1) {
     e = my->epoch[channel] + 1ull;
     for (int p = 0; p < W; ++p)
       __atomic_store_n(&CtrlOf(w->peer_base[p])->flag_in[channel][R], e, __ATOMIC_RELEASE);

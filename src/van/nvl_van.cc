@@ -384,6 +384,31 @@ class Exchange : public SimpleApp {
 
 size_t DtypeSize(int dt) { return dt == PSDEV_F32 ? 4 : (dt == PSDEV_BF16 ? 2 : 1); }
 
+// Ends of the slices of [begin, end): sizes small, 2*small, 4*small ... below `step`, then
+// slices of `step`, then the same ramp mirrored.  All cuts but the last are multiples of 8
+// away from `begin`.
+std::vector<int64_t> SliceEnds(int64_t begin, int64_t end, int64_t small, int64_t step) {
+  // the plan is made for the length rounded up to a multiple of 8, then the last cut is
+  // pulled back to `end`
+  const int64_t len = (end - begin + 7) & ~int64_t(7);
+  std::vector<int64_t> ramp;
+  int64_t used = 0;
+  for (int64_t sz = small; sz < step && used + 2 * sz + step <= len; sz *= 2) {
+    ramp.push_back(sz);
+    used += 2 * sz;
+  }
+  std::vector<int64_t> cuts;
+  int64_t at = 0;
+  for (int64_t sz : ramp) cuts.push_back(at += sz);
+  const int64_t mid_end = len - used / 2;
+  while (at + step < mid_end) cuts.push_back(at += step);
+  if (mid_end > at) cuts.push_back(at = mid_end);
+  for (auto it = ramp.rbegin(); it != ramp.rend(); ++it) cuts.push_back(at += *it);
+  for (int64_t& c : cuts) c = std::min(begin + c, end);
+  if (cuts.empty() || cuts.back() != end) cuts.push_back(end);
+  return cuts;
+}
+
 thread_local void* tls_stream = nullptr;
 thread_local bool tls_has_stream = false;
 
@@ -1006,11 +1031,17 @@ void Plane::Submit(const DeviceRequest& req) {
   }
   if (req.lens_out) { CHECK_EQ(req.lens_out_n, lens.size()); }
 
-  const bool in_dev = req.push && (m.sim ? true : m.rt.is_device_pointer(req.vals) != 0);
-  const bool out_dev =
-      req.pull && req.outs && (m.sim ? true : m.rt.is_device_pointer(req.outs) != 0);
-  const bool host_in = req.push && !in_dev && !m.sim;
-  const bool host_out = req.pull && req.outs && !out_dev && !m.sim;
+  // (the CPU stand-in calls "device memory" what lies in an arena)
+  auto on_device = [&](const void* p) {
+    if (!m.sim) return m.rt.is_device_pointer(p) != 0;
+    const char* c = static_cast<const char*>(p);
+    const char* lo = static_cast<const char*>(m.ws.peer_base[m.rank]);
+    return c >= lo && c < lo + m.arena_bytes;
+  };
+  const bool in_dev = req.push && on_device(req.vals);
+  const bool out_dev = req.pull && req.outs && on_device(req.outs);
+  const bool host_in = req.push && !in_dev;
+  const bool host_out = req.pull && req.outs && !out_dev;
   const bool staged = host_in || host_out;
   int op = (req.push ? PSDEV_OP_PUSH : 0) | (req.pull ? PSDEV_OP_PULL : 0);
   if (req.push && !req.pull && req.cmd == kCmdPublish) op |= PSDEV_OP_PUBLISH;
@@ -1087,10 +1118,18 @@ void Plane::Submit(const DeviceRequest& req) {
     }
     const int64_t step_g =
         std::max<int64_t>(8, static_cast<int64_t>(m.opts.slice_bytes / gsz) & ~int64_t(7));
+    // The first slice's copy in and the last slice's copy out overlap with nothing, so the
+    // slices grow from 1/16 of the configured size (at least 256 KiB), doubling up to it, and
+    // shrink again the same way towards the end of a run.
+    const int64_t small_g = std::max<int64_t>(
+        8, std::min<int64_t>(step_g, std::max<int64_t>(step_g / 16, (256 << 10) / gsz)) &
+               ~int64_t(7));
     size_t elem_off = 0;  // position in the request's value list
     for (const Run& r : runs) {
-      for (int64_t b = r.begin; b < r.end; b += step_g) {
-        const int64_t e = std::min<int64_t>(b + step_g, r.end);
+      const std::vector<int64_t> cuts = SliceEnds(r.begin, r.end, small_g, step_g);
+      int64_t b = r.begin;
+      for (const int64_t e : cuts) {
+        if (e <= b) continue;
         const size_t at = elem_off + static_cast<size_t>(b - r.begin);
         const size_t cnt = static_cast<size_t>(e - b);
         if (req.push) {
@@ -1120,6 +1159,7 @@ void Plane::Submit(const DeviceRequest& req) {
                 m.rt.memcpy_async(outs + at * osz, weight + b * osz, cnt * osz, m.s_compute), 0);
           }
         }
+        b = e;
       }
       elem_off += static_cast<size_t>(r.end - r.begin);
     }

@@ -36,9 +36,10 @@ int main(int argc, char** argv) {
     return 0;
   }
   device::PlaneOptions po;
-  po.heap_bytes = 8u << 20;
+  po.heap_bytes = 16u << 20;
+  po.slice_bytes = 1u << 20;  // several slices per request, with the ramp at both ends
   po.device = PLANE_DEVICE < 0 ? -1 : MyRank();
-  po.timeout_ns = 3000000000ull;
+  po.timeout_ns = 1500000000ull;
   Plane* plane = Plane::Get();
   plane->Start(po);
   const int W = plane->world(), R = plane->rank();
@@ -49,7 +50,7 @@ int main(int argc, char** argv) {
   CHECK_EQ(all.size(), (size_t)W);
   for (int r = 0; r < W; ++r) CHECK_EQ(all[r], "rank-" + std::to_string(r));
 
-  const int64_t n = 1000 + 8 * W + 3;  // not a multiple of anything convenient
+  const int64_t n = 600000 + 8 * W + 3;  // not a multiple of anything convenient
   const uint64_t kTensor = 7;
   const device::DenseInfo& d =
       plane->DeclareDense(0, kTensor, n, PSDEV_F32, PSDEV_F32, Sgd(0.5f));

@@ -13,11 +13,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 
 
-def _job(script, nproc, timeout=600, extra_env=None, log=None):
+def _job(script, nproc, timeout=240, extra_env=None, log=None):
     sys.path.insert(0, ROOT)
     from ps_lite_b200.launch.local import LocalJob
     job = LocalJob([sys.executable, os.path.join(HERE, script)], num_joint=nproc,
-                   env=extra_env or {}, capture=True)
+                   env=extra_env or {}, capture=True, fail_fast=True)
     job.start()
     rc = job.wait(timeout)
     out = job.output()
@@ -78,9 +78,9 @@ def test_cpp_program_through_ps_start_across_gpus(cuda_device):
            "-lpsb200_core", f"-Wl,-rpath,{libdir}", "-pthread"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-3000:]
-    job = LocalJob([exe], num_joint=nproc, capture=True,
+    job = LocalJob([exe], num_joint=nproc, capture=True, fail_fast=True,
                    env={"PSB200_NVLS": "0", "PSB200_MULTICAST": "0"})
     job.start()
-    rc = job.wait(300)
+    rc = job.wait(120)
     out = job.output()
     assert rc == 0 and out.count("DEVICE_PLANE_OK") == nproc, out[-4000:]
