@@ -123,8 +123,8 @@ class Plane : public DeviceRoute {
   void UnregisterDense(int app_id, uint64_t tensor_id);
   const DenseInfo* FindDense(int app_id, uint64_t tensor_id) const;
   void SetOptimizer(int app_id, uint64_t tensor_id, const psdev_opt_t& opt);
-  // After a failed request (Wait threw because a peer did not arrive): clears the error word
-  // of the tensor's channel so that later requests can run.
+  // After a failed request (Wait threw because a peer did not arrive): puts the tensor back
+  // into service.  Collective: every worker calls it, also those that saw no error.
   void ClearStatus(int app_id, uint64_t tensor_id);
   int NewChannel();
 

@@ -45,7 +45,10 @@ enum {
   PSDEV_OPT_SGD = 1,      /* w -= lr * (g + wd*w)                                       */
   PSDEV_OPT_MOMENTUM = 2, /* m = mu*m + g + wd*w ; w -= lr*m                            */
   PSDEV_OPT_ADAM = 3,     /* Adam / AdamW with host-computed bias corrections           */
-  PSDEV_OPT_ASSIGN = 4    /* w = scale * sum_w g   (initialisation push)                */
+  PSDEV_OPT_ASSIGN = 4,   /* w = scale * sum_w g   (initialisation push)                */
+  /* kinds from here on belong to handles that applications compile and register themselves
+   * (include/ps/device/user_handle.cuh) */
+  PSDEV_OPT_USER = 100
 };
 
 /* which halves of the round trip a launch performs */
@@ -88,6 +91,7 @@ typedef struct {
   float beta1, beta2, eps; /* ADAM                                                 */
   float bias1, bias2;      /* ADAM: 1-beta1^t and sqrt(1-beta2^t), from the host   */
   int32_t decoupled_wd;    /* ADAM: 1 = AdamW                                      */
+  float user[4];           /* free for user-defined handles                         */
 } psdev_opt_t;
 
 /*
@@ -108,6 +112,11 @@ typedef struct {
   int32_t grad_dtype;  /* PSDEV_F32 | PSDEV_BF16                                 */
   int32_t out_dtype;   /* dtype of the pulled-weight buffer                      */
   uint64_t gscale_off; /* PSDEV_I8 gradients: heap offset of the fp32 scales     */
+  /* Optional low-latency region (0 / 0: none): psdev_ll_bytes(world, ll_cap) zero-filled bytes
+   * at heap offset ll_off.  A fused push+pull of at most ll_cap values then runs without flag
+   * rendezvous: values travel next to a sequence number (include/ps/device/push_pull_ll.cuh). */
+  uint64_t ll_off;
+  int64_t ll_cap;
 } psdev_table_t;
 
 /* ---- symmetric heap ------------------------------------------------------ */
@@ -200,8 +209,14 @@ int psdev_dense_op_multi(const psdev_world_t* w, const psdev_table_t* t, int op,
                          int channel, int num_ctas, uint64_t timeout_ns, int sync, void* stream);
 size_t psdev_sched_bytes(int nseg);
 
+/* Bytes of the low-latency region of a table for requests of up to ll_cap values. */
+size_t psdev_ll_bytes(int world, int64_t ll_cap);
+
 /* Number of kernels this library has launched in this process (for reporting). */
 uint64_t psdev_launch_count(void);
+void psdev_count_launch(void);
+/* State arrays (0, 1 or 2) that the handle of `kind` needs, or -1 for an unknown kind. */
+int psdev_handle_states(int kind);
 
 /* Flag-only rendezvous of all ranks on a channel (device barrier). */
 int psdev_device_barrier(const psdev_world_t* w, int channel, uint64_t timeout_ns,

@@ -37,14 +37,16 @@ class Opt(C.Structure):
     _fields_ = [("kind", C.c_int32), ("scale", C.c_float), ("lr", C.c_float),
                 ("momentum", C.c_float), ("weight_decay", C.c_float),
                 ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float),
-                ("bias1", C.c_float), ("bias2", C.c_float), ("decoupled_wd", C.c_int32)]
+                ("bias1", C.c_float), ("bias2", C.c_float), ("decoupled_wd", C.c_int32),
+                ("user", C.c_float * 4)]
 
 
 class Table(C.Structure):
     _fields_ = [("grad_off", C.c_uint64), ("weight_off", C.c_uint64),
                 ("n", C.c_int64), ("blk", C.c_int64),
                 ("master", C.c_void_p), ("state1", C.c_void_p), ("state2", C.c_void_p),
-                ("grad_dtype", C.c_int32), ("out_dtype", C.c_int32), ("gscale_off", C.c_uint64)]
+                ("grad_dtype", C.c_int32), ("out_dtype", C.c_int32), ("gscale_off", C.c_uint64),
+                ("ll_off", C.c_uint64), ("ll_cap", C.c_int64)]
 
 
 class Sparse(C.Structure):
@@ -95,6 +97,8 @@ def _declare(lib: C.CDLL) -> None:
                                        C.POINTER(Opt), i32, i32, u64, i32, vp]),
         "psdev_sched_bytes": (sz, [i32]),
         "psdev_launch_count": (u64, []),
+        "psdev_ll_bytes": (sz, [i32, i64]),
+        "psdev_handle_states": (i32, [i32]),
         "psdev_device_barrier": (i32, [C.POINTER(World), i32, u64, vp]),
         "psdev_link_copy": (i32, [vp, vp, sz, i32, vp]),
         "psdev_gemm_bf16": (i32, [vp, vp, vp, i64, i64, i64, i32, u64, vp]),

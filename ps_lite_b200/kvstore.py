@@ -286,5 +286,5 @@ class KVStore:
 
     def clear_error(self, key: int) -> None:
         """After a request on ``key`` failed because a peer did not arrive: make the tensor
-        usable again."""
+        usable again.  Collective: every worker calls it."""
         host._ck(host.lib().psnvl_clear_status(APP_ID, int(key)))

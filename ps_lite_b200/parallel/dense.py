@@ -30,7 +30,9 @@ class ServerOptimizer:
 
     ``kind``: ``"sum"`` (the reference's ``KVServerDefaultHandle``: ``store += val``,
     include/ps/kv_app.h:440-463), ``"assign"``, ``"sgd"``, ``"momentum"``, ``"adam"``,
-    ``"adamw"``.
+    ``"adamw"``, or ``"user"`` with ``user_kind`` >= 100 for a handle that the application
+    compiled and registered itself (include/ps/device/user_handle.cuh); ``user`` then carries
+    up to four extra hyper-parameters of that handle.
     """
     kind: str = "sum"
     lr: float = 0.01
@@ -40,17 +42,27 @@ class ServerOptimizer:
     beta2: float = 0.999
     eps: float = 1e-8
     scale: float = 1.0  # multiplies the sum over workers (use 1/world to average)
+    user_kind: int = 0
+    user: tuple = ()
 
     _KINDS = {"sum": _lib.OPT_SUM, "assign": _lib.OPT_ASSIGN, "sgd": _lib.OPT_SGD,
               "momentum": _lib.OPT_MOMENTUM, "adam": _lib.OPT_ADAM, "adamw": _lib.OPT_ADAM}
 
     @property
     def num_states(self) -> int:
+        if self.kind == "user":
+            n = int(_lib.device_lib().psdev_handle_states(int(self.user_kind)))
+            if n < 0:
+                raise ValueError(f"no handle is registered as kind {self.user_kind}: load the "
+                                 "shared object that defines it first")
+            return n
         return {"momentum": 1, "adam": 2, "adamw": 2}.get(self.kind, 0)
 
     def to_struct(self, step: int = 1) -> _lib.Opt:
         o = _lib.Opt()
-        o.kind = self._KINDS[self.kind]
+        o.kind = int(self.user_kind) if self.kind == "user" else self._KINDS[self.kind]
+        for i, v in enumerate(self.user[:4]):
+            o.user[i] = float(v)
         o.scale, o.lr, o.momentum, o.weight_decay = self.scale, self.lr, self.momentum, self.weight_decay
         o.beta1, o.beta2, o.eps = self.beta1, self.beta2, self.eps
         o.bias1 = 1.0 - self.beta1 ** step
@@ -86,7 +98,7 @@ class DenseTable:
     def __init__(self, heap: SymmetricHeap, n: int, grad_dtype=torch.float32,
                  out_dtype=torch.float32, blk: Optional[int] = None,
                  optimizer: Optional[ServerOptimizer] = None, channel: int = 0,
-                 num_ctas: int = 0, nvls: Optional[bool] = None):
+                 num_ctas: int = 0, nvls: Optional[bool] = None, ll_cap: Optional[int] = None):
         self.heap = heap
         W = heap.world
         self.n_user = int(n)
@@ -138,6 +150,21 @@ class DenseTable:
         t.gscale_off = self.gscale_off
         self.grad.zero_()
         self.weight.zero_()
+        # Low-latency region for small fused requests (include/ps/device/push_pull_ll.cuh):
+        # up to `ll_cap` values per request travel next to a sequence number instead of between
+        # two flag rendezvous.  Needs real ranks (kernels of all ranks run at the same time).
+        if ll_cap is None:
+            import os
+            ll_cap = int(os.environ.get("PSB200_LL_CAP", str(128 << 10)))
+        self.ll_cap = 0
+        if W > 1 and ll_cap > 0 and grad_dtype != torch.int8 and not heap.emulated_ranks:
+            self.ll_cap = min(int(ll_cap), self.n)
+            nb = int(heap.lib.psdev_ll_bytes(W, self.ll_cap))
+            self.ll_off = heap.alloc(nb)
+            heap.tensor(self.ll_off, nb, torch.uint8).zero_()
+            t.ll_off, t.ll_cap = self.ll_off, self.ll_cap
+            # nobody writes into a peer's region before that peer has cleared it
+            heap.barrier()
 
     def stage_int8(self, grad: torch.Tensor, begin: int = 0) -> None:
         """Compress an fp32 gradient into this table's int8 gradient buffer starting at element

@@ -62,6 +62,7 @@ class SymmetricHeap:
         self._symm = None       # torch symmetric-memory tensor and handle, when used
         self.backend = "ipc"
         self._plane = False
+        self.emulated_ranks = _bases is not None  # ranks of one process on one GPU
         if backend == "plane":
             self._init_plane()
             return

@@ -2,4 +2,5 @@
 #define PSDEV_DENSE_GT __nv_bfloat16
 #define PSDEV_DENSE_OT float
 #define PSDEV_DENSE_FN dense_dispatch_bf16_f32
+#define PSDEV_DENSE_LL_FN dense_ll_dispatch_bf16_f32
 #include "kernels/dense_inst.inl"

@@ -2,4 +2,5 @@
 #define PSDEV_DENSE_GT float
 #define PSDEV_DENSE_OT __nv_bfloat16
 #define PSDEV_DENSE_FN dense_dispatch_f32_bf16
+#define PSDEV_DENSE_LL_FN dense_ll_dispatch_f32_bf16
 #include "kernels/dense_inst.inl"

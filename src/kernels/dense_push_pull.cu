@@ -4,7 +4,10 @@
 #include <atomic>
 #include <cstdlib>
 
-#include "ps/device/push_pull.cuh"
+#include <map>
+#include <mutex>
+
+#include "ps/device/user_handle.cuh"
 
 namespace psdev {
 std::atomic<uint64_t> g_launches{0};
@@ -14,7 +17,56 @@ int dense_dispatch_bf16_f32(int op, const DenseArgs& a, int ctas, cudaStream_t s
 int dense_dispatch_f32_bf16(int op, const DenseArgs& a, int ctas, cudaStream_t s);
 int dense_dispatch_i8_f32(int op, const DenseArgs& a, int ctas, cudaStream_t s);
 int dense_dispatch_i8_bf16(int op, const DenseArgs& a, int ctas, cudaStream_t s);
+int dense_ll_dispatch_f32_f32(const LLArgs& a, cudaStream_t s);
+int dense_ll_dispatch_bf16_bf16(const LLArgs& a, cudaStream_t s);
+int dense_ll_dispatch_bf16_f32(const LLArgs& a, cudaStream_t s);
+int dense_ll_dispatch_f32_bf16(const LLArgs& a, cudaStream_t s);
 }  // namespace psdev
+
+// ---- user-defined handles -------------------------------------------------------------------
+namespace {
+struct UserHandle {
+  int num_states;
+  psdev_user_dense_fn dense;
+  psdev_user_ll_fn ll;
+};
+std::mutex g_user_mu;
+std::map<int, UserHandle>& user_handles() {
+  static std::map<int, UserHandle>* m = new std::map<int, UserHandle>;  // used by static ctors
+  return *m;
+}
+bool find_user(int kind, UserHandle* out) {
+  std::lock_guard<std::mutex> lk(g_user_mu);
+  auto it = user_handles().find(kind);
+  if (it == user_handles().end()) return false;
+  *out = it->second;
+  return true;
+}
+}  // namespace
+
+extern "C" int psdev_register_dense_handle(int kind, int num_states, psdev_user_dense_fn dense,
+                                           psdev_user_ll_fn ll) {
+  if (kind < PSDEV_OPT_USER || num_states < 0 || num_states > 2 || !dense) return PSDEV_ERR_ARG;
+  std::lock_guard<std::mutex> lk(g_user_mu);
+  if (user_handles().count(kind)) return PSDEV_ERR_ARG;
+  user_handles()[kind] = UserHandle{num_states, dense, ll};
+  return 0;
+}
+
+extern "C" int psdev_handle_states(int kind) {
+  switch (kind) {
+    case PSDEV_OPT_SUM: case PSDEV_OPT_SGD: case PSDEV_OPT_ASSIGN: return 0;
+    case PSDEV_OPT_MOMENTUM: return 1;
+    case PSDEV_OPT_ADAM: return 2;
+    default: break;
+  }
+  UserHandle h;
+  return find_user(kind, &h) ? h.num_states : -1;
+}
+
+extern "C" void psdev_count_launch(void) {
+  psdev::g_launches.fetch_add(1, std::memory_order_relaxed);
+}
 
 // ---- P3 slice schedule (device side) ----------------------------------------------------------
 // Orders the slices of one launch by priority (highest first, ties in submission order -- the
@@ -107,6 +159,20 @@ extern "C" int psdev_dense_op_multi(const psdev_world_t* w, const psdev_table_t*
                        stream, segs, nseg, sched);
 }
 
+extern "C" size_t psdev_ll_bytes(int world, int64_t ll_cap) {
+  if (world < 1 || ll_cap <= 0) return 0;
+  return kLLHeaderBytes + (size_t)(world + 1) * (size_t)ll_cap * 8;
+}
+
+// PSB200_LL=0 keeps every request on the general kernel (read once).
+static bool ll_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("PSB200_LL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 extern "C" size_t psdev_sched_bytes(int nseg) { return sizeof(SchedEntry) * (size_t)(nseg + 1); }
 
 static int dense_op_impl(const psdev_world_t* w, const psdev_table_t* t, int op, int64_t begin,
@@ -196,6 +262,52 @@ static int dense_op_impl(const psdev_world_t* w, const psdev_table_t* t, int op,
   const int ctas = num_ctas;
   cudaStream_t s = (cudaStream_t)stream;
   const bool gbf = t->grad_dtype == PSDEV_BF16, obf = t->out_dtype == PSDEV_BF16;
+  if (op == PSDEV_OP_PUSHPULL && !a.self_only && (sync & 1) && W > 1 && nseg == 0 &&
+      t->ll_cap > 0 && end - begin <= t->ll_cap && end > begin && t->grad_dtype != PSDEV_I8 &&
+      ll_enabled()) {
+    // small request: one sequence-numbered exchange instead of two flag rendezvous
+    if (w->heap_bytes) {
+      const uint64_t need = psdev_ll_bytes(W, t->ll_cap);
+      if (t->ll_off < PSDEV_CTRL_BYTES || t->ll_off > w->heap_bytes ||
+          need > w->heap_bytes - t->ll_off)
+        return PSDEV_ERR_BOUNDS;
+    }
+    LLArgs l{};
+    for (int p = 0; p < W; ++p) l.base[p] = a.base[p];
+    l.rank = R;
+    l.world = W;
+    l.grad_off = t->grad_off;
+    l.weight_off = t->weight_off;
+    l.ll_off = t->ll_off;
+    l.ll_cap = t->ll_cap;
+    l.blk = t->blk;
+    l.begin = begin;
+    l.end = end;
+    l.master = t->master;
+    l.s1 = t->state1;
+    l.s2 = t->state2;
+    l.opt = a.opt;
+    l.channel = channel;
+    l.timeout_ns = timeout_ns;
+    l.n_total = a.n_total;
+    l.local_len = a.local_len;
+    if (a.opt.kind >= PSDEV_OPT_USER) {
+      UserHandle h;
+      if (!find_user(a.opt.kind, &h)) return PSDEV_ERR_UNSUPPORTED;
+      if (h.ll) return h.ll(&l, stream, t->grad_dtype, t->out_dtype);
+    } else {
+      if (gbf && obf) return dense_ll_dispatch_bf16_bf16(l, s);
+      if (gbf && !obf) return dense_ll_dispatch_bf16_f32(l, s);
+      if (!gbf && obf) return dense_ll_dispatch_f32_bf16(l, s);
+      return dense_ll_dispatch_f32_f32(l, s);
+    }
+  }
+  if ((op & PSDEV_OP_PUSH) && a.opt.kind >= PSDEV_OPT_USER) {
+    // a handle that the application compiled and registered (ps/device/user_handle.cuh)
+    UserHandle h;
+    if (!find_user(a.opt.kind, &h)) return PSDEV_ERR_UNSUPPORTED;
+    return h.dense(op, &a, ctas, stream, t->grad_dtype, t->out_dtype);
+  }
   if (t->grad_dtype == PSDEV_I8) {
     // int8 block-scale gradients: 16 values per vector, ranges aligned to 16, no multicast
     // reduction (the switch cannot apply per-block scales)

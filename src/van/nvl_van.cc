@@ -57,6 +57,9 @@ struct Rt {
   int (*event_sync)(void*) = nullptr;
   int (*stream_wait_event)(void*, void*) = nullptr;
   int (*memcpy_async)(void*, const void*, size_t, void*) = nullptr;
+  int (*memset_async)(void*, int, size_t, void*) = nullptr;
+  size_t (*ll_bytes)(int, int64_t) = nullptr;
+  int (*handle_states)(int) = nullptr;
   int (*is_device_pointer)(const void*) = nullptr;
   int (*heap_create)(size_t, void**, unsigned char*) = nullptr;
   int (*heap_open)(const unsigned char*, void**) = nullptr;
@@ -118,6 +121,9 @@ void* LoadRt(const std::string& configured, Rt* rt) {
   Bind(lib, "psdev_rt_event_sync", &rt->event_sync);
   Bind(lib, "psdev_rt_stream_wait_event", &rt->stream_wait_event);
   Bind(lib, "psdev_rt_memcpy_async", &rt->memcpy_async);
+  Bind(lib, "psdev_rt_memset_async", &rt->memset_async);
+  Bind(lib, "psdev_ll_bytes", &rt->ll_bytes);
+  Bind(lib, "psdev_handle_states", &rt->handle_states);
   Bind(lib, "psdev_rt_is_device_pointer", &rt->is_device_pointer);
   Bind(lib, "psdev_heap_create", &rt->heap_create);
   Bind(lib, "psdev_heap_open", &rt->heap_open);
@@ -835,7 +841,7 @@ std::vector<Key> Plane::DenseKeys(uint64_t tensor_id) const {
   return keys;
 }
 
-static int NumStates(int kind) {
+static int BuiltinStates(int kind) {
   return kind == PSDEV_OPT_MOMENTUM ? 1 : (kind == PSDEV_OPT_ADAM ? 2 : 0);
 }
 
@@ -862,14 +868,35 @@ const DenseInfo& Plane::DeclareDense(int app_id, uint64_t tensor_id, int64_t n, 
     CHECK_GE(soff, 0);
     t.gscale_off = static_cast<uint64_t>(soff);
   }
+  if (!m.sim && W > 1 && grad_dtype != PSDEV_I8) {
+    // low-latency region for small fused requests; cleared before any peer may write into it
+    int64_t cap = 128 << 10;
+    if (const char* env = getenv("PSB200_LL_CAP")) cap = atoll(env);
+    cap = std::min<int64_t>(cap, t.n);
+    if (cap > 0) {
+      const size_t nb = m.rt.ll_bytes(W, cap);
+      const int64_t loff = Alloc(nb);
+      CHECK_GE(loff, 0) << "symmetric heap exhausted";
+      m.rt.set_device(m.opts.device);
+      CHECK_EQ(m.rt.memset_async(Local(loff), 0, nb, m.s_compute), 0);
+      CHECK_EQ(m.rt.stream_sync(m.s_compute), 0);
+      t.ll_off = static_cast<uint64_t>(loff);
+      t.ll_cap = cap;
+      Barrier();
+    }
+  }
   void* p = nullptr;
   CHECK_EQ(m.rt.malloc_(&p, static_cast<size_t>(local_len) * 4), 0);
   t.master = static_cast<float*>(p);
-  if (NumStates(opt.kind) >= 1) {
+  // (a handle that the application registered says itself how much state it keeps)
+  const int num_states =
+      m.rt.handle_states ? m.rt.handle_states(opt.kind) : BuiltinStates(opt.kind);
+  CHECK_GE(num_states, 0) << "no server handle is registered as kind " << opt.kind;
+  if (num_states >= 1) {
     CHECK_EQ(m.rt.malloc_(&p, static_cast<size_t>(local_len) * 4), 0);
     t.state1 = static_cast<float*>(p);
   }
-  if (NumStates(opt.kind) >= 2) {
+  if (num_states >= 2) {
     CHECK_EQ(m.rt.malloc_(&p, static_cast<size_t>(local_len) * 4), 0);
     t.state2 = static_cast<float*>(p);
   }
@@ -930,9 +957,19 @@ const DenseInfo* Plane::FindDense(int app_id, uint64_t tensor_id) const {
 void Plane::ClearStatus(int app_id, uint64_t tensor_id) {
   const DenseInfo* d = FindDense(app_id, tensor_id);
   CHECK(d) << "unknown tensor " << tensor_id;
-  impl_->Drain();
-  impl_->rt.set_device(impl_->opts.device);
-  CHECK_EQ(impl_->rt.channel_clear(impl_->ws.peer_base[impl_->rank], d->channel), 0);
+  Impl& m = *impl_;
+  m.Drain();
+  m.rt.set_device(m.opts.device);
+  Barrier();  // nobody is inside a kernel on this tensor any more
+  CHECK_EQ(m.rt.channel_clear(m.ws.peer_base[m.rank], d->channel), 0);
+  if (d->table.ll_cap > 0 && !m.sim) {
+    // words of the abandoned round must not be mistaken for those of a later one
+    const size_t nb = m.rt.ll_bytes(m.world, d->table.ll_cap);
+    void* region = Local(static_cast<int64_t>(d->table.ll_off));
+    CHECK_EQ(m.rt.memset_async(region, 0, nb, m.s_compute), 0);
+    CHECK_EQ(m.rt.stream_sync(m.s_compute), 0);
+  }
+  Barrier();
 }
 
 void Plane::SetOptimizer(int app_id, uint64_t tensor_id, const psdev_opt_t& opt) {

@@ -26,7 +26,10 @@ def main():
     cases = [("momentum", torch.bfloat16, torch.bfloat16, 1_000_003, 4096),
              ("adam", torch.float32, torch.float32, 300_000, None),
              ("sum", torch.float32, torch.float32, 4096, 8),
-             ("sgd", torch.bfloat16, torch.float32, 2_000_000, 1 << 16)]
+             ("sgd", torch.bfloat16, torch.float32, 2_000_000, 1 << 16),
+             # small enough for the low-latency exchange (values next to sequence numbers)
+             ("momentum", torch.bfloat16, torch.bfloat16, 50_003, 64),
+             ("adam", torch.float32, torch.bfloat16, 8, None)]
     for key, (kind, gdt, odt, n, blk) in enumerate(cases):
         opt = ServerOptimizer(kind, lr=0.05, momentum=0.9, eps=1e-6, scale=1.0 / world)
         g0 = torch.Generator(device=dev)
