@@ -222,6 +222,58 @@ int psdev_handle_states(int kind);
 int psdev_device_barrier(const psdev_world_t* w, int channel, uint64_t timeout_ns,
                          void* stream);
 
+/* ---- sparse (keyed) push / pull --------------------------------------------------------- */
+/*
+ * One keyed table.  Server s owns keys [s*range, (s+1)*range); a value has `width` fp32
+ * elements, or, when lens_off != 0, lens[i] <= width elements packed back to back in the request
+ * (dynamic-length values).  Request buffers live in every rank's arena at the same offsets; the
+ * owner's state arrays (`slots` x `width` elements) are local memory.
+ */
+typedef struct {
+  uint64_t range;      /* keys per shard                                                  */
+  uint64_t keys_off;   /* u64[max_n]   request keys, sorted and unique                    */
+  uint64_t grads_off;  /* f32[max_vals] pushed values                                     */
+  uint64_t out_off;    /* f32[max_vals] pulled values                                     */
+  uint64_t pos_off;    /* i64[world+2] cut points of the key list, [world+1] = n          */
+  uint64_t acc_off;    /* f32[slots*width] the server's gradient accumulator              */
+  float* w;            /* values                                                          */
+  float* z;            /* FTRL z, or NULL                                                 */
+  float* n;            /* FTRL n, or NULL                                                 */
+  int32_t kind;        /* 0 sum, 1 SGD, 2 FTRL-proximal                                   */
+  float lr, alpha, beta, l1, l2;
+  uint64_t hkeys_off;  /* hash store: u64[capacity] key table (filled with 0xff)          */
+  uint64_t capacity;   /* hash store: slots per server, power of two; 0 = direct index    */
+  int32_t* overflow;   /* hash store: device int set to 1 when a table is full            */
+  int32_t width;       /* elements per value (maximum, with lengths)                      */
+  int32_t channel;     /* rendezvous channel of the table                                 */
+  int64_t max_n;       /* keys per request at most                                        */
+  int64_t max_vals;    /* values per request at most                                      */
+  int64_t slots;       /* slots of the store: keys of the range, or capacity              */
+  uint64_t lens_off;   /* i32[max_n] per-key lengths of the request, or 0                 */
+  uint64_t offs_off;   /* i64[max_n+1] value offsets (computed by the scatter call)       */
+  int32_t* klen;       /* owner state: stored length per slot (with lengths), or NULL     */
+  uint64_t timeout_ns; /* bound of the rendezvous waits; 0 = 20 s                         */
+} psdev_sparse_t;
+
+/* Cut points of a sorted key list at the W+1 shard boundaries (device pointers; pos[world+1]
+ * receives n). */
+int psdev_key_shard_lookup(const uint64_t* keys, int64_t n, uint64_t range, int world,
+                           int64_t* pos, void* stream);
+/* offs[i] = lens[0] + ... + lens[i-1] for i = 0..n (device pointers). */
+int psdev_lens_to_offsets(const int32_t* lens, int64_t n, int64_t* offs, void* stream);
+/* Worker role: cut points (and value offsets), then every element of the n staged pairs is
+ * added into its owner's accumulator over NVLink. */
+int psdev_sparse_scatter(const psdev_world_t* w, const psdev_sparse_t* t, int64_t n, int num_ctas,
+                         void* stream);
+/* Server role: applies the handle to every key that any worker pushed.  sync != 0: first waits
+ * until every rank has entered this kernel (i.e. finished its scatter). */
+int psdev_sparse_apply(const psdev_world_t* w, const psdev_sparse_t* t, int num_ctas, int sync,
+                       void* stream);
+/* Server role: stores the value of every requested key into the requester's output buffer.
+ * sync != 0: ends by waiting until every rank has done so. */
+int psdev_sparse_respond(const psdev_world_t* w, const psdev_sparse_t* t, int num_ctas, int sync,
+                         void* stream);
+
 /* ---- bf16 GEMM on tcgen05, alone or fused with the pull of its weights ----------------- */
 /* c[M,N] = x[M,K] * w[N,K]^T; all row-major bf16, 16-byte aligned, N and K multiples of 8. */
 int psdev_gemm_bf16(const void* x, const void* w, void* c, int64_t M, int64_t N, int64_t K,

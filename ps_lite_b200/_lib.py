@@ -55,7 +55,10 @@ class Sparse(C.Structure):
                 ("w", C.c_void_p), ("z", C.c_void_p), ("n", C.c_void_p),
                 ("kind", C.c_int32), ("lr", C.c_float), ("alpha", C.c_float),
                 ("beta", C.c_float), ("l1", C.c_float), ("l2", C.c_float),
-                ("hkeys_off", C.c_uint64), ("capacity", C.c_uint64), ("overflow", C.c_void_p)]
+                ("hkeys_off", C.c_uint64), ("capacity", C.c_uint64), ("overflow", C.c_void_p),
+                ("width", C.c_int32), ("channel", C.c_int32), ("max_n", C.c_int64),
+                ("max_vals", C.c_int64), ("slots", C.c_int64), ("lens_off", C.c_uint64),
+                ("offs_off", C.c_uint64), ("klen", C.c_void_p), ("timeout_ns", C.c_uint64)]
 
 
 class PsdevError(RuntimeError):
@@ -117,8 +120,9 @@ def _declare(lib: C.CDLL) -> None:
         "psdev_ordered_match": (i32, [vp, vp, i64, vp, vp, i64, i32, i32, i32, vp, vp]),
         "psdev_key_shard_lookup": (i32, [vp, i64, u64, i32, vp, vp]),
         "psdev_sparse_scatter": (i32, [C.POINTER(World), C.POINTER(Sparse), i64, i32, vp]),
-        "psdev_sparse_apply": (i32, [C.POINTER(World), C.POINTER(Sparse), i32, vp]),
-        "psdev_sparse_respond": (i32, [C.POINTER(World), C.POINTER(Sparse), i32, vp]),
+        "psdev_sparse_apply": (i32, [C.POINTER(World), C.POINTER(Sparse), i32, i32, vp]),
+        "psdev_sparse_respond": (i32, [C.POINTER(World), C.POINTER(Sparse), i32, i32, vp]),
+        "psdev_lens_to_offsets": (i32, [vp, i64, vp, vp]),
     }
     for name, (res, args) in sig.items():
         if hasattr(lib, name):

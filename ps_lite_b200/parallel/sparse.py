@@ -1,10 +1,14 @@
 """Sparse key-value table on the device data plane (direct-index store, range-sharded keys).
 
-Per step every worker pushes sorted unique uint64 keys with one fp32 gradient each and pulls
-the updated values of the same keys (``KVWorker::ZPush`` + ``ZPull`` of the reference,
-include/ps/kv_app.h:243-280).  Server ``s`` owns keys ``[s*range, (s+1)*range)``
-(src/postoffice.cc:169-180) and applies ``sum``, ``sgd`` or FTRL-proximal to the keys that were
-pushed.  See ``src/kernels/sparse.cu`` for the kernels.
+Per step every worker pushes sorted unique uint64 keys with their fp32 values and pulls the
+updated values of the same keys (``KVWorker::ZPush`` + ``ZPull`` of the reference,
+include/ps/kv_app.h:243-280).  A value has ``width`` elements, or, with ``var_len=True``, a
+per-key number of elements up to ``width`` given by ``lens`` (the reference's dynamic-length
+values, kv_app.h:24-31): the values of a request are then packed back to back and the kernels
+find value ``i`` at the prefix sum of the lengths, as ``DefaultSlicer`` does (kv_app.h:547-567).
+Server ``s`` owns keys ``[s*range, (s+1)*range)`` (src/postoffice.cc:169-180) and applies
+``sum``, ``sgd`` or FTRL-proximal element-wise to the keys that were pushed.  See
+``src/kernels/sparse.cu`` for the kernels.
 """
 from __future__ import annotations
 
@@ -24,7 +28,7 @@ class SparseTable:
     def __init__(self, heap: SymmetricHeap, key_space: int, max_keys: int, kind: str = "ftrl",
                  lr: float = 0.01, alpha: float = 0.1, beta: float = 1.0, l1: float = 1.0,
                  l2: float = 1.0, barrier_channel: int = _lib.NUM_CHANNELS - 2,
-                 hash_capacity: int = 0):
+                 hash_capacity: int = 0, width: int = 1, var_len: bool = False):
         self.heap = heap
         W = heap.world
         self.key_space, self.max_keys, self.kind = int(key_space), int(max_keys), kind
@@ -35,17 +39,26 @@ class SparseTable:
         if hash_capacity:
             self.capacity = 1 << (int(hash_capacity) - 1).bit_length()
         slots = self.capacity or self.range
+        self.slots, self.width, self.var_len = slots, int(width), bool(var_len)
+        if self.width < 1:
+            raise ValueError("width must be at least 1")
+        max_vals = max_keys * self.width
+        self.max_vals = max_vals
         self.keys_off = heap.alloc(8 * max_keys)
-        self.grads_off = heap.alloc(4 * max_keys)
-        self.out_off = heap.alloc(4 * max_keys)
+        self.grads_off = heap.alloc(4 * max_vals)
+        self.out_off = heap.alloc(4 * max_vals)
         self.pos_off = heap.alloc(8 * (W + 2))
-        self.acc_off = heap.alloc(4 * slots)
+        self.acc_off = heap.alloc(4 * slots * self.width)
         self.hkeys_off = heap.alloc(8 * self.capacity) if self.capacity else 0
+        self.lens_off = heap.alloc(4 * max_keys) if var_len else 0
+        self.offs_off = heap.alloc(8 * (max_keys + 1)) if var_len else 0
         self.keys = heap.tensor(self.keys_off, max_keys, torch.int64)  # bit pattern of uint64
-        self.grads = heap.tensor(self.grads_off, max_keys, torch.float32)
-        self.out = heap.tensor(self.out_off, max_keys, torch.float32)
+        self.grads = heap.tensor(self.grads_off, max_vals, torch.float32)
+        self.out = heap.tensor(self.out_off, max_vals, torch.float32)
         self.pos = heap.tensor(self.pos_off, W + 2, torch.int64)
-        self.acc = heap.tensor(self.acc_off, slots, torch.float32)
+        self.acc = heap.tensor(self.acc_off, slots * self.width, torch.float32)
+        self.lens = heap.tensor(self.lens_off, max_keys, torch.int32) if var_len else None
+        self.offs = heap.tensor(self.offs_off, max_keys + 1, torch.int64) if var_len else None
         self.hkeys = (heap.tensor(self.hkeys_off, self.capacity, torch.int64)
                       if self.capacity else None)
         if self.hkeys is not None:
@@ -53,9 +66,11 @@ class SparseTable:
         self.acc.zero_()
         self.pos.zero_()
         dev = heap.device
-        self.w = torch.zeros(slots, dtype=torch.float32, device=dev)
-        self.z = torch.zeros(slots, dtype=torch.float32, device=dev) if kind == "ftrl" else None
-        self.n = torch.zeros(slots, dtype=torch.float32, device=dev) if kind == "ftrl" else None
+        ne = slots * self.width
+        self.w = torch.zeros(ne, dtype=torch.float32, device=dev)
+        self.z = torch.zeros(ne, dtype=torch.float32, device=dev) if kind == "ftrl" else None
+        self.n = torch.zeros(ne, dtype=torch.float32, device=dev) if kind == "ftrl" else None
+        self.klen = torch.zeros(slots, dtype=torch.int32, device=dev) if var_len else None
         self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
         self._world = heap.world_struct()
         t = _lib.Sparse()
@@ -69,46 +84,65 @@ class SparseTable:
         t.lr, t.alpha, t.beta, t.l1, t.l2 = lr, alpha, beta, l1, l2
         t.hkeys_off, t.capacity = self.hkeys_off, self.capacity
         t.overflow = self.overflow.data_ptr()
+        t.width, t.channel = self.width, int(barrier_channel)
+        t.max_n, t.max_vals, t.slots = int(max_keys), int(max_vals), int(slots)
+        t.lens_off, t.offs_off = self.lens_off, self.offs_off
+        t.klen = self.klen.data_ptr() if self.klen is not None else None
+        from .dense import default_timeout_s
+        t.timeout_ns = int(default_timeout_s() * 1e9)
         self._t = t
         self.barrier_channel = barrier_channel
         self.count = 0
 
     # -- the three phases; `sync=False` lets a test run all ranks' phases on one GPU ----------
-    def stage(self, keys: torch.Tensor, grads: torch.Tensor) -> None:
-        """Copy a request (sorted unique keys, one gradient each) into the heap buffers."""
+    def stage(self, keys: torch.Tensor, grads: torch.Tensor,
+              lens: "torch.Tensor | None" = None) -> None:
+        """Copy a request into the heap buffers: sorted unique keys and their values (``width``
+        per key, or ``lens[i]`` per key back to back for a ``var_len`` table)."""
         n = keys.numel()
         if n > self.max_keys:
             raise ValueError("more keys than max_keys")
+        nv = grads.numel()
+        if self.var_len:
+            if lens is None or lens.numel() != n:
+                raise ValueError("a var_len table needs one length per key")
+            if nv > self.max_vals:
+                raise ValueError("more values than the table was sized for")
+            self.lens[:n].copy_(lens.to(torch.int32), non_blocking=True)
+        elif nv != n * self.width:
+            raise ValueError(f"expected {self.width} values per key")
         self.keys[:n].copy_(keys.view(torch.int64), non_blocking=True)
-        self.grads[:n].copy_(grads, non_blocking=True)
-        self.count = n
+        self.grads[:nv].copy_(grads.reshape(-1), non_blocking=True)
+        self.count, self.count_vals = n, nv
 
     def scatter(self, stream=None) -> None:
         s = stream or torch.cuda.current_stream(self.heap.device)
         _lib.check(self.heap.lib.psdev_sparse_scatter(C.byref(self._world), C.byref(self._t),
                                                       self.count, 0, s.cuda_stream), "sparse_scatter")
 
-    def apply(self, stream=None) -> None:
+    def apply(self, stream=None, sync: bool = False) -> None:
         s = stream or torch.cuda.current_stream(self.heap.device)
         _lib.check(self.heap.lib.psdev_sparse_apply(C.byref(self._world), C.byref(self._t), 0,
-                                                    s.cuda_stream), "sparse_apply")
+                                                    int(sync), s.cuda_stream), "sparse_apply")
 
-    def respond(self, stream=None) -> None:
+    def respond(self, stream=None, sync: bool = False) -> None:
         s = stream or torch.cuda.current_stream(self.heap.device)
         _lib.check(self.heap.lib.psdev_sparse_respond(C.byref(self._world), C.byref(self._t), 0,
-                                                      s.cuda_stream), "sparse_respond")
+                                                      int(sync), s.cuda_stream), "sparse_respond")
 
-    def push_pull(self, keys: torch.Tensor, grads: torch.Tensor) -> torch.Tensor:
-        """One step: push (keys, grads), apply the handle on the owners, pull the new values.
+    def push_pull(self, keys: torch.Tensor, grads: torch.Tensor,
+                  lens: "torch.Tensor | None" = None) -> torch.Tensor:
+        """One step: push (keys, values), apply the handle on the owners, pull the new values.
 
-        Returns a view of the heap output buffer (valid until the next call)."""
-        self.stage(keys, grads)
+        Three launches: scatter; apply, which first waits for every rank's scatter; respond,
+        which ends when every rank's answers have landed.  Returns a view of the heap output
+        buffer (valid until the next call), laid out like the pushed values."""
+        self.stage(keys, grads, lens)
         self.scatter()
-        self.heap.barrier(self.barrier_channel)   # every worker's gradients are accumulated
-        self.apply()
-        self.respond()
-        self.heap.barrier(self.barrier_channel)   # every server's answers have landed
-        return self.out[: self.count]
+        multi = self.heap.world > 1
+        self.apply(sync=multi)
+        self.respond(sync=multi)
+        return self.out[: self.count_vals]
 
     def check(self) -> None:
         self.heap.check_channel(self.barrier_channel)
@@ -119,7 +153,8 @@ class SparseTable:
         """Write this rank's key range (values and FTRL state) to ``path``."""
         torch.cuda.synchronize(self.heap.device)
         torch.save({"key_space": self.key_space, "world": self.heap.world, "rank": self.heap.rank,
-                    "kind": self.kind, "w": self.w.cpu(),
+                    "kind": self.kind, "width": self.width, "w": self.w.cpu(),
+                    "klen": None if self.klen is None else self.klen.cpu(),
                     "z": None if self.z is None else self.z.cpu(),
                     "n": None if self.n is None else self.n.cpu()}, path)
 
@@ -128,7 +163,11 @@ class SparseTable:
         if (ck["key_space"], ck["world"], ck["rank"]) != (self.key_space, self.heap.world,
                                                           self.heap.rank):
             raise ValueError("checkpoint belongs to a different key layout or rank")
+        if ck.get("width", 1) != self.width:
+            raise ValueError("checkpoint has another value width")
         self.w.copy_(ck["w"])
+        if self.klen is not None and ck.get("klen") is not None:
+            self.klen.copy_(ck["klen"])
         if self.z is not None and ck["z"] is not None:
             self.z.copy_(ck["z"])
             self.n.copy_(ck["n"])

@@ -64,6 +64,35 @@ def main():
         torch.testing.assert_close(t.weight[:cut], ref2[:cut], rtol=2e-5, atol=2e-5)
         assert torch.equal(t.weight[cut:], b[cut:]), "refused vectors must not be written"
     assert refused >= 1, "the tail belongs to at least one rank"
+    for h in heaps:
+        h.close()
+
+    # 3. sparse kernels: silent on a consistent table; told that the store has fewer slots
+    #    than it has, they refuse the keys beyond (status PSDEV_ERR_BOUNDS on the table's
+    #    channel) and leave them alone -- no address outside an allocation is formed
+    from ps_lite_b200.parallel import SparseTable
+    key_space, nk = 1 << 14, 2000
+    heap = SymmetricHeap(65536 + 64 * nk + 4 * key_space + (1 << 20), 0, 1, device=dev)
+    st = SparseTable(heap, key_space, nk, kind="sum")
+    keys = torch.sort(torch.randperm(key_space, device=dev)[:nk]).values
+    vals = torch.randn(nk, device=dev)
+    out = st.push_pull(keys, vals).clone()
+    torch.cuda.synchronize()
+    st.check()
+    torch.testing.assert_close(out, vals)
+    st._t.slots = key_space // 2          # the lie: every address still lies inside the store
+    out = st.push_pull(keys, vals).clone()
+    torch.cuda.synchronize()
+    try:
+        st.check()
+        raise AssertionError("the sparse kernels accepted slots beyond the stated capacity")
+    except _lib.PsdevError as exc:
+        assert exc.code == -8, exc
+    low = keys < key_space // 2
+    torch.testing.assert_close(out[low], 2 * vals[low])
+    assert torch.equal(st.w[key_space // 2:][keys[~low] - key_space // 2], vals[~low]), \
+        "refused keys must keep their old values"
+    heap.close()
     print("CHECKS_OK", refused, flush=True)
 
 

@@ -57,6 +57,7 @@ def test_sparse_descriptor_is_checked_against_the_arena():
         t.keys_off, t.grads_off, t.out_off, t.pos_off, t.acc_off = keys_off, *offs[1:]
         t.w = 0x20000000                         # never dereferenced on this path
         t.kind = 0
+        t.width, t.channel, t.max_n, t.max_vals, t.slots = 1, 3, max_keys, max_keys, slots
         return t
     w = _world(heap)
     good, bad = table(offs[0]), table(heap - 64)

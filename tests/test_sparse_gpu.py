@@ -68,6 +68,60 @@ def test_sparse_push_pull_matches_oracle(cuda_device, world, kind, store):
             t.check()
 
 
+@pytest.mark.parametrize("world", [1, 4])
+@pytest.mark.parametrize("var_len", [False, True])
+def test_sparse_wide_and_dynamic_length_values(cuda_device, world, var_len):
+    """Values of width 5, and values of per-key length 1..5 packed back to back (the
+    reference's `lens`): sum handle against index_add on a dense [key_space, width] table."""
+    from ps_lite_b200.parallel import SparseTable, SymmetricHeap
+    key_space, n, width = 1 << 16, 3000, 5
+    nbytes = 65536 + 64 * n * width + 4 * width * ((key_space + world - 1) // world) + (1 << 20)
+    heaps = (SymmetricHeap.emulated(nbytes, world, device=cuda_device) if world > 1
+             else [SymmetricHeap(nbytes, 0, 1, device=cuda_device)])
+    tables = [SparseTable(h, key_space, n, kind="sum", width=width, var_len=var_len)
+              for h in heaps]
+    gen = torch.Generator(device=cuda_device)
+    gen.manual_seed(5)
+    dense = torch.zeros(key_space, width, device=cuda_device)
+    # a key always has the same length, whoever pushes it
+    key_len = torch.randint(1, width + 1, (key_space,), generator=gen, device=cuda_device)
+    for step in range(3):
+        reqs = []
+        for t in tables:
+            keys = _zipf_keys(n - 7 * step, key_space, gen, cuda_device)
+            if var_len:
+                lens = key_len[keys]
+                vals = torch.randn(int(lens.sum().item()), generator=gen, device=cuda_device)
+                t.stage(keys, vals, lens)
+            else:
+                lens = torch.full_like(keys, width)
+                vals = torch.randn(keys.numel() * width, generator=gen, device=cuda_device)
+                t.stage(keys, vals)
+            reqs.append((keys, vals, lens))
+        for t in tables:
+            t.scatter()
+        for t in tables:
+            t.apply()
+        for t in tables:
+            t.respond()
+        torch.cuda.synchronize()
+        for keys, vals, lens in reqs:
+            offs = torch.cumsum(lens, 0) - lens
+            for j in range(width):
+                m = lens > j
+                dense[keys[m], j] += vals[(offs + j)[m]]
+        for t, (keys, vals, lens) in zip(tables, reqs):
+            offs = torch.cumsum(lens, 0) - lens
+            got = t.out[: vals.numel()]
+            for j in range(width):
+                m = lens > j
+                torch.testing.assert_close(got[(offs + j)[m]], dense[keys[m], j],
+                                           rtol=1e-5, atol=1e-5)
+            if var_len:
+                assert torch.equal(t.offs[: keys.numel()], offs)
+            t.check()
+
+
 def test_key_shard_lookup(cuda_device):
     from ps_lite_b200 import _lib
     lib = _lib.device_lib()
