@@ -33,7 +33,12 @@ def zipf_keys(n, key_space, s, gen, dev):
         r = (r * 2654435761) % key_space
         keys = torch.unique(torch.cat([keys, r]))
     idx = torch.randperm(keys.numel(), generator=gen, device=dev)[:n]
-    return torch.sort(keys[idx]).values
+    picked = keys[idx].contiguous()
+    if picked.is_cuda:
+        # unsorted keys become the sorted list a push needs with the library's own radix sort
+        from ps_lite_b200.ops.keys import sort_keys
+        return sort_keys(picked, max(1, (key_space - 1).bit_length()))[0]
+    return torch.sort(picked).values
 
 
 def cpu_oracle(args):

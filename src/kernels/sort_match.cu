@@ -1,5 +1,5 @@
-// Utility kernels for key lists: radix sort of 64-bit keys (with an optional payload of
-// 32-bit indices) and ordered match (merge-join) of two sorted key lists with an assignment
+// Utility kernels for key lists: radix sort of 64-bit keys, 8 bits per pass (with an optional
+// payload of 32-bit indices) and ordered match (merge-join) of two sorted key lists with an assignment
 // operator applied to the values of the keys present in both.
 //
 // They are the device form of helpers the reference ships as headers that nothing includes
@@ -20,101 +20,141 @@ namespace psdev {
 extern std::atomic<uint64_t> g_launches;
 
 namespace sortk {
+// Least-significant-digit radix sort with 8-bit digits.  One pass = three kernels:
+//   tile_count  every CTA counts the digits of its tile of 4096 keys (warp-aggregated shared
+//               atomics) into hist[digit][tile] and adds them to the pass's 256 digit totals;
+//   tile_scan   one CTA per digit: exclusive prefix of that digit's row over the tiles, plus
+//               the number of keys with smaller digits -> where each (digit, tile) group starts;
+//   scatter     every CTA re-reads its tile, ranks each key among the keys of the same digit
+//               in the tile, in input order (the sort is stable), and stores key and payload at
+//               group start + rank.
+// ceil(key_bits / 8) passes: a caller that knows its keys are below 2^30 pays four passes,
+// not eight.
 constexpr int kThreads = 256;
-constexpr int kItems = 8;                  // keys per thread, contiguous
-constexpr int kTile = kThreads * kItems;   // keys per block
-constexpr int kRadixBits = 4;
+constexpr int kWarps = kThreads / 32;
+constexpr int kItems = 16;                 // keys per thread
+constexpr int kTile = kThreads * kItems;   // keys per CTA
+constexpr int kRadixBits = 8;
 constexpr int kDigits = 1 << kRadixBits;
 
-__device__ __forceinline__ int digit_of(unsigned long long k, int shift) {
-  return (int)((k >> shift) & (kDigits - 1));
+__device__ __forceinline__ unsigned int digit_of(unsigned long long k, int shift) {
+  return (unsigned int)((k >> shift) & (kDigits - 1));
+}
+__device__ __forceinline__ unsigned int lanemask_lt() {
+  unsigned int m;
+  asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
+  return m;
 }
 
-// counts[d * nblocks + b] = number of keys of block b whose digit is d
-__global__ void histogram_kernel(const unsigned long long* keys, long long n, int shift,
-                                 unsigned int* counts, int nblocks) {
+// hist[d * ntiles + tile] = keys of the tile with digit d; totals[d] += the same
+__global__ void __launch_bounds__(kThreads)
+    tile_count_kernel(const unsigned long long* keys, long long n, int shift, unsigned int* hist,
+                      unsigned int* totals, int ntiles) {
   __shared__ unsigned int s[kDigits];
-  if (threadIdx.x < kDigits) s[threadIdx.x] = 0;
+  s[threadIdx.x] = 0;
   __syncthreads();
-  const long long base = (long long)blockIdx.x * kTile + (long long)threadIdx.x * kItems;
-#pragma unroll
-  for (int i = 0; i < kItems; ++i)
-    if (base + i < n) atomicAdd(&s[digit_of(keys[base + i], shift)], 1u);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long base = (long long)blockIdx.x * kTile + (long long)warp * (32 * kItems) + lane;
+#pragma unroll 4
+  for (int j = 0; j < kItems; ++j) {
+    const long long i = base + j * 32;
+    const bool valid = i < n;
+    // lanes past the end vote with a digit no key can have
+    const unsigned int d = valid ? digit_of(keys[i], shift) : (unsigned int)kDigits;
+    const unsigned int same = __match_any_sync(0xffffffffu, d);
+    if (valid && (same & lanemask_lt()) == 0) atomicAdd(&s[d], (unsigned int)__popc(same));
+  }
   __syncthreads();
-  if (threadIdx.x < kDigits) counts[threadIdx.x * nblocks + blockIdx.x] = s[threadIdx.x];
+  const unsigned int c = s[threadIdx.x];
+  hist[(size_t)threadIdx.x * ntiles + blockIdx.x] = c;
+  if (c) atomicAdd(&totals[threadIdx.x], c);
 }
 
-// exclusive prefix sum over `len` counters, in place (one block; len = 16 * nblocks)
-__global__ void scan_kernel(unsigned int* counts, int len) {
+// One CTA per digit: hist row -> exclusive prefix over the tiles + keys with smaller digits.
+__global__ void __launch_bounds__(1024)
+    tile_scan_kernel(unsigned int* hist, const unsigned int* totals, int ntiles) {
   __shared__ unsigned int s[1024];
   __shared__ unsigned int carry;
-  if (threadIdx.x == 0) carry = 0;
+  const int d = blockIdx.x;
+  // keys with a smaller digit
+  unsigned int below = 0;
+  for (int j = threadIdx.x; j < d; j += 1024) below += totals[j];
+  s[threadIdx.x] = below;
   __syncthreads();
-  for (int base = 0; base < len; base += 1024) {
+  for (int off = 512; off > 0; off >>= 1) {
+    if (threadIdx.x < off) s[threadIdx.x] += s[threadIdx.x + off];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) carry = s[0];
+  __syncthreads();
+  unsigned int* row = hist + (size_t)d * ntiles;
+  for (int base = 0; base < ntiles; base += 1024) {
     const int i = base + threadIdx.x;
-    const unsigned int v = i < len ? counts[i] : 0u;
+    const unsigned int v = i < ntiles ? row[i] : 0u;
+    __syncthreads();
     s[threadIdx.x] = v;
     __syncthreads();
     for (int off = 1; off < 1024; off <<= 1) {
-      unsigned int t = threadIdx.x >= off ? s[threadIdx.x - off] : 0u;
+      const unsigned int t = threadIdx.x >= off ? s[threadIdx.x - off] : 0u;
       __syncthreads();
       s[threadIdx.x] += t;
       __syncthreads();
     }
-    if (i < len) counts[i] = carry + s[threadIdx.x] - v;
+    if (i < ntiles) row[i] = carry + s[threadIdx.x] - v;
     __syncthreads();
     if (threadIdx.x == 1023) carry += s[1023];
-    __syncthreads();
   }
 }
 
-// stable scatter of one 4-bit digit
-__global__ void scatter_kernel(const unsigned long long* keys_in, unsigned long long* keys_out,
-                               const unsigned int* pay_in, unsigned int* pay_out, long long n,
-                               int shift, const unsigned int* offsets, int nblocks) {
-  // per-thread digit counts, then an exclusive scan over threads for every digit
-  __shared__ unsigned short cnt[kDigits][kThreads + 1];
-  const long long base = (long long)blockIdx.x * kTile + (long long)threadIdx.x * kItems;
-  unsigned long long k[kItems];
-  int d[kItems];
-  unsigned short mine[kDigits];
+// Stable scatter of one 8-bit digit.
+__global__ void __launch_bounds__(kThreads)
+    scatter_kernel(const unsigned long long* keys_in, unsigned long long* keys_out,
+                   const unsigned int* pay_in, unsigned int* pay_out, long long n, int shift,
+                   const unsigned int* offsets, int ntiles) {
+  // cnt[w][d]: first the number of keys with digit d seen so far by warp w, afterwards the
+  // output position of that warp's first key with digit d
+  __shared__ unsigned int cnt[kWarps][kDigits];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
-  for (int j = 0; j < kDigits; ++j) mine[j] = 0;
-#pragma unroll
-  for (int i = 0; i < kItems; ++i) {
-    d[i] = -1;
-    if (base + i < n) {
-      k[i] = keys_in[base + i];
-      d[i] = digit_of(k[i], shift);
-      ++mine[d[i]];
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < kDigits; ++j) cnt[j][threadIdx.x] = mine[j];
+  for (int w = 0; w < kWarps; ++w) cnt[w][threadIdx.x] = 0;
   __syncthreads();
-  // 16 warps-worth of work: thread t < 16 scans digit t over the 256 threads
-  if (threadIdx.x < kDigits) {
-    unsigned short run = 0;
-    for (int t = 0; t < kThreads; ++t) {
-      const unsigned short c = cnt[threadIdx.x][t];
-      cnt[threadIdx.x][t] = run;
+  const long long base = (long long)blockIdx.x * kTile + (long long)warp * (32 * kItems) + lane;
+  unsigned long long k[kItems];
+  unsigned short rank[kItems];
+#pragma unroll
+  for (int j = 0; j < kItems; ++j) {
+    const long long i = base + j * 32;
+    const bool valid = i < n;
+    k[j] = valid ? keys_in[i] : ~0ull;
+    const unsigned int d = valid ? digit_of(k[j], shift) : (unsigned int)kDigits;
+    const unsigned int same = __match_any_sync(0xffffffffu, d);
+    const unsigned int before = __popc(same & lanemask_lt());
+    unsigned int seen = 0;
+    if (valid) seen = cnt[warp][d];
+    __syncwarp();
+    if (valid && before == 0) cnt[warp][d] = seen + __popc(same);
+    __syncwarp();
+    rank[j] = (unsigned short)(seen + before);
+  }
+  __syncthreads();
+  {
+    // digit threadIdx.x: where each warp's keys of that digit go
+    unsigned int run = offsets[(size_t)threadIdx.x * ntiles + blockIdx.x];
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const unsigned int c = cnt[w][threadIdx.x];
+      cnt[w][threadIdx.x] = run;
       run += c;
     }
   }
   __syncthreads();
-  unsigned int pos[kDigits];
 #pragma unroll
-  for (int j = 0; j < kDigits; ++j)
-    pos[j] = offsets[j * nblocks + blockIdx.x] + cnt[j][threadIdx.x];
-#pragma unroll
-  for (int i = 0; i < kItems; ++i) {
-    if (d[i] >= 0) {
-      unsigned int p = 0;
-#pragma unroll
-      for (int j = 0; j < kDigits; ++j)
-        if (j == d[i]) p = pos[j]++;
-      keys_out[p] = k[i];
-      if (pay_in) pay_out[p] = pay_in[base + i];
+  for (int j = 0; j < kItems; ++j) {
+    const long long i = base + j * 32;
+    if (i < n) {
+      const unsigned int p = cnt[warp][digit_of(k[j], shift)] + rank[j];
+      keys_out[p] = k[j];
+      if (pay_in) pay_out[p] = pay_in[i];
     }
   }
 }
@@ -184,10 +224,11 @@ extern "C" {
 
 // Bytes of scratch psdev_sort_keys needs for n keys (with or without a payload).
 size_t psdev_sort_scratch_bytes(int64_t n, int with_payload) {
-  const int64_t nblocks = (n + kTile - 1) / kTile;
+  const int64_t ntiles = (n + kTile - 1) / kTile;
   size_t b = ((size_t)n * 8 + 255) & ~size_t(255);                 // second key buffer
   if (with_payload) b += (((size_t)n * 4 + 255) & ~size_t(255));   // second payload buffer
-  b += (((size_t)nblocks * kDigits * 4 + 255) & ~size_t(255));     // digit counters
+  b += (((size_t)ntiles * kDigits * 4 + 255) & ~size_t(255));      // digit counts per tile
+  b += 8 * kDigits * 4;                                            // digit totals per pass
   return b + 256;
 }
 
@@ -203,7 +244,7 @@ int psdev_sort_keys(uint64_t* keys, uint32_t* perm, int64_t n, int key_bits, voi
   if (!scratch || scratch_bytes < psdev_sort_scratch_bytes(n, perm != nullptr))
     return PSDEV_ERR_ARG;
   cudaStream_t s = (cudaStream_t)stream;
-  const int nblocks = (int)((n + kTile - 1) / kTile);
+  const int ntiles = (int)((n + kTile - 1) / kTile);
   char* p = static_cast<char*>(scratch);
   p = reinterpret_cast<char*>(((uintptr_t)p + 255) & ~uintptr_t(255));
   unsigned long long* alt = reinterpret_cast<unsigned long long*>(p);
@@ -213,28 +254,31 @@ int psdev_sort_keys(uint64_t* keys, uint32_t* perm, int64_t n, int key_bits, voi
     alt_pay = reinterpret_cast<unsigned int*>(p);
     p += ((size_t)n * 4 + 255) & ~size_t(255);
     iota_kernel<<<296, 256, 0, s>>>(perm, n);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
   }
-  unsigned int* counts = reinterpret_cast<unsigned int*>(p);
+  unsigned int* hist = reinterpret_cast<unsigned int*>(p);
+  p += ((size_t)ntiles * kDigits * 4 + 255) & ~size_t(255);
+  unsigned int* totals = reinterpret_cast<unsigned int*>(p);
+  const int passes = (key_bits + kRadixBits - 1) / kRadixBits;
+  cudaMemsetAsync(totals, 0, (size_t)passes * kDigits * 4, s);
   unsigned long long* in = reinterpret_cast<unsigned long long*>(keys);
   unsigned long long* out = alt;
   unsigned int* pin = perm;
   unsigned int* pout = alt_pay;
-  int passes = (key_bits + kRadixBits - 1) / kRadixBits;
-  if (passes & 1) ++passes;  // an even number of passes leaves the result in `keys`
   for (int pass = 0; pass < passes; ++pass) {
     const int shift = pass * kRadixBits;
-    if (shift >= 64) {
-      // padding pass beyond the key width: plain copy back
-      cudaMemcpyAsync(out, in, (size_t)n * 8, cudaMemcpyDeviceToDevice, s);
-      if (perm) cudaMemcpyAsync(pout, pin, (size_t)n * 4, cudaMemcpyDeviceToDevice, s);
-    } else {
-      histogram_kernel<<<nblocks, kThreads, 0, s>>>(in, n, shift, counts, nblocks);
-      scan_kernel<<<1, 1024, 0, s>>>(counts, nblocks * kDigits);
-      scatter_kernel<<<nblocks, kThreads, 0, s>>>(in, out, pin, pout, n, shift, counts, nblocks);
-      g_launches.fetch_add(3, std::memory_order_relaxed);
-    }
+    unsigned int* tot = totals + pass * kDigits;
+    tile_count_kernel<<<ntiles, kThreads, 0, s>>>(in, n, shift, hist, tot, ntiles);
+    tile_scan_kernel<<<kDigits, 1024, 0, s>>>(hist, tot, ntiles);
+    scatter_kernel<<<ntiles, kThreads, 0, s>>>(in, out, pin, pout, n, shift, hist, ntiles);
+    g_launches.fetch_add(3, std::memory_order_relaxed);
     unsigned long long* t = in; in = out; out = t;
     unsigned int* tp = pin; pin = pout; pout = tp;
+  }
+  if (passes & 1) {
+    // an odd number of passes leaves the result in the scratch buffers
+    cudaMemcpyAsync(keys, in, (size_t)n * 8, cudaMemcpyDeviceToDevice, s);
+    if (perm) cudaMemcpyAsync(perm, pin, (size_t)n * 4, cudaMemcpyDeviceToDevice, s);
   }
   return (int)cudaGetLastError();
 }

@@ -1,7 +1,8 @@
 """The checks variant of the device library (-DPSDEV_CHECKS): the dense kernel verifies every
 index against the table, the owner's state arrays and the arena, the sparse kernels every slot
 index against the store's capacity and every value offset against the request buffers; a bad
-index is recorded as PSDEV_ERR_BOUNDS and the access is skipped instead of performed.  The variant is chosen per process, so the test
+index is recorded as PSDEV_ERR_BOUNDS and the access is skipped instead of performed.  The
+variant is chosen per process, so the test
 body runs in a child (tests/checks_build_child.py).  Nothing here touches memory outside an
 allocation: the refused indices are made by telling the kernel that the table is shorter than
 it really is."""
