@@ -69,8 +69,12 @@ def run_pushpull(args):
     nbytes = n * isz
     # ps::Start from the launcher's environment, then the device plane: arena handles and
     # barriers travel over the parameter server's own control plane (no collective library)
-    ctx = kvstore.init(heap_bytes=2 * nbytes + (64 << 20),
-                       slice_bytes=int(args.slice_mb * (1 << 20)))
+    heap_bytes = 2 * nbytes + (64 << 20)
+    if not args.no_extras:
+        # room for the extra records: the 1 GiB point of the sweep, the sparse table's
+        # accumulator (4 bytes per key of the rank's range) and the models' buffers
+        heap_bytes += (2 << 30) + (4 << 30) // world_hint + (4 << 30)
+    ctx = kvstore.init(heap_bytes=heap_bytes, slice_bytes=int(args.slice_mb * (1 << 20)))
     rank, world, dev = ctx.rank, ctx.world, ctx.device
     local = dev.index or 0
     reporter = bootstrap.launcher_rank() == 0

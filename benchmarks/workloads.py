@@ -23,48 +23,52 @@ def _setup(args):
     return rank, world, dev
 
 
-def run(args):
-    from ps_lite_b200 import _lib, kvstore
+def _build(workload, batch, world, dev):
+    """Model, server-side optimizer, batch factory and forward function of a workload."""
     from ps_lite_b200.parallel import ServerOptimizer
-    from ps_lite_b200.parallel.optimizer import DistributedOptimizer
-    from ps_lite_b200.utils.timing import ClockSampler, max_over_ranks
-    rank, world, dev = _setup(args)
-    torch.manual_seed(0)
-    torch.backends.cudnn.benchmark = True
-    if args.workload == "resnet50":
+    if workload == "resnet50":
         from ps_lite_b200.models.resnet import ResNet50
-        batch = args.batch or 256
+        batch = batch or 256
         model = ResNet50().to(dev).to(memory_format=torch.channels_last)
         sopt = ServerOptimizer("momentum", lr=0.01, momentum=0.9, scale=1.0 / world)
         make = lambda: (torch.randn(batch, 3, 224, 224).pin_memory(),
                         torch.randint(0, 1000, (batch,)).pin_memory())
-        unit, per_step = "img/s", batch
-        metric = "resnet50_train_img_per_s"
+        unit, metric = "img/s", "resnet50_train_img_per_s"
 
-        def fwd(x, y):
+        def fwd(net, x, y):
             with torch.autocast("cuda", dtype=torch.bfloat16):
-                out = model(x.contiguous(memory_format=torch.channels_last))
+                out = net(x.contiguous(memory_format=torch.channels_last))
             return F.cross_entropy(out.float(), y)
     else:
         from ps_lite_b200.models.bert import BertLarge
-        batch, seq = args.batch or 32, 512
+        batch, seq = batch or 32, 512
         model = BertLarge().to(dev).to(torch.bfloat16)
         sopt = ServerOptimizer("adam", lr=1e-4, eps=1e-6, scale=1.0 / world)
         make = lambda: (torch.randint(0, 30522, (batch, seq)).pin_memory(),
                         torch.randint(0, 30522, (batch, seq)).pin_memory())
-        unit, per_step = "seq/s", batch
-        metric = "bert_large_train_seq_per_s"
+        unit, metric = "seq/s", "bert_large_train_seq_per_s"
 
-        def fwd(x, y):
-            return model(x, y)
+        def fwd(net, x, y):
+            return net(x, y)
+    return model, sopt, make, fwd, unit, metric, batch
+
+
+def measure_ps(ctx, workload, steps, warmup, batch=0, ctas=0, sample_clocks=False):
+    """Trains `workload` for `warmup` + `steps` steps through the server-side optimizer of an
+    existing context; returns the record (a dict) on every rank.  One step = pinned-host batch
+    copied in, forward, backward with gradient slices pushed as they appear, pull, loss read
+    back."""
+    from ps_lite_b200 import _lib
+    from ps_lite_b200.parallel.optimizer import DistributedOptimizer
+    from ps_lite_b200.utils.timing import ClockSampler
+    rank, world, dev = ctx.rank, ctx.world, ctx.device
+    torch.manual_seed(0)
+    torch.backends.cudnn.benchmark = True
+    model, sopt, make, fwd, unit, metric, per_step = _build(workload, batch, world, dev)
     nparam = sum(p.numel() for p in model.parameters())
-    if getattr(args, "trainer", "ps") == "ddp":
-        return _run_ddp(args, model, fwd, make, rank, world, dev, metric, unit, per_step, nparam)
-    ctx = kvstore.init(heap_bytes=nparam * 8 + (256 << 20), device=dev)
-    rank, world = ctx.rank, ctx.world
-    fused = args.workload == "bert"
+    fused = workload == "bert"
     dopt = DistributedOptimizer(model.parameters(), ctx.heap, sopt, grad_dtype=torch.bfloat16,
-                                num_ctas=args.ctas or 32,
+                                num_ctas=ctas or 32, channel=ctx.new_channel(),
                                 publish_params=[model.layers[0].qkv.weight] if fused else ())
     if fused:
         # the first GEMM that consumes pulled weights (layer-0 QKV) pulls them itself
@@ -79,44 +83,66 @@ def run(args):
         x = hx.to(dev, non_blocking=True)   # host -> device copy of this step's inputs
         y = hy.to(dev, non_blocking=True)
         dopt.zero_grad()
-        loss = fwd(x, y)
+        loss = fwd(model, x, y)
         loss.backward()
         dopt.step()
         return loss
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step()
     torch.cuda.synchronize()
     ctx.host_barrier()
-    sampler = ClockSampler(dev.index)
-    if rank == 0:
+    sampler = ClockSampler(dev.index) if sample_clocks else None
+    if sampler:
         sampler.start()
     l0 = lib.psdev_launch_count()
+    slices0 = dopt.launched_slices
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     losses = []
-    for _ in range(args.steps):
+    for _ in range(steps):
         losses.append(float(step().item()))   # device -> host read of the step's loss
     e1.record()
     torch.cuda.synchronize()
-    ms = max_over_ranks(e0.elapsed_time(e1), dev) / args.steps
-    clocks = sampler.stop() if rank == 0 else None
+    ms = ctx.max_over_ranks(e0.elapsed_time(e1)) / steps
+    clocks = sampler.stop() if sampler else None
     dopt.check()
     value = world * per_step / (ms * 1e-3)
-    if rank == 0:
-        print(json.dumps({
-            "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 3),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "impl": "ours",
-            "config": {"model": args.workload, "global_batch": per_step * world,
-                       "parameters": nparam, "parallelism": f"dp{world}, server-side optimizer",
-                       "slices_per_step": dopt.launched_slices // max(1, dopt.steps),
-                       "pull_fused_with_first_gemm": bool(fused),
-                       "timing": "end to end: pinned-host inputs copied in and loss read back "
-                                 "every step"},
-            "loss_first_last": [losses[0], losses[-1]], "clocks": clocks,
-            "gpu_launches": int(lib.psdev_launch_count() - l0)}), flush=True)
+    rec = {
+        "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world,
+        "steps": steps, "warmup": max(warmup, 3), "ms_per_step": round(ms, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "impl": "ours",
+        "config": {"model": workload, "global_batch": per_step * world,
+                   "parameters": nparam, "parallelism": f"dp{world}, server-side optimizer",
+                   "slices_per_step": (dopt.launched_slices - slices0) // max(1, steps),
+                   "pull_fused_with_first_gemm": bool(fused),
+                   "timing": "end to end: pinned-host inputs copied in and loss read back "
+                             "every step"},
+        "loss_first_last": [losses[0], losses[-1]], "clocks": clocks,
+        "gpu_launches": int(lib.psdev_launch_count() - l0)}
+    dopt.close()
+    del model, dopt
+    torch.cuda.empty_cache()
+    return rec
+
+
+def run(args):
+    from ps_lite_b200 import kvstore
+    rank, world, dev = _setup(args)
+    if getattr(args, "trainer", "ps") == "ddp":
+        model, _sopt, make, fwd, unit, metric, per_step = _build(args.workload, args.batch,
+                                                                 world, dev)
+        nparam = sum(p.numel() for p in model.parameters())
+        torch.manual_seed(0)
+        torch.backends.cudnn.benchmark = True
+        return _run_ddp(args, model, fwd, make, rank, world, dev, metric, unit, per_step, nparam)
+    nparam_bound = 400_000_000 if args.workload == "bert" else 30_000_000
+    ctx = kvstore.init(heap_bytes=nparam_bound * 8 + (256 << 20), device=dev)
+    rec = measure_ps(ctx, args.workload, args.steps, args.warmup, args.batch, args.ctas,
+                     sample_clocks=ctx.rank == 0)
+    if ctx.rank == 0:
+        print(json.dumps(rec), flush=True)
     kvstore.finalize()
 
 
@@ -134,22 +160,13 @@ def _run_ddp(args, model, fwd, make, rank, world, dev, metric, unit, per_step, n
     else:
         opt = torch.optim.Adam(model.parameters(), lr=1e-4, eps=1e-6, fused=True)
     hx, hy = make()
-    if net is not model:
-        # route the forward through the DDP wrapper so that its hooks fire
-        if args.workload == "resnet50":
-            def fwd(x, y):  # noqa: F811
-                with torch.autocast("cuda", dtype=torch.bfloat16):
-                    out = net(x.contiguous(memory_format=torch.channels_last))
-                return F.cross_entropy(out.float(), y)
-        else:
-            def fwd(x, y):  # noqa: F811
-                return net(x, y)
+    # (the forward goes through the DDP wrapper so that its hooks fire)
 
     def step():
         x = hx.to(dev, non_blocking=True)
         y = hy.to(dev, non_blocking=True)
         opt.zero_grad(set_to_none=True)
-        loss = fwd(x, y)
+        loss = fwd(net, x, y)
         loss.backward()
         opt.step()
         return loss

@@ -166,6 +166,15 @@ class DenseTable:
             # nobody writes into a peer's region before that peer has cleared it
             heap.barrier()
 
+    def free(self) -> None:
+        """Give the table's heap buffers back (every rank, in the same order as the other
+        ranks' calls); the table must not be used afterwards."""
+        for off in (self.grad_off, self.weight_off, self.gscale_off,
+                    getattr(self, "ll_off", 0)):
+            if off:
+                self.heap.free(off)
+        self.grad_off = self.weight_off = self.gscale_off = self.ll_off = 0
+
     def stage_int8(self, grad: torch.Tensor, begin: int = 0) -> None:
         """Compress an fp32 gradient into this table's int8 gradient buffer starting at element
         ``begin`` (a multiple of 256): values plus one scale per 256 (the block-scale filter)."""

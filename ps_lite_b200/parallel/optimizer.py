@@ -184,6 +184,15 @@ class DistributedOptimizer:
     def check(self) -> None:
         self.table.check()
 
+    def close(self) -> None:
+        """Detach from the model and give the table's buffers back to the heap.  The
+        parameters keep pointing at the pulled-weight buffer: drop the model too."""
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+        torch.cuda.synchronize(self.heap.device)
+        self.table.free()
+
     def offset_of(self, param: torch.nn.Parameter) -> int:
         for p, o in zip(self.params, self.offsets):
             if p is param:

@@ -1,6 +1,6 @@
-// Utility kernels for key lists: radix sort of 64-bit keys, 8 bits per pass (with an optional
-// payload of 32-bit indices) and ordered match (merge-join) of two sorted key lists with an assignment
-// operator applied to the values of the keys present in both.
+// Utility kernels for key lists: radix sort of 64-bit keys, 8 bits per pass (with an
+// optional payload of 32-bit indices) and ordered match (merge-join) of two sorted key lists
+// with an assignment operator applied to the values of the keys present in both.
 //
 // They are the device form of helpers the reference ships as headers that nothing includes
 // and that do not compile as written: ParallelSort (include/ps/internal/parallel_sort.h:23-55,

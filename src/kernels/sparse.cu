@@ -68,6 +68,11 @@ struct SparseArgs {
 __device__ __forceinline__ char* heap(const SparseArgs& a, int r) {
   return reinterpret_cast<char*>(a.base[r]);
 }
+__device__ __forceinline__ long long ld_volatile_s64(const long long* p) {
+  long long v;
+  asm volatile("ld.volatile.global.s64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ void note_bounds(const SparseArgs& a) {
   atomicMin(&ctrl_of(a.base[a.rank])->status[a.channel], (int)PSDEV_ERR_BOUNDS);
 }
@@ -275,9 +280,7 @@ __global__ void sparse_apply_kernel(const __grid_constant__ SparseArgs a) {
     float* acc = reinterpret_cast<float*>(heap(a, a.rank) + a.acc_off);
     for (int r = 0; r < a.world; ++r) {
       const long long* pos = reinterpret_cast<const long long*>(heap(a, r) + a.pos_off);
-      long long lo, hi;
-      asm volatile("ld.volatile.global.s64 %0, [%1];" : "=l"(lo) : "l"(pos + a.rank) : "memory");
-      asm volatile("ld.volatile.global.s64 %0, [%1];" : "=l"(hi) : "l"(pos + a.rank + 1) : "memory");
+      const long long lo = ld_volatile_s64(pos + a.rank), hi = ld_volatile_s64(pos + a.rank + 1);
 #ifdef PSDEV_CHECKS
       if (lo < 0 || hi < lo || hi > a.max_n) {
         if (threadIdx.x == 0 && blockIdx.x == 0) note_bounds(a);
@@ -324,9 +327,7 @@ __global__ void sparse_respond_kernel(const __grid_constant__ SparseArgs a) {
       int r = a.rank + rr;
       if (r >= a.world) r -= a.world;
       const long long* pos = reinterpret_cast<const long long*>(heap(a, r) + a.pos_off);
-      long long lo, hi;
-      asm volatile("ld.volatile.global.s64 %0, [%1];" : "=l"(lo) : "l"(pos + a.rank) : "memory");
-      asm volatile("ld.volatile.global.s64 %0, [%1];" : "=l"(hi) : "l"(pos + a.rank + 1) : "memory");
+      const long long lo = ld_volatile_s64(pos + a.rank), hi = ld_volatile_s64(pos + a.rank + 1);
 #ifdef PSDEV_CHECKS
       if (lo < 0 || hi < lo || hi > a.max_n) {
         if (threadIdx.x == 0 && blockIdx.x == 0) note_bounds(a);
@@ -429,7 +430,8 @@ int psdev_key_shard_lookup(const uint64_t* keys, int64_t n, uint64_t range, int 
 // offs[n] = number of values (device pointers).
 int psdev_lens_to_offsets(const int32_t* lens, int64_t n, int64_t* offs, void* stream) {
   if (!lens || !offs || n < 0) return PSDEV_ERR_ARG;
-  lens_scan_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(lens, n, reinterpret_cast<long long*>(offs));
+  lens_scan_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(lens, n,
+                                                         reinterpret_cast<long long*>(offs));
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return (int)cudaGetLastError();
 }
