@@ -115,6 +115,8 @@ class DenseTable:
         self.optimizer = optimizer or ServerOptimizer("sum")
         self.channel, self.num_ctas = int(channel), int(num_ctas)
         self.step = 0
+        self._opt_key, self._opt_cached = None, None
+        self._default_timeout = default_timeout_s()
         # NVSwitch multicast path: on by default from four ranks up when the heap has a
         # multicast alias (with two ranks plain peer accesses move fewer bytes per link)
         if nvls is None:
@@ -220,9 +222,9 @@ class DenseTable:
         end = self.n if end is None else end
         if op & _lib.OP_PUSH and opt_step:
             self.step += 1
-        o = self.optimizer.to_struct(max(self.step, 1))
+        o = self._opt_struct()
         s = stream or torch.cuda.current_stream(self.heap.device)
-        tmo = int((timeout_s if timeout_s is not None else default_timeout_s()) * 1e9)
+        tmo = int((timeout_s if timeout_s is not None else self._default_timeout) * 1e9)
         if _nvtx_enabled():
             torch.cuda.nvtx.range_push(f"{_OP_NAMES.get(op, 'ps.op')}[{begin}:{end}]")
         # measured on 8 GPUs: the multicast path wins up to 256 MiB per request (855 vs 741
@@ -236,6 +238,17 @@ class DenseTable:
         if _nvtx_enabled():
             torch.cuda.nvtx.range_pop()
         _lib.check(rc, "psdev_dense_op")
+
+    def _opt_struct(self) -> _lib.Opt:
+        """The handle's parameters for the current step (rebuilt only when something changed:
+        small requests are launch-bound, and building the structure costs microseconds)."""
+        p = self.optimizer
+        key = (max(self.step, 1) if p.kind in ("adam", "adamw") else 0, p.kind, p.lr, p.momentum,
+               p.weight_decay, p.beta1, p.beta2, p.eps, p.scale, p.user_kind, p.user)
+        if key != self._opt_key:
+            self._opt_key = key
+            self._opt_cached = p.to_struct(max(self.step, 1))
+        return self._opt_cached
 
     def push(self, begin: int = 0, end: Optional[int] = None, *, sync: bool = True, stream=None,
              timeout_s=None, opt_step: bool = True, publish: bool = False) -> None:
@@ -309,8 +322,8 @@ class DenseTable:
         with torch.cuda.stream(s):
             self._seg_dev[: len(flat)].copy_(self._seg_host[: len(flat)], non_blocking=True)
         self._seg_free.record(s)
-        o = self.optimizer.to_struct(max(self.step, 1))
-        tmo = int((timeout_s if timeout_s is not None else default_timeout_s()) * 1e9)
+        o = self._opt_struct()
+        tmo = int((timeout_s if timeout_s is not None else self._default_timeout) * 1e9)
         rc = self.heap.lib.psdev_dense_op_multi(
             C.byref(self._world), C.byref(self._table), op, self._seg_dev.data_ptr(),
             len(segments), self._sched_dev.data_ptr(), C.byref(o), self.channel, self.num_ctas,

@@ -1216,45 +1216,51 @@ static int launch_ex(GemmKernel k, const Args& a, const CUtensorMap& tx, const C
 template <int BN>
 static int launch(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, int grid,
                   cudaStream_t s) {
-  static bool attr_set[64] = {};
+  // (set once per device; the attribute call is idempotent, the flag is atomic because the
+  // entry points may be used from several host threads)
+  static std::atomic<bool> attr_set[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!attr_set[dev & 63]) {
+  if (!attr_set[dev & 63].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(pull_gemm_kernel<BN>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg<BN>::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    attr_set[dev & 63] = true;
+    attr_set[dev & 63].store(true, std::memory_order_release);
   }
   return launch_ex(pull_gemm_kernel<BN>, a, tx, tw, grid, kThreads, Cfg<BN>::kSmemBytes, 1, s);
 }
 
 static int launch256(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, int grid,
                      cudaStream_t s) {
-  static bool attr_set[64] = {};
+  // (set once per device; the attribute call is idempotent, the flag is atomic because the
+  // entry points may be used from several host threads)
+  static std::atomic<bool> attr_set[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!attr_set[dev & 63]) {
+  if (!attr_set[dev & 63].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(pull_gemm256_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg256::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    attr_set[dev & 63] = true;
+    attr_set[dev & 63].store(true, std::memory_order_release);
   }
   return launch_ex(pull_gemm256_kernel, a, tx, tw, grid, kThreads256, Cfg256::kSmemBytes, 1, s);
 }
 
 static int launch_pair(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, int grid,
                        cudaStream_t s) {
-  static bool attr_set[64] = {};
+  // (set once per device; the attribute call is idempotent, the flag is atomic because the
+  // entry points may be used from several host threads)
+  static std::atomic<bool> attr_set[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!attr_set[dev & 63]) {
+  if (!attr_set[dev & 63].load(std::memory_order_acquire)) {
     cudaError_t e = cudaFuncSetAttribute(pull_gemm_pair_kernel,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          CfgPair::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    attr_set[dev & 63] = true;
+    attr_set[dev & 63].store(true, std::memory_order_release);
   }
   return launch_ex(pull_gemm_pair_kernel, a, tx, tw, grid, kThreads, CfgPair::kSmemBytes, 2, s);
 }
@@ -1508,20 +1514,21 @@ extern "C" int psdev_gemm_bf16_noalloc(const void* x, const void* w, void* c, in
   int rc = noalloc_scratch(&scratch);
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  // the array keeps the previous call's contents: counters and error word start at zero
-  cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(Scratch), s);
-  if (e != cudaSuccess) return (int)e;
   Args a{};
   a.M = M; a.N = N; a.K = K;
   a.c = static_cast<__nv_bfloat16*>(c);
   a.scratch = scratch;
   a.timeout_ns = timeout_ns ? timeout_ns : 2000000000ull;
   a.fused = 0;
+  // everything that can fail on the host comes before the first operation on the stream
   CUtensorMap tx, tw;
   rc = make_tmap(&tx, x, M, K, BM);
   if (rc) return rc;
   rc = make_tmap(&tw, w, N, K, BN);
   if (rc) return rc;
+  // the array keeps the previous call's contents: counters and error word start at zero
+  cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(Scratch), s);
+  if (e != cudaSuccess) return (int)e;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

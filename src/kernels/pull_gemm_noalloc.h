@@ -35,7 +35,10 @@
  * Arguments as for psdev_gemm_bf16 (c[M,N] = x[M,K] * w[N,K]^T, row-major bf16, 16-byte
  * aligned, N and K multiples of 8).  `status_dev`, if not NULL, is a device pointer to an
  * int32 that receives, in stream order after the kernel, 0 or the negative psdev error the
- * kernel recorded (for instance PSDEV_ERR_TIMEOUT_PIPE).
+ * kernel recorded (for instance PSDEV_ERR_TIMEOUT_PIPE).  It is the only way to learn of an
+ * error inside the kernel: the next call clears the array, error word included, and
+ * psdev_gemm_status reads the other entry points' scratch block, not this one.  A caller that
+ * passes NULL gives that information up.
  * Returns 0, a negative psdev error, or a positive cudaError_t.
  */
 #ifndef PS_KERNELS_PULL_GEMM_NOALLOC_H_
