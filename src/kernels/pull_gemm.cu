@@ -74,7 +74,21 @@ struct Args {
   unsigned long long weight_off;  // heap offset of the table's weight buffer
   long long w_elem_off;           // first element of W inside the table
   long long blk;
+  int tile_group;  // panels per group of the tile order (1 = panel-major)
 };
+
+// Tile order.  Panel-major order (tn = t / tiles_m) makes every CTA of a round read the same
+// panel of W at the same time, which lands on a few L2 slices.  With group > 1 the tiles are
+// taken in groups of `group` panels with the panel index running fastest, so that a round
+// spreads over `group` panels of W and about (CTAs / group) blocks of X.
+__device__ __forceinline__ void tile_order(long long t, long long tiles_m, long long tiles_n,
+                                           long long group, int* tn, int* tm) {
+  const long long per_group = tiles_m * group;
+  const long long g = t / per_group, r = t % per_group;
+  const long long width = (g + 1) * group <= tiles_n ? group : tiles_n - g * group;
+  *tn = (int)(g * group + r % width);
+  *tm = (int)(r / width);
+}
 
 template <int BN>
 struct Cfg {
@@ -487,7 +501,8 @@ __device__ void gemm_role(const Args& a, const CUtensorMap* tmap_x, const CUtens
       int last_panel = -1;
       bool ok = true;
       for (long long t = gemm_idx; t < num_tiles && ok; t += num_gemm_ctas) {
-        const int tn = (int)(t / tiles_m), tm = (int)(t % tiles_m);  // panel-major order
+        int tn, tm;
+        tile_order(t, tiles_m, tiles_n, a.tile_group > 1 ? a.tile_group : 1, &tn, &tm);
         if (a.fused && tn != last_panel) {
           ok = wait_panel(a, tn, abort_flag);
           if (!ok) break;
@@ -568,7 +583,8 @@ __device__ void gemm_role(const Args& a, const CUtensorMap* tmap_x, const CUtens
     long long local = 0;
     bool ok = true;
     for (long long t = gemm_idx; t < num_tiles && ok; t += num_gemm_ctas, ++local) {
-      const int tn = (int)(t / tiles_m), tm = (int)(t % tiles_m);
+      int tn, tm;
+        tile_order(t, tiles_m, tiles_n, a.tile_group > 1 ? a.tile_group : 1, &tn, &tm);
       const int acc = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
       if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag, a.timeout_ns)) {
@@ -690,7 +706,8 @@ __device__ void gemm_role_256(const Args& a, const CUtensorMap* tmap_x, const CU
       int armed = 0, last_panel = -1;
       bool ok = true;
       for (long long t = gemm_idx; t < num_tiles && ok; t += num_gemm_ctas) {
-        const int tn = (int)(t / tiles_m), tm = (int)(t % tiles_m);
+        int tn, tm;
+        tile_order(t, tiles_m, tiles_n, a.tile_group > 1 ? a.tile_group : 1, &tn, &tm);
         if (a.fused && tn != last_panel) {
           ok = wait_panel(a, tn, abort_flag);
           if (!ok) break;
@@ -779,7 +796,8 @@ __device__ void gemm_role_256(const Args& a, const CUtensorMap* tmap_x, const CU
     long long local = 0;
     bool ok = true;
     for (long long t = gemm_idx; t < num_tiles && ok; t += num_gemm_ctas, ++local) {
-      const int tn = (int)(t / tiles_m), tm = (int)(t % tiles_m);
+      int tn, tm;
+        tile_order(t, tiles_m, tiles_n, a.tile_group > 1 ? a.tile_group : 1, &tn, &tm);
       if (!mbar_wait_bounded(&tmem_full[0], (uint32_t)(local & 1), abort_flag, a.timeout_ns)) {
         ok = false;
         break;
@@ -867,21 +885,27 @@ __global__ void __launch_bounds__(kThreads256, 1)
 // next tile), and the even CTA issues one M=256 MMA per K step for both.  Loads carry no
 // cluster multicast: each CTA fetches its own halves; only the completion counts and the
 // MMA-done signals cross between the two CTAs.
-struct CfgPair {
+// kRing: room for the pull ring of the fused form; the plain GEMM spends it on a seventh stage.
+template <bool kRing>
+struct CfgPairT {
   static constexpr int BN = 256;
   static constexpr int kABytes = 128 * BK * 2;  // this CTA's 128 rows of X
   static constexpr int kBBytes = 128 * BK * 2;  // this CTA's 128 rows of W
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = 6;
+  static constexpr int kStages = kRing ? 6 : 7;
   static constexpr int kTmemCols = 512;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256 + kRingBytes;
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + 1024 + 256 + (kRing ? kRingBytes : 0);
 };
+using CfgPair = CfgPairT<true>;
 
+template <bool kRing>
 __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const CUtensorMap* tmap_w,
                                int pair_idx, int num_pairs, unsigned char* smem_raw,
                                volatile int* abort_flag) {
-  using C = CfgPair;
+  using C = CfgPairT<kRing>;
   constexpr int BN = C::BN;
+  static_assert(2 * C::kStages + 5 <= kRingBarIndex, "pipeline barriers overlap the ring's");
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
@@ -899,6 +923,35 @@ __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const C
   const long long tiles_n = (a.N + BN - 1) / BN;
   const long long num_tiles = tiles_m * tiles_n;
   const int num_kb = (int)((a.K + BK - 1) / BK);
+  // Work items.  The tiles of the last, partly filled round are cut along N into 2 or 4 pieces
+  // when that lets every piece have a pair of its own: the round then lasts a half or a
+  // quarter of a tile time instead of a whole one.  (A piece of n columns needs n/2 rows of W in
+  // each CTA: the usual 128-row box is loaded and the MMA reads its first n/2 rows.)
+  const long long rest = num_tiles % num_pairs;
+  int split = 1;
+  if (rest != 0 && num_tiles > num_pairs) {
+    if (rest * 4 <= num_pairs) split = 4;
+    else if (rest * 2 <= num_pairs) split = 2;
+  }
+  const long long num_whole = split > 1 ? num_tiles - rest : num_tiles;
+  const long long num_items = num_whole + (split > 1 ? rest * split : 0);
+  const long long group = a.tile_group > 1 ? a.tile_group : 1;
+  auto tile_of = [&](long long t, int* tn, int* tm) {
+    tile_order(t, tiles_m, tiles_n, group, tn, tm);
+  };
+  // item -> (tile, first column inside the tile, columns)
+  auto item_of = [&](long long i, long long* t, int* n_off, int* n_len) {
+    if (i < num_whole) {
+      *t = i;
+      *n_off = 0;
+      *n_len = BN;
+    } else {
+      const long long j = i - num_whole;
+      *t = num_whole + j / split;
+      *n_len = BN / split;
+      *n_off = (int)(j % split) * *n_len;
+    }
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::kStages; ++s) {
@@ -930,8 +983,12 @@ __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const C
       uint32_t phase = 0;
       int last_panel = -1;
       bool ok = true;
-      for (long long t = pair_idx; t < num_tiles && ok; t += num_pairs) {
-        const int tn = (int)(t / tiles_m), tm = (int)(t % tiles_m);
+      for (long long it = pair_idx; it < num_items && ok; it += num_pairs) {
+        long long t;
+        int n_off, n_len;
+        item_of(it, &t, &n_off, &n_len);
+        int tn, tm;
+        tile_of(t, &tn, &tm);
         if (a.fused && tn != last_panel) {
           ok = wait_panel(a, tn, abort_flag);
           if (!ok) break;
@@ -945,8 +1002,8 @@ __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const C
           unsigned char* sa = smem + stage * C::kStageBytes;
           if (cta == 0) mbar_arrive_expect_tx(&full_bar[stage], 2 * C::kStageBytes);
           tma_load_2d_pair(sa, tmap_x, kb * BK, tm * 256 + (int)cta * 128, &full_bar[stage]);
-          tma_load_2d_pair(sa + C::kABytes, tmap_w, kb * BK, tn * BN + (int)cta * 128,
-                           &full_bar[stage]);
+          tma_load_2d_pair(sa + C::kABytes, tmap_w, kb * BK,
+                           tn * BN + n_off + (int)cta * (n_len / 2), &full_bar[stage]);
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -956,12 +1013,15 @@ __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const C
   } else if (warp == 1) {
     // ================= MMA issuer (leader CTA only) =================
     if (lane == 0 && cta == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(256, BN);
       int stage = 0;
       uint32_t phase = 0;
       long long local = 0;
       bool ok = true;
-      for (long long t = pair_idx; t < num_tiles && ok; t += num_pairs, ++local) {
+      for (long long it = pair_idx; it < num_items && ok; it += num_pairs, ++local) {
+        long long t;
+        int n_off, n_len;
+        item_of(it, &t, &n_off, &n_len);
+        const uint32_t idesc = make_idesc_bf16(256, n_len);
         const int acc = (int)(local & 1);
         const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
         if (!mbar_wait_bounded(&tmem_empty[acc], acc_phase ^ 1, abort_flag, a.timeout_ns)) {
@@ -996,8 +1056,12 @@ __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const C
     const int q = warp & 3;
     long long local = 0;
     bool ok = true;
-    for (long long t = pair_idx; t < num_tiles && ok; t += num_pairs, ++local) {
-      const int tn = (int)(t / tiles_m), tm = (int)(t % tiles_m);
+    for (long long it = pair_idx; it < num_items && ok; it += num_pairs, ++local) {
+      long long t;
+      int n_off, n_len;
+      item_of(it, &t, &n_off, &n_len);
+      int tn, tm;
+        tile_of(t, &tn, &tm);
       const int acc = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
       if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag, a.timeout_ns)) {
@@ -1009,11 +1073,11 @@ __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const C
       const long long row = (long long)tm * 256 + (long long)cta * 128 + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < n_len; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(taddr + (uint32_t)c0, r);
         tmem_ld_wait();
-        const long long col = (long long)tn * BN + c0;
+        const long long col = (long long)tn * BN + n_off + c0;
         if (row < a.M) {
           __nv_bfloat16* dst = a.c + row * a.N + col;
 #pragma unroll
@@ -1033,7 +1097,7 @@ __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const C
       mbar_arrive_leader(&tmem_empty[acc]);  // counted on the leader, where the MMAs are issued
     }
     if (!ok && lane == 0) report(a.scratch, PSDEV_ERR_TIMEOUT_PIPE);
-  } else if (a.fused && a.inline_copy) {
+  } else if (kRing && a.fused && a.inline_copy) {
     // warps 6 and 7: pull W while the other warps multiply
     const int cta_lin = pair_idx * 2 + (int)cta;
     if (a.ring_mode == 0)
@@ -1052,6 +1116,7 @@ __device__ void gemm_role_pair(const Args& a, const CUtensorMap* tmap_x, const C
 }
 
 // Grid: [copy CTAs (even count)][GEMM CTA pairs], clusters of 2 along x.
+template <bool kRing>
 __global__ void __launch_bounds__(kThreads, 1)
     pull_gemm_pair_kernel(const __grid_constant__ Args a,
                           const __grid_constant__ CUtensorMap tmap_x,
@@ -1065,8 +1130,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   if ((int)blockIdx.x < ncopy) {
     copy_role<256>(a, (int)blockIdx.x);
   } else {
-    gemm_role_pair(a, &tmap_x, &tmap_w, ((int)blockIdx.x - ncopy) >> 1,
-                   ((int)gridDim.x - ncopy) >> 1, smem_raw, &s_abort);
+    gemm_role_pair<kRing>(a, &tmap_x, &tmap_w, ((int)blockIdx.x - ncopy) >> 1,
+                          ((int)gridDim.x - ncopy) >> 1, smem_raw, &s_abort);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -1248,21 +1313,33 @@ static int launch256(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw
   return launch_ex(pull_gemm256_kernel, a, tx, tw, grid, kThreads256, Cfg256::kSmemBytes, 1, s);
 }
 
-static int launch_pair(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, int grid,
-                       cudaStream_t s) {
-  // (set once per device; the attribute call is idempotent, the flag is atomic because the
-  // entry points may be used from several host threads)
+template <bool kRing>
+static int launch_pair_t(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, int grid,
+                         cudaStream_t s) {
   static std::atomic<bool> attr_set[64];
   int dev = 0;
   cudaGetDevice(&dev);
   if (!attr_set[dev & 63].load(std::memory_order_acquire)) {
-    cudaError_t e = cudaFuncSetAttribute(pull_gemm_pair_kernel,
+    cudaError_t e = cudaFuncSetAttribute(pull_gemm_pair_kernel<kRing>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         CfgPair::kSmemBytes);
+                                         CfgPairT<kRing>::kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     attr_set[dev & 63].store(true, std::memory_order_release);
   }
-  return launch_ex(pull_gemm_pair_kernel, a, tx, tw, grid, kThreads, CfgPair::kSmemBytes, 2, s);
+  return launch_ex(pull_gemm_pair_kernel<kRing>, a, tx, tw, grid, kThreads,
+                   CfgPairT<kRing>::kSmemBytes, 2, s);
+}
+static int launch_pair(const Args& a, const CUtensorMap& tx, const CUtensorMap& tw, int grid,
+                       cudaStream_t s) {
+  // (the plain GEMM needs no pull ring and could spend its room on a seventh pipeline stage)
+  static const int stages_env = [] {
+    const char* e = getenv("PSB200_GEMM_PAIR_STAGES");
+    return e ? atoi(e) : 0;
+  }();
+  // measured on 16384x3072x1024: six stages 1258 TFLOP/s, seven (possible without the pull
+  // ring) 1228-1243: the seventh stage stays an option (PSB200_GEMM_PAIR_STAGES=7)
+  if (a.fused || stages_env != 7) return launch_pair_t<true>(a, tx, tw, grid, s);
+  return launch_pair_t<false>(a, tx, tw, grid, s);
 }
 
 // Output-tile height used by run(): 128 (double-buffered accumulators) or 256 (twice the
@@ -1332,6 +1409,20 @@ static int run(Args a, const void* x, const void* w, int num_ctas, cudaStream_t 
     if (tile_m == 256) return launch256(a, tx, tw, grid, s);
     return BN == 256 ? launch<256>(a, tx, tw, grid, s) : launch<128>(a, tx, tw, grid, s);
   };
+  {
+    // a GEMM that waits for panels of W to arrive takes them in order; otherwise groups of 8
+    static const int group_env = [] {
+      const char* e = getenv("PSB200_GEMM_GROUP");
+      return e ? atoi(e) : 0;
+    }();
+    const long long tn_count = (a.N + BN - 1) / BN;
+    // measured: with up to 16 panels the best order runs through all of them for each block of
+    // X rows (16384x3072x1024: 1213 / 1242 / 1307 / 1325 TFLOP/s for groups of 2 / 4 / 8 / 16);
+    // with more, groups of 8 (8192^3: 1591 against 1568 with 16)
+    long long group = group_env > 0 ? group_env : (tn_count <= 16 ? tn_count : 8);
+    if (group > tn_count) group = tn_count;
+    a.tile_group = a.fused ? 1 : (int)group;
+  }
   if (!a.fused) {
     a.inline_copy = 0;
     return go(0);

@@ -12,7 +12,10 @@ def _ref(x, w):
 @pytest.mark.parametrize("tile", [128, 256, 2])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (384, 128, 192),
                                    (1000, 392, 520), (2048, 3072, 1024), (130, 264, 72),
-                                   (4096, 1024, 512)])
+                                   (4096, 1024, 512),
+                                   # more tiles than CTA pairs with a short last round: the
+                                   # pair kernel cuts that round's tiles in 4 / in 2 along N
+                                   (2560, 2304, 128), (3328, 2048, 192), (2560, 2296, 128)])
 def test_gemm_matches_fp32_matmul(cuda_device, M, N, K, tile):
     from ps_lite_b200 import _lib
     from ps_lite_b200.ops.gemm import gemm_status, linear_bf16
