@@ -79,6 +79,18 @@ struct DenseInfo {
   bool owns_state = false;  // master/state allocated by the plane
 };
 
+// A registered keyed (sparse) table of an app, as seen by this rank.
+struct SparseInfo {
+  int app_id = 0;
+  uint64_t key_space = 0;   // keys are below this; server s owns [s*range, (s+1)*range)
+  int64_t max_keys = 0;     // keys per request at most
+  int width = 1;            // fp32 elements per value
+  psdev_sparse_t table;     // offsets of the request buffers, owner state, handle
+  void* keys = nullptr;     // this rank's request buffers in the arena
+  void* vals = nullptr;
+  void* out = nullptr;
+};
+
 class Plane : public DeviceRoute {
  public:
   static Plane* Get();
@@ -128,6 +140,20 @@ class Plane : public DeviceRoute {
   void ClearStatus(int app_id, uint64_t tensor_id);
   int NewChannel();
 
+  // ---- keyed (sparse) tables ---------------------------------------------------------------
+  // One keyed table per app: sorted unique uint64 keys below `key_space`, `width` fp32 elements
+  // per key, owner state in a direct-index store; handle `kind` 0 = sum, 1 = SGD (lr),
+  // 2 = FTRL-proximal (alpha, beta, l1, l2).  Same call on every rank.  Afterwards a KVWorker
+  // request of that app whose key array lives in DEVICE memory (SArray::FromDevice) is served by
+  // the keyed kernels (src/kernels/sparse.cu): values and outputs are device arrays too.
+  const SparseInfo& DeclareSparse(int app_id, uint64_t key_space, int64_t max_keys, int width,
+                                  int kind, float lr, float alpha, float beta, float l1,
+                                  float l2);
+  const SparseInfo* FindSparse(int app_id) const;
+  // Synchronous copy between host and device memory in either direction (set-up and tests of
+  // programs that are not compiled with the CUDA headers).
+  void Memcpy(void* dst, const void* src, size_t bytes);
+
   // Stream on which requests of the calling thread are ordered: a request with device-resident
   // values runs on it; a staged request starts after what the stream holds and the stream
   // waits for its end.  A null handle names the legacy default stream.  Without a call (or
@@ -148,6 +174,7 @@ class Plane : public DeviceRoute {
   struct Impl;
 
  private:
+  void SubmitSparse(const DeviceRequest& req);
   Plane();
   ~Plane();
   std::unique_ptr<Impl> impl_;

@@ -60,6 +60,9 @@ struct Rt {
   int (*memset_async)(void*, int, size_t, void*) = nullptr;
   size_t (*ll_bytes)(int, int64_t) = nullptr;
   int (*handle_states)(int) = nullptr;
+  int (*sparse_scatter)(const psdev_world_t*, const psdev_sparse_t*, int64_t, int, void*) = nullptr;
+  int (*sparse_apply)(const psdev_world_t*, const psdev_sparse_t*, int, int, void*) = nullptr;
+  int (*sparse_respond)(const psdev_world_t*, const psdev_sparse_t*, int, int, void*) = nullptr;
   int (*is_device_pointer)(const void*) = nullptr;
   int (*heap_create)(size_t, void**, unsigned char*) = nullptr;
   int (*heap_open)(const unsigned char*, void**) = nullptr;
@@ -124,6 +127,9 @@ void* LoadRt(const std::string& configured, Rt* rt) {
   Bind(lib, "psdev_rt_memset_async", &rt->memset_async);
   Bind(lib, "psdev_ll_bytes", &rt->ll_bytes);
   Bind(lib, "psdev_handle_states", &rt->handle_states);
+  Bind(lib, "psdev_sparse_scatter", &rt->sparse_scatter);
+  Bind(lib, "psdev_sparse_apply", &rt->sparse_apply);
+  Bind(lib, "psdev_sparse_respond", &rt->sparse_respond);
   Bind(lib, "psdev_rt_is_device_pointer", &rt->is_device_pointer);
   Bind(lib, "psdev_heap_create", &rt->heap_create);
   Bind(lib, "psdev_heap_open", &rt->heap_open);
@@ -436,6 +442,7 @@ struct Plane::Impl {
   std::unique_ptr<SubAlloc> sub;
   mutable std::mutex mu;  // tables, allocator, channel counter
   std::map<std::pair<int, uint64_t>, std::unique_ptr<DenseInfo>> dense;
+  std::map<int, std::unique_ptr<SparseInfo>> sparse;
   int next_channel = 0;
 
   void* s_h2d = nullptr;
@@ -446,7 +453,7 @@ struct Plane::Impl {
   std::mutex ev_mu;
   // requests on one tensor are serialised against each other: the last event of the previous
   // one (keyed by DenseInfo*)
-  std::map<const DenseInfo*, void*> last_done;
+  std::map<const void*, void*> last_done;
 
   struct Pending {
     void* event = nullptr;
@@ -458,7 +465,7 @@ struct Plane::Impl {
     std::function<void()> on_done;
     int* lens_out = nullptr;
     std::vector<int> lens;
-    const DenseInfo* tensor = nullptr;
+    const void* tensor = nullptr;  // DenseInfo* or SparseInfo*: key of the ordering entry
   };
   std::mutex q_mu;
   std::condition_variable q_cv, idle_cv;
@@ -767,6 +774,14 @@ void Plane::Stop() {
       }
     }
     m.dense.clear();
+    for (auto& kv : m.sparse) {
+      psdev_sparse_t& t = kv.second->table;
+      m.rt.free_(t.w);
+      if (t.z) m.rt.free_(t.z);
+      if (t.n) m.rt.free_(t.n);
+      if (t.overflow) m.rt.free_(t.overflow);
+    }
+    m.sparse.clear();
     m.last_done.clear();
   }
   if (m.mc) {
@@ -993,7 +1008,9 @@ inline void SplitKey(Key key, int world, int* shard, uint64_t* tensor_id) {
 
 bool Plane::Claims(int app_id, const SArray<Key>& keys) {
   Impl& m = *impl_;
-  if (!m.started || keys.empty() || keys.mem_kind() != MemKind::kHost) return false;
+  if (!m.started || keys.empty()) return false;
+  // a key array in device memory addresses the app's keyed table
+  if (keys.mem_kind() == MemKind::kDevice) return FindSparse(app_id) != nullptr;
   int shard;
   uint64_t id;
   SplitKey(keys[0], m.world, &shard, &id);
@@ -1003,6 +1020,10 @@ bool Plane::Claims(int app_id, const SArray<Key>& keys) {
 size_t Plane::PullBytes(int app_id, const SArray<Key>& keys) {
   Impl& m = *impl_;
   if (!m.started || keys.empty()) return 0;
+  if (keys.mem_kind() == MemKind::kDevice) {
+    const SparseInfo* sp = FindSparse(app_id);
+    return sp ? keys.size() * static_cast<size_t>(sp->width) * 4 : 0;
+  }
   int shard;
   uint64_t id;
   SplitKey(keys[0], m.world, &shard, &id);
@@ -1019,10 +1040,92 @@ size_t Plane::PullBytes(int app_id, const SArray<Key>& keys) {
   return elems * DtypeSize(d->table.out_dtype);
 }
 
+// ---- keyed tables -----------------------------------------------------------------------------
+const SparseInfo& Plane::DeclareSparse(int app_id, uint64_t key_space, int64_t max_keys, int width,
+                                       int kind, float lr, float alpha, float beta, float l1,
+                                       float l2) {
+  Impl& m = *impl_;
+  CHECK(m.started);
+  CHECK(!m.sim) << "keyed tables need a GPU (the CPU stand-in serves dense tensors only)";
+  CHECK(key_space > 0 && max_keys > 0 && width >= 1 && kind >= 0 && kind <= 2);
+  CHECK(!FindSparse(app_id)) << "app " << app_id << " already has a keyed table";
+  const int W = m.world;
+  std::unique_ptr<SparseInfo> sp(new SparseInfo);
+  sp->app_id = app_id;
+  sp->key_space = key_space;
+  sp->max_keys = max_keys;
+  sp->width = width;
+  psdev_sparse_t& t = sp->table;
+  t = psdev_sparse_t{};
+  t.range = (key_space + W - 1) / W;
+  t.width = width;
+  t.max_n = max_keys;
+  t.max_vals = max_keys * width;
+  t.slots = static_cast<int64_t>(t.range);
+  t.kind = kind;
+  t.lr = lr; t.alpha = alpha; t.beta = beta; t.l1 = l1; t.l2 = l2;
+  t.channel = NewChannel();
+  t.timeout_ns = m.opts.timeout_ns;
+  auto alloc = [&](size_t bytes) {
+    const int64_t off = Alloc(bytes);
+    CHECK_GE(off, 0) << "symmetric heap exhausted (keyed table)";
+    return static_cast<uint64_t>(off);
+  };
+  t.keys_off = alloc(8 * static_cast<size_t>(max_keys));
+  t.grads_off = alloc(4 * static_cast<size_t>(t.max_vals));
+  t.out_off = alloc(4 * static_cast<size_t>(t.max_vals));
+  t.pos_off = alloc(8 * static_cast<size_t>(W + 2));
+  const size_t acc_bytes = 4 * static_cast<size_t>(t.slots) * width;
+  t.acc_off = alloc(acc_bytes);
+  m.rt.set_device(m.opts.device);
+  void* acc = Local(static_cast<int64_t>(t.acc_off));
+  void* pos = Local(static_cast<int64_t>(t.pos_off));
+  CHECK_EQ(m.rt.memset_async(acc, 0, acc_bytes, m.s_compute), 0);
+  CHECK_EQ(m.rt.memset_async(pos, 0, 8 * static_cast<size_t>(W + 2), m.s_compute), 0);
+  CHECK_EQ(m.rt.stream_sync(m.s_compute), 0);
+  void* p = nullptr;
+  CHECK_EQ(m.rt.malloc_(&p, acc_bytes), 0);
+  t.w = static_cast<float*>(p);
+  if (kind == 2) {
+    CHECK_EQ(m.rt.malloc_(&p, acc_bytes), 0);
+    t.z = static_cast<float*>(p);
+    CHECK_EQ(m.rt.malloc_(&p, acc_bytes), 0);
+    t.n = static_cast<float*>(p);
+  }
+  sp->keys = Local(static_cast<int64_t>(t.keys_off));
+  sp->vals = Local(static_cast<int64_t>(t.grads_off));
+  sp->out = Local(static_cast<int64_t>(t.out_off));
+  SparseInfo* raw = sp.get();
+  {
+    std::lock_guard<std::mutex> lk(m.mu);
+    m.sparse[app_id] = std::move(sp);
+  }
+  Barrier();  // every rank's accumulator is clear before anybody scatters into it
+  return *raw;
+}
+
+const SparseInfo* Plane::FindSparse(int app_id) const {
+  std::lock_guard<std::mutex> lk(impl_->mu);
+  auto it = impl_->sparse.find(app_id);
+  return it == impl_->sparse.end() ? nullptr : it->second.get();
+}
+
+void Plane::Memcpy(void* dst, const void* src, size_t bytes) {
+  Impl& m = *impl_;
+  CHECK(m.started);
+  m.rt.set_device(m.opts.device);
+  CHECK_EQ(m.rt.memcpy_async(dst, src, bytes, m.s_status), 0);
+  CHECK_EQ(m.rt.stream_sync(m.s_status), 0);
+}
+
 void Plane::Submit(const DeviceRequest& req) {
   Impl& m = *impl_;
   CHECK(m.started);
   m.rt.set_device(m.opts.device);
+  if (req.keys.mem_kind() == MemKind::kDevice) {
+    SubmitSparse(req);
+    return;
+  }
   const int W = m.world;
   int shard;
   uint64_t id;
@@ -1213,6 +1316,72 @@ void Plane::Submit(const DeviceRequest& req) {
     std::lock_guard<std::mutex> lk(m.mu);
     // `done` doubles as the ordering point for the next request on this tensor
     m.last_done[d] = done;
+  }
+  {
+    std::lock_guard<std::mutex> lk(m.q_mu);
+    ++m.in_flight;
+    m.queue.push_back(std::move(pend));
+  }
+  m.q_cv.notify_one();
+}
+
+// A keyed request: keys, values and outputs are device arrays.  The request is staged into the
+// table's buffers in the arena (device-to-device, unless it already lives there), then scatter,
+// apply and respond run on the caller's stream; the rendezvous of the ranks is inside the last
+// two kernels.  A push without pull still runs the respond kernel (it closes the round); a pull
+// without push scatters zeros, which changes nothing on the owners.
+void Plane::SubmitSparse(const DeviceRequest& req) {
+  Impl& m = *impl_;
+  SparseInfo* sp = const_cast<SparseInfo*>(FindSparse(req.app_id));
+  CHECK(sp) << "app " << req.app_id << " has no keyed table";
+  const psdev_sparse_t& t = sp->table;
+  const int64_t n = static_cast<int64_t>(req.keys.size());
+  CHECK_LE(n, sp->max_keys) << "more keys than the table was declared for";
+  CHECK(req.lens.empty()) << "keyed tables of the plane take fixed-width values";
+  const size_t vbytes = static_cast<size_t>(n) * sp->width * 4;
+  if (req.push) {
+    CHECK(req.vals && req.vals_bytes == vbytes) << "expected " << sp->width << " fp32 per key";
+  }
+  if (req.pull && req.outs) { CHECK_EQ(req.outs_bytes, vbytes); }
+  void* s = tls_has_stream ? tls_stream : m.s_compute;
+  void* prev_done = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(m.mu);
+    auto it = m.last_done.find(sp);
+    if (it != m.last_done.end()) prev_done = it->second;
+  }
+  if (prev_done) m.rt.stream_wait_event(s, prev_done);
+  const void* kptr = req.keys.data();
+  if (kptr != sp->keys) {
+    CHECK_EQ(m.rt.memcpy_async(sp->keys, kptr, static_cast<size_t>(n) * 8, s), 0);
+  }
+  if (req.push) {
+    if (req.vals != sp->vals) {
+      CHECK_EQ(m.rt.memcpy_async(sp->vals, req.vals, vbytes, s), 0);
+    }
+  } else {
+    CHECK_EQ(m.rt.memset_async(sp->vals, 0, vbytes, s), 0);
+  }
+  const int sync = m.world > 1 ? 1 : 0;
+  CHECK_EQ(m.rt.sparse_scatter(&m.ws, &t, n, 0, s), 0) << "psdev_sparse_scatter failed";
+  CHECK_EQ(m.rt.sparse_apply(&m.ws, &t, 0, sync, s), 0) << "psdev_sparse_apply failed";
+  CHECK_EQ(m.rt.sparse_respond(&m.ws, &t, 0, sync, s), 0) << "psdev_sparse_respond failed";
+  if (req.pull && req.outs && req.outs != sp->out) {
+    CHECK_EQ(m.rt.memcpy_async(req.outs, sp->out, vbytes, s), 0);
+  }
+  void* done = m.NewEvent();
+  m.rt.event_record(done, s);
+  Impl::Pending pend;
+  pend.event = done;
+  pend.channel = t.channel;
+  pend.timestamp = req.timestamp;
+  pend.responses = req.responses;
+  pend.customer = req.customer;
+  pend.on_done = req.on_done;
+  pend.tensor = sp;
+  {
+    std::lock_guard<std::mutex> lk(m.mu);
+    m.last_done[sp] = done;
   }
   {
     std::lock_guard<std::mutex> lk(m.q_mu);

@@ -36,7 +36,7 @@ int main(int argc, char** argv) {
     return 0;
   }
   device::PlaneOptions po;
-  po.heap_bytes = 16u << 20;
+  po.heap_bytes = PLANE_DEVICE < 0 ? (16u << 20) : (96u << 20);
   po.slice_bytes = 1u << 20;  // several slices per request, with the ramp at both ends
   po.device = PLANE_DEVICE < 0 ? -1 : MyRank();
   po.timeout_ns = 1500000000ull;
@@ -156,6 +156,47 @@ int main(int argc, char** argv) {
     kv.Wait(kv.Pull(keys, &got));
     for (int64_t i = 0; i < n; ++i) CHECK_LT(std::fabs(got[i] - expect[i]), 1e-4f) << "at " << i;
   }
+
+  // 6. keyed (sparse) requests: key array in device memory -> the app's keyed table.  Every
+  // worker pushes the same sorted keys with value (rank + 1) per element; the sum handle then
+  // holds W(W+1)/2 per element after one push, and a pull-only request reads it back.
+#if PLANE_DEVICE >= 0
+  {
+    const int kApp = 3, width = 2;
+    const int64_t nk = 5000;
+    const uint64_t key_space = 1u << 20;
+    const device::SparseInfo& sp =
+        plane->DeclareSparse(kApp, key_space, nk, width, /*sum*/ 0, 0.f, 0.f, 0.f, 0.f, 0.f);
+    KVWorker<float> skv(kApp, 1);
+    std::vector<Key> hkeys(nk);
+    for (int64_t i = 0; i < nk; ++i) hkeys[i] = static_cast<Key>(i) * (key_space / nk) + 7;
+    std::vector<float> hvals(nk * width, static_cast<float>(R + 1));
+    // device copies: scratch from the symmetric heap (any device memory would do)
+    const int64_t koff = plane->Alloc(nk * 8), voff = plane->Alloc(nk * width * 4),
+                  ooff = plane->Alloc(nk * width * 4);
+    CHECK(koff >= 0 && voff >= 0 && ooff >= 0);
+    Key* dkeys = static_cast<Key*>(plane->Local(koff));
+    float* dvals = static_cast<float*>(plane->Local(voff));
+    float* dout = static_cast<float*>(plane->Local(ooff));
+    plane->Memcpy(dkeys, hkeys.data(), nk * 8);
+    plane->Memcpy(dvals, hvals.data(), nk * width * 4);
+    SArray<Key> sk = SArray<Key>::FromDevice(dkeys, nk);
+    SArray<float> sv = SArray<float>::FromDevice(dvals, nk * width);
+    SArray<float> so = SArray<float>::FromDevice(dout, nk * width);
+    std::atomic<int> done{0};
+    skv.Wait(skv.ZPushPull(sk, sv, &so, nullptr, 0, [&done]() { ++done; }));
+    CHECK_EQ(done.load(), 1);
+    std::vector<float> back(nk * width);
+    plane->Memcpy(back.data(), dout, nk * width * 4);
+    const float want = 0.5f * W * (W + 1);
+    for (size_t i = 0; i < back.size(); ++i) CHECK_EQ(back[i], want) << "at " << i;
+    skv.Wait(skv.ZPush(sk, sv));                       // push only
+    skv.Wait(skv.ZPull(sk, &so));                      // pull only
+    plane->Memcpy(back.data(), dout, nk * width * 4);
+    for (size_t i = 0; i < back.size(); ++i) CHECK_EQ(back[i], 2 * want) << "at " << i;
+    CHECK(&sp == plane->FindSparse(kApp));
+  }
+#endif
 
   CHECK_GT(plane->launches(), (uint64_t)0);
   LOG(INFO) << "DEVICE_PLANE_OK rank " << R << " of " << W << " backend " << plane->backend();
