@@ -66,7 +66,11 @@ def measure_ps(ctx, workload, steps, warmup, batch=0, ctas=0, sample_clocks=Fals
     torch.backends.cudnn.benchmark = True
     model, sopt, make, fwd, unit, metric, per_step = _build(workload, batch, world, dev)
     nparam = sum(p.numel() for p in model.parameters())
-    fused = workload == "bert"
+    # the pull of the first GEMM's weight is fused into that GEMM when the weight is large
+    # enough for the fusion to pay (ops.gemm.fusion_pays; BERT-large's 6 MiB QKV weight is not)
+    from ps_lite_b200.ops.gemm import fusion_pays
+    fused = (workload == "bert" and
+             fusion_pays(model.layers[0].qkv.weight.numel() * 2, world))
     dopt = DistributedOptimizer(model.parameters(), ctx.heap, sopt, grad_dtype=torch.bfloat16,
                                 num_ctas=ctas or 32, channel=ctx.new_channel(),
                                 publish_params=[model.layers[0].qkv.weight] if fused else ())

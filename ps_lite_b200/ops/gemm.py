@@ -58,6 +58,18 @@ def pull_linear_bf16(table, w_offset: int, n_out: int, x: torch.Tensor,
     return out
 
 
+def fusion_pays(weight_bytes: int, world: int) -> bool:
+    """Whether pulling a weight inside the GEMM that consumes it beats push+pull followed by
+    the GEMM.  Measured (benchmarks/pull_gemm_bench.py): with a 128 MiB weight the fused form
+    is 1.12-1.16x faster; with the 6 MiB QKV weight of BERT-large it is slower (0.96x on 2 GPUs,
+    0.91x on 4: the cooperative launch and the per-panel waits cost more than the pull they
+    hide).  The switch-over lies between; ``PSB200_FUSE_MIN_MB`` (default 32) sets it."""
+    import os
+    if world < 2:
+        return False
+    return weight_bytes >= int(os.environ.get("PSB200_FUSE_MIN_MB", "32")) << 20
+
+
 class _PullLinearFn(torch.autograd.Function):
     """``x @ W^T`` where W is pulled from its owners inside the GEMM kernel.
 

@@ -198,6 +198,8 @@ class DenseTable:
     def owned_index(self) -> torch.Tensor:
         """Global element indices of the values this rank owns, in state order."""
         W, R = self.heap.world, self.heap.rank
+        if R >= self.nblocks:   # fewer blocks than ranks: this rank serves none
+            return torch.empty(0, dtype=torch.int64, device=self.heap.device)
         blocks = torch.arange(R, self.nblocks, W, device=self.heap.device)
         idx = blocks[:, None] * self.blk + torch.arange(self.blk, device=self.heap.device)[None, :]
         return idx.reshape(-1)

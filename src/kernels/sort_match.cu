@@ -106,19 +106,32 @@ __global__ void __launch_bounds__(1024)
   }
 }
 
-// Stable scatter of one 8-bit digit.
+// Stable scatter of one 8-bit digit.  Keys (and payloads) are first put in sorted order inside
+// the tile in shared memory, then stored: consecutive threads store consecutive keys of one
+// digit, i.e. consecutive addresses.
+constexpr int kScatterSmem = kTile * 8 + kTile * 4 + kWarps * kDigits * 4 + 2 * kDigits * 4;
+
 __global__ void __launch_bounds__(kThreads)
     scatter_kernel(const unsigned long long* keys_in, unsigned long long* keys_out,
                    const unsigned int* pay_in, unsigned int* pay_out, long long n, int shift,
                    const unsigned int* offsets, int ntiles) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  unsigned long long* skeys = reinterpret_cast<unsigned long long*>(smem_raw);
+  unsigned int* spay = reinterpret_cast<unsigned int*>(smem_raw + kTile * 8);
   // cnt[w][d]: first the number of keys with digit d seen so far by warp w, afterwards the
-  // output position of that warp's first key with digit d
-  __shared__ unsigned int cnt[kWarps][kDigits];
+  // position inside the tile's digit-d run of that warp's first key with digit d
+  unsigned int (*cnt)[kDigits] =
+      reinterpret_cast<unsigned int (*)[kDigits]>(smem_raw + kTile * 12);
+  unsigned int* tile_start = reinterpret_cast<unsigned int*>(smem_raw + kTile * 12 +
+                                                             kWarps * kDigits * 4);
+  unsigned int* goff = tile_start + kDigits;  // output index of sorted position q: goff[d] + q
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) cnt[w][threadIdx.x] = 0;
   __syncthreads();
-  const long long base = (long long)blockIdx.x * kTile + (long long)warp * (32 * kItems) + lane;
+  const long long tile_base = (long long)blockIdx.x * kTile;
+  const long long base = tile_base + (long long)warp * (32 * kItems) + lane;
+  const int tile_n = (int)(n - tile_base < kTile ? n - tile_base : kTile);
   unsigned long long k[kItems];
   unsigned short rank[kItems];
 #pragma unroll
@@ -138,23 +151,53 @@ __global__ void __launch_bounds__(kThreads)
   }
   __syncthreads();
   {
-    // digit threadIdx.x: where each warp's keys of that digit go
-    unsigned int run = offsets[(size_t)threadIdx.x * ntiles + blockIdx.x];
+    // digit threadIdx.x: each warp's start inside the digit's run, and the run's length
+    unsigned int run = 0;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) {
       const unsigned int c = cnt[w][threadIdx.x];
       cnt[w][threadIdx.x] = run;
       run += c;
     }
+    tile_start[threadIdx.x] = run;
+  }
+  __syncthreads();
+  // exclusive prefix of the run lengths over the digits (256 values, one per thread)
+  {
+    const unsigned int mine = tile_start[threadIdx.x];
+    unsigned int incl = mine;
+    for (int off = 1; off < kDigits; off <<= 1) {
+      const unsigned int v = threadIdx.x >= off ? tile_start[threadIdx.x - off] : 0u;
+      __syncthreads();
+      incl += v;
+      tile_start[threadIdx.x] = incl;
+      __syncthreads();
+    }
+    const unsigned int excl = incl - mine;
+    __syncthreads();
+    tile_start[threadIdx.x] = excl;
+    goff[threadIdx.x] = offsets[(size_t)threadIdx.x * ntiles + blockIdx.x] - excl;
   }
   __syncthreads();
 #pragma unroll
   for (int j = 0; j < kItems; ++j) {
     const long long i = base + j * 32;
     if (i < n) {
-      const unsigned int p = cnt[warp][digit_of(k[j], shift)] + rank[j];
-      keys_out[p] = k[j];
-      if (pay_in) pay_out[p] = pay_in[i];
+      const unsigned int d = digit_of(k[j], shift);
+      const unsigned int q = tile_start[d] + cnt[warp][d] + rank[j];
+      skeys[q] = k[j];
+      if (pay_in) spay[q] = pay_in[i];
+    }
+  }
+  __syncthreads();
+#pragma unroll 4
+  for (int j = 0; j < kItems; ++j) {
+    const int q = threadIdx.x + j * kThreads;
+    if (q < tile_n) {
+      const unsigned long long key = skeys[q];
+      const unsigned int p = goff[digit_of(key, shift)] + (unsigned int)q;
+      keys_out[p] = key;
+      if (pay_in) pay_out[p] = spay[q];
     }
   }
 }
@@ -260,6 +303,19 @@ int psdev_sort_keys(uint64_t* keys, uint32_t* perm, int64_t n, int key_bits, voi
   p += ((size_t)ntiles * kDigits * 4 + 255) & ~size_t(255);
   unsigned int* totals = reinterpret_cast<unsigned int*>(p);
   const int passes = (key_bits + kRadixBits - 1) / kRadixBits;
+  {
+    // the scatter kernel's tile buffers exceed the default limit of dynamic shared memory
+    static std::atomic<bool> attr_set[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev & 63].load(std::memory_order_acquire)) {
+      cudaError_t e = cudaFuncSetAttribute(scatter_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kScatterSmem);
+      if (e != cudaSuccess) return (int)e;
+      attr_set[dev & 63].store(true, std::memory_order_release);
+    }
+  }
   cudaMemsetAsync(totals, 0, (size_t)passes * kDigits * 4, s);
   unsigned long long* in = reinterpret_cast<unsigned long long*>(keys);
   unsigned long long* out = alt;
@@ -270,7 +326,8 @@ int psdev_sort_keys(uint64_t* keys, uint32_t* perm, int64_t n, int key_bits, voi
     unsigned int* tot = totals + pass * kDigits;
     tile_count_kernel<<<ntiles, kThreads, 0, s>>>(in, n, shift, hist, tot, ntiles);
     tile_scan_kernel<<<kDigits, 1024, 0, s>>>(hist, tot, ntiles);
-    scatter_kernel<<<ntiles, kThreads, 0, s>>>(in, out, pin, pout, n, shift, hist, ntiles);
+    scatter_kernel<<<ntiles, kThreads, kScatterSmem, s>>>(in, out, pin, pout, n, shift, hist,
+                                                         ntiles);
     g_launches.fetch_add(3, std::memory_order_relaxed);
     unsigned long long* t = in; in = out; out = t;
     unsigned int* tp = pin; pin = pout; pout = tp;
