@@ -18,15 +18,48 @@ extern std::atomic<uint64_t> g_launches;
 namespace filt {
 constexpr int kGroup = 256;
 
+// Eight values per thread and trip (two 16-byte loads, one 16-byte store, or the reverse) when
+// both arrays are 16-byte aligned; scalar accesses for the tail and for unaligned arrays.
 __global__ void cast_scale_f32_to_bf16(const float* in, __nv_bfloat16* out, long long n, float s) {
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x)
-    out[i] = __float2bfloat16_rn(in[i] * s);
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  long long vec = 0;
+  if ((((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+    vec = n / 8;
+    for (long long v = tid; v < vec; v += nthreads) {
+      const float4 a = reinterpret_cast<const float4*>(in)[2 * v];
+      const float4 b = reinterpret_cast<const float4*>(in)[2 * v + 1];
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x * s, a.y * s);
+      __nv_bfloat162 p1 = __floats2bfloat162_rn(a.z * s, a.w * s);
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x * s, b.y * s);
+      __nv_bfloat162 p3 = __floats2bfloat162_rn(b.z * s, b.w * s);
+      uint4 u;
+      u.x = *reinterpret_cast<unsigned int*>(&p0);
+      u.y = *reinterpret_cast<unsigned int*>(&p1);
+      u.z = *reinterpret_cast<unsigned int*>(&p2);
+      u.w = *reinterpret_cast<unsigned int*>(&p3);
+      reinterpret_cast<uint4*>(out)[v] = u;
+    }
+  }
+  for (long long i = vec * 8 + tid; i < n; i += nthreads) out[i] = __float2bfloat16_rn(in[i] * s);
 }
 __global__ void cast_scale_bf16_to_f32(const __nv_bfloat16* in, float* out, long long n, float s) {
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x)
-    out[i] = __bfloat162float(in[i]) * s;
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  long long vec = 0;
+  if ((((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+    vec = n / 8;
+    for (long long v = tid; v < vec; v += nthreads) {
+      const uint4 u = reinterpret_cast<const uint4*>(in)[v];
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+      const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.z));
+      const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.w));
+      reinterpret_cast<float4*>(out)[2 * v] = make_float4(a.x * s, a.y * s, b.x * s, b.y * s);
+      reinterpret_cast<float4*>(out)[2 * v + 1] = make_float4(c.x * s, c.y * s, d.x * s, d.y * s);
+    }
+  }
+  for (long long i = vec * 8 + tid; i < n; i += nthreads) out[i] = __bfloat162float(in[i]) * s;
 }
 
 // one warp per group of 256 values (8 per lane)
@@ -57,8 +90,33 @@ __global__ void int8_pack(const float* in, signed char* q, float* scales, long l
 }
 __global__ void int8_unpack(const signed char* q, const float* scales, float* out, long long n,
                             int accumulate) {
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x) {
+  // sixteen values per thread and trip (one 16-byte load, four 16-byte stores) when aligned; a
+  // vector of 16 never straddles a group of 256
+  const long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  long long vec = 0;
+  if ((((uintptr_t)q | (uintptr_t)out) & 15) == 0) {
+    vec = n / 16;
+    for (long long v = tid; v < vec; v += nthreads) {
+      const uint4 u = reinterpret_cast<const uint4*>(q)[v];
+      const float sc = scales[(v * 16) / kGroup];
+      const unsigned int w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float4 o = make_float4((float)(signed char)(w[j] & 0xff) * sc,
+                               (float)(signed char)((w[j] >> 8) & 0xff) * sc,
+                               (float)(signed char)((w[j] >> 16) & 0xff) * sc,
+                               (float)(signed char)((w[j] >> 24) & 0xff) * sc);
+        float4* dst = reinterpret_cast<float4*>(out) + 4 * v + j;
+        if (accumulate) {
+          const float4 p = *dst;
+          o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+        }
+        *dst = o;
+      }
+    }
+  }
+  for (long long i = vec * 16 + tid; i < n; i += nthreads) {
     const float v = (float)q[i] * scales[i / kGroup];
     out[i] = accumulate ? out[i] + v : v;
   }
