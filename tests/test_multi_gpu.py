@@ -84,3 +84,11 @@ def test_cpp_program_through_ps_start_across_gpus(cuda_device):
     rc = job.wait(120)
     out = job.output()
     assert rc == 0 and out.count("DEVICE_PLANE_OK") == nproc, out[-4000:]
+
+
+def test_bert_large_parity_with_single_process_adam(cuda_device):
+    """Ten steps of BERT-large through the server-side Adam on N ranks against single-process
+    torch Adam on the global batch, loss compared at every step."""
+    nproc = min(_nproc(), 4)
+    rc, out = _job("mp_bert_parity.py", nproc, timeout=400, log=f"mp_bert_parity_n{nproc}.log")
+    assert rc == 0 and "MP_BERT_PARITY_OK" in out, out[-4000:]
