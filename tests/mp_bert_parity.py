@@ -74,9 +74,10 @@ def main():
             ok = False
     # the weights themselves, after 10 steps
     num = den = 0.0
-    for a, b in zip(mine.parameters(), ref.parameters()):
-        num += float((a.float() - b.float()).pow(2).sum())
-        den += float(b.float().pow(2).sum())
+    with torch.no_grad():
+        for a, b in zip(mine.parameters(), ref.parameters()):
+            num += float((a.float() - b.float()).pow(2).sum())
+            den += float(b.float().pow(2).sum())
     rel = (num / max(den, 1e-30)) ** 0.5
     if rel > 2e-2:
         ok = False
