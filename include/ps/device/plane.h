@@ -89,6 +89,9 @@ struct SparseInfo {
   void* keys = nullptr;     // this rank's request buffers in the arena
   void* vals = nullptr;
   void* out = nullptr;
+  bool var_len = false;     // values have per-key lengths of at most `width` elements
+  void* lens = nullptr;     // i32[max_keys] lengths of the current request (var_len)
+  void* offs = nullptr;     // i64[max_keys+1] their running sum
 };
 
 class Plane : public DeviceRoute {
@@ -146,9 +149,15 @@ class Plane : public DeviceRoute {
   // 2 = FTRL-proximal (alpha, beta, l1, l2).  Same call on every rank.  Afterwards a KVWorker
   // request of that app whose key array lives in DEVICE memory (SArray::FromDevice) is served by
   // the keyed kernels (src/kernels/sparse.cu): values and outputs are device arrays too.
+  // `var_len`: the value of key i has lens[i] <= width elements, packed back to back (the
+  // reference's `lens`, include/ps/kv_app.h:24-45).  A push (ZPush, ZPushPull) names the lengths
+  // in a device array; a pull (ZPull) sizes its output for `width` per key, and receives the
+  // packed values and, in its `lens` array (device memory), the lengths that the owners hold.
+  // On such a table every worker issues the same kind of request at the same position of its
+  // sequence of requests (the pull has two device barriers that the push has not).
   const SparseInfo& DeclareSparse(int app_id, uint64_t key_space, int64_t max_keys, int width,
                                   int kind, float lr, float alpha, float beta, float l1,
-                                  float l2);
+                                  float l2, bool var_len = false);
   const SparseInfo* FindSparse(int app_id) const;
   // Synchronous copy between host and device memory in either direction (set-up and tests of
   // programs that are not compiled with the CUDA headers).

@@ -274,6 +274,13 @@ int psdev_sparse_apply(const psdev_world_t* w, const psdev_sparse_t* t, int num_
 int psdev_sparse_respond(const psdev_world_t* w, const psdev_sparse_t* t, int num_ctas, int sync,
                          void* stream);
 
+/* Server role, tables with lengths: stores the length of the value of every key that a worker
+ * staged (keys in its arena, cut points computed with psdev_key_shard_lookup) into that worker's
+ * array of lengths; 0 for a key that was never pushed.  Used by a pull that does not know the
+ * lengths: barrier, this call, barrier, psdev_lens_to_offsets, then apply and respond. */
+int psdev_sparse_lens(const psdev_world_t* w, const psdev_sparse_t* t, int num_ctas,
+                      void* stream);
+
 /* ---- bf16 GEMM on tcgen05, alone or fused with the pull of its weights ----------------- */
 /* c[M,N] = x[M,K] * w[N,K]^T; all row-major bf16, 16-byte aligned, N and K multiples of 8. */
 int psdev_gemm_bf16(const void* x, const void* w, void* c, int64_t M, int64_t N, int64_t K,

@@ -123,6 +123,7 @@ def _declare(lib: C.CDLL) -> None:
         "psdev_sparse_apply": (i32, [C.POINTER(World), C.POINTER(Sparse), i32, i32, vp]),
         "psdev_sparse_respond": (i32, [C.POINTER(World), C.POINTER(Sparse), i32, i32, vp]),
         "psdev_lens_to_offsets": (i32, [vp, i64, vp, vp]),
+        "psdev_sparse_lens": (i32, [C.POINTER(World), C.POINTER(Sparse), i32, vp]),
     }
     for name, (res, args) in sig.items():
         if hasattr(lib, name):

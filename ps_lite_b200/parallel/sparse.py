@@ -144,6 +144,42 @@ class SparseTable:
         self.respond(sync=multi)
         return self.out[: self.count_vals]
 
+    def pull(self, keys: torch.Tensor, sync: "bool | None" = None):
+        """Pull without push.  Fixed width: the values of ``keys`` (``width`` per key).  With
+        ``var_len``: the owners first store the lengths they hold into this rank's array of
+        lengths (between two device barriers), then answer; returns ``(values, lens)`` with the
+        values packed back to back.  Collective on several ranks, like ``push_pull``."""
+        n = keys.numel()
+        if n > self.max_keys:
+            raise ValueError("more keys than max_keys")
+        multi = self.heap.world > 1 if sync is None else sync
+        lib, s = self.heap.lib, torch.cuda.current_stream(self.heap.device)
+        self.keys[:n].copy_(keys.view(torch.int64), non_blocking=True)
+        self.count = n
+        if not self.var_len:
+            self.count_vals = n * self.width
+            self.grads[: self.count_vals].zero_()
+            self.scatter()
+            self.apply(sync=multi)
+            self.respond(sync=multi)
+            return self.out[: self.count_vals]
+        self.lens[:n].zero_()
+        _lib.check(lib.psdev_key_shard_lookup(self.keys.data_ptr(), n, self.range,
+                                              self.heap.world, self.pos.data_ptr(),
+                                              s.cuda_stream), "key_shard_lookup")
+        if multi:
+            self.heap.barrier(self.barrier_channel)
+        _lib.check(lib.psdev_sparse_lens(C.byref(self._world), C.byref(self._t), 0,
+                                         s.cuda_stream), "sparse_lens")
+        if multi:
+            self.heap.barrier(self.barrier_channel)
+        _lib.check(lib.psdev_lens_to_offsets(self.lens.data_ptr(), n, self.offs.data_ptr(),
+                                             s.cuda_stream), "lens_to_offsets")
+        self.apply(sync=multi)
+        self.respond(sync=multi)
+        self.count_vals = int(self.offs[n].item())
+        return self.out[: self.count_vals], self.lens[:n]
+
     def check(self) -> None:
         self.heap.check_channel(self.barrier_channel)
         if self.capacity and int(self.overflow.item()):

@@ -303,7 +303,7 @@ __global__ void sparse_apply_kernel(const __grid_constant__ SparseArgs a) {
           long long off;
           int len;
           value_span(a, r, i, &off, &len);
-          a.klen[idx] = len;
+          if (len > 0) a.klen[idx] = len;  // a pull (length 0) leaves the stored length alone
         }
         const long long el = idx * a.width + j;
         const float g = atomicExch(acc + el, 0.f);
@@ -314,6 +314,33 @@ __global__ void sparse_apply_kernel(const __grid_constant__ SparseArgs a) {
   }
   // the round that this rendezvous opened is closed by the respond kernel, which follows on
   // the same stream
+}
+
+// Server: store the length of the value of every requested key into the requester's array of
+// lengths (a pull whose caller does not know the lengths).  Keys that own no slot get 0.
+__global__ void sparse_lens_kernel(const __grid_constant__ SparseArgs a) {
+  for (int rr = 0; rr < a.world; ++rr) {
+    int r = a.rank + rr;
+    if (r >= a.world) r -= a.world;
+    const long long* pos = reinterpret_cast<const long long*>(heap(a, r) + a.pos_off);
+    const long long lo = ld_volatile_s64(pos + a.rank), hi = ld_volatile_s64(pos + a.rank + 1);
+#ifdef PSDEV_CHECKS
+    if (lo < 0 || hi < lo || hi > a.max_n) {
+      if (threadIdx.x == 0 && blockIdx.x == 0) note_bounds(a);
+      continue;
+    }
+#endif
+    const unsigned long long* keys =
+        reinterpret_cast<const unsigned long long*>(heap(a, r) + a.keys_off);
+    int* lens = reinterpret_cast<int*>(heap(a, r) + a.lens_off);
+    for (long long i = lo + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < hi;
+         i += (long long)gridDim.x * blockDim.x) {
+      unsigned long long k;
+      asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(k) : "l"(keys + i) : "memory");
+      const long long idx = state_index(a, a.rank, k, false);
+      lens[i] = idx >= 0 ? a.klen[idx] : 0;
+    }
+  }
 }
 
 // Server: write the value of every requested key into the requester's output array, then wait
@@ -479,6 +506,20 @@ int psdev_sparse_respond(const psdev_world_t* w, const psdev_sparse_t* t, int nu
   if (rc) return rc;
   a.sync = sync ? 1 : 0;
   sparse_respond_kernel<<<num_ctas > 0 ? num_ctas : 592, 256, 0, (cudaStream_t)stream>>>(a);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return (int)cudaGetLastError();
+}
+
+// Server role: the stored length of every key that a worker staged (keys and cut points, see
+// psdev_key_shard_lookup) goes into that worker's array of lengths.  The caller orders it after
+// every rank's staging and before anybody reads the lengths (psdev_device_barrier on both sides).
+int psdev_sparse_lens(const psdev_world_t* w, const psdev_sparse_t* t, int num_ctas,
+                      void* stream) {
+  SparseArgs a{};
+  int rc = fill(&a, w, t, 0);
+  if (rc) return rc;
+  if (!t->lens_off || !t->klen) return PSDEV_ERR_ARG;
+  sparse_lens_kernel<<<num_ctas > 0 ? num_ctas : 296, 256, 0, (cudaStream_t)stream>>>(a);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return (int)cudaGetLastError();
 }

@@ -63,6 +63,10 @@ struct Rt {
   int (*sparse_scatter)(const psdev_world_t*, const psdev_sparse_t*, int64_t, int, void*) = nullptr;
   int (*sparse_apply)(const psdev_world_t*, const psdev_sparse_t*, int, int, void*) = nullptr;
   int (*sparse_respond)(const psdev_world_t*, const psdev_sparse_t*, int, int, void*) = nullptr;
+  int (*sparse_lens)(const psdev_world_t*, const psdev_sparse_t*, int, void*) = nullptr;
+  int (*key_shard_lookup)(const uint64_t*, int64_t, uint64_t, int, int64_t*, void*) = nullptr;
+  int (*lens_to_offsets)(const int32_t*, int64_t, int64_t*, void*) = nullptr;
+  int (*device_barrier)(const psdev_world_t*, int, uint64_t, void*) = nullptr;
   int (*is_device_pointer)(const void*) = nullptr;
   int (*heap_create)(size_t, void**, unsigned char*) = nullptr;
   int (*heap_open)(const unsigned char*, void**) = nullptr;
@@ -130,6 +134,10 @@ void* LoadRt(const std::string& configured, Rt* rt) {
   Bind(lib, "psdev_sparse_scatter", &rt->sparse_scatter);
   Bind(lib, "psdev_sparse_apply", &rt->sparse_apply);
   Bind(lib, "psdev_sparse_respond", &rt->sparse_respond);
+  Bind(lib, "psdev_sparse_lens", &rt->sparse_lens);
+  Bind(lib, "psdev_key_shard_lookup", &rt->key_shard_lookup);
+  Bind(lib, "psdev_lens_to_offsets", &rt->lens_to_offsets);
+  Bind(lib, "psdev_device_barrier", &rt->device_barrier);
   Bind(lib, "psdev_rt_is_device_pointer", &rt->is_device_pointer);
   Bind(lib, "psdev_heap_create", &rt->heap_create);
   Bind(lib, "psdev_heap_open", &rt->heap_open);
@@ -1043,7 +1051,7 @@ size_t Plane::PullBytes(int app_id, const SArray<Key>& keys) {
 // ---- keyed tables -----------------------------------------------------------------------------
 const SparseInfo& Plane::DeclareSparse(int app_id, uint64_t key_space, int64_t max_keys, int width,
                                        int kind, float lr, float alpha, float beta, float l1,
-                                       float l2) {
+                                       float l2, bool var_len) {
   Impl& m = *impl_;
   CHECK(m.started);
   CHECK(!m.sim) << "keyed tables need a GPU (the CPU stand-in serves dense tensors only)";
@@ -1055,6 +1063,7 @@ const SparseInfo& Plane::DeclareSparse(int app_id, uint64_t key_space, int64_t m
   sp->key_space = key_space;
   sp->max_keys = max_keys;
   sp->width = width;
+  sp->var_len = var_len;
   psdev_sparse_t& t = sp->table;
   t = psdev_sparse_t{};
   t.range = (key_space + W - 1) / W;
@@ -1077,6 +1086,10 @@ const SparseInfo& Plane::DeclareSparse(int app_id, uint64_t key_space, int64_t m
   t.pos_off = alloc(8 * static_cast<size_t>(W + 2));
   const size_t acc_bytes = 4 * static_cast<size_t>(t.slots) * width;
   t.acc_off = alloc(acc_bytes);
+  if (var_len) {
+    t.lens_off = alloc(4 * static_cast<size_t>(max_keys));
+    t.offs_off = alloc(8 * static_cast<size_t>(max_keys + 1));
+  }
   m.rt.set_device(m.opts.device);
   void* acc = Local(static_cast<int64_t>(t.acc_off));
   void* pos = Local(static_cast<int64_t>(t.pos_off));
@@ -1095,6 +1108,16 @@ const SparseInfo& Plane::DeclareSparse(int app_id, uint64_t key_space, int64_t m
   sp->keys = Local(static_cast<int64_t>(t.keys_off));
   sp->vals = Local(static_cast<int64_t>(t.grads_off));
   sp->out = Local(static_cast<int64_t>(t.out_off));
+  if (var_len) {
+    const size_t klen_bytes = 4 * static_cast<size_t>(t.slots);
+    CHECK_EQ(m.rt.malloc_(&p, klen_bytes), 0);
+    t.klen = static_cast<int32_t*>(p);
+    sp->lens = Local(static_cast<int64_t>(t.lens_off));
+    sp->offs = Local(static_cast<int64_t>(t.offs_off));
+    CHECK_EQ(m.rt.memset_async(t.klen, 0, klen_bytes, m.s_compute), 0);
+    CHECK_EQ(m.rt.memset_async(sp->lens, 0, 4 * static_cast<size_t>(max_keys), m.s_compute), 0);
+    CHECK_EQ(m.rt.stream_sync(m.s_compute), 0);
+  }
   SparseInfo* raw = sp.get();
   {
     std::lock_guard<std::mutex> lk(m.mu);
@@ -1337,12 +1360,25 @@ void Plane::SubmitSparse(const DeviceRequest& req) {
   const psdev_sparse_t& t = sp->table;
   const int64_t n = static_cast<int64_t>(req.keys.size());
   CHECK_LE(n, sp->max_keys) << "more keys than the table was declared for";
-  CHECK(req.lens.empty()) << "keyed tables of the plane take fixed-width values";
-  const size_t vbytes = static_cast<size_t>(n) * sp->width * 4;
-  if (req.push) {
-    CHECK(req.vals && req.vals_bytes == vbytes) << "expected " << sp->width << " fp32 per key";
+  // Tables with lengths: a push names the length of every value (a device array, like the keys);
+  // a pull asks the owners for the stored lengths first and returns them beside the values.
+  const bool ask_lens = sp->var_len && !req.push;
+  if (sp->var_len) {
+    if (req.push) { CHECK_EQ(static_cast<int64_t>(req.lens.size()), n) << "one length per key"; }
+  } else {
+    CHECK(req.lens.empty()) << "app " << req.app_id << " holds fixed-width values";
   }
-  if (req.pull && req.outs) { CHECK_EQ(req.outs_bytes, vbytes); }
+  const size_t cap_bytes = static_cast<size_t>(t.max_vals) * 4;
+  const size_t vbytes = sp->var_len ? req.vals_bytes : static_cast<size_t>(n) * sp->width * 4;
+  if (req.push) {
+    CHECK(req.vals && req.vals_bytes == vbytes && vbytes <= cap_bytes && vbytes % 4 == 0)
+        << "expected " << (sp->var_len ? "at most " : "") << sp->width << " fp32 per key";
+  }
+  const size_t obytes = sp->var_len ? req.outs_bytes : vbytes;
+  if (req.pull && req.outs) {
+    CHECK(req.outs_bytes == obytes && obytes <= cap_bytes) << "output of " << req.outs_bytes
+                                                           << " bytes does not fit the request";
+  }
   void* s = tls_has_stream ? tls_stream : m.s_compute;
   void* prev_done = nullptr;
   {
@@ -1359,15 +1395,38 @@ void Plane::SubmitSparse(const DeviceRequest& req) {
     if (req.vals != sp->vals) {
       CHECK_EQ(m.rt.memcpy_async(sp->vals, req.vals, vbytes, s), 0);
     }
-  } else {
+  } else if (!sp->var_len) {
     CHECK_EQ(m.rt.memset_async(sp->vals, 0, vbytes, s), 0);
   }
   const int sync = m.world > 1 ? 1 : 0;
-  CHECK_EQ(m.rt.sparse_scatter(&m.ws, &t, n, 0, s), 0) << "psdev_sparse_scatter failed";
+  const uint64_t tmo = t.timeout_ns ? t.timeout_ns : 20000000000ull;
+  if (sp->var_len && !ask_lens && req.lens.data() != sp->lens) {
+    CHECK_EQ(m.rt.memcpy_async(sp->lens, req.lens.data(), static_cast<size_t>(n) * 4, s), 0);
+  }
+  if (ask_lens) {
+    // cut points of my keys; then every owner stores the lengths it holds into the requesters'
+    // arrays (a device barrier on either side), and the offsets follow from them
+    CHECK_EQ(m.rt.memset_async(sp->lens, 0, static_cast<size_t>(n) * 4, s), 0);
+    CHECK_EQ(m.rt.key_shard_lookup(static_cast<const uint64_t*>(sp->keys), n, t.range, m.world,
+                                   static_cast<int64_t*>(Local(static_cast<int64_t>(t.pos_off))),
+                                   s), 0);
+    if (sync) { CHECK_EQ(m.rt.device_barrier(&m.ws, t.channel, tmo, s), 0); }
+    CHECK_EQ(m.rt.sparse_lens(&m.ws, &t, 0, s), 0) << "psdev_sparse_lens failed";
+    if (sync) { CHECK_EQ(m.rt.device_barrier(&m.ws, t.channel, tmo, s), 0); }
+    CHECK_EQ(m.rt.lens_to_offsets(static_cast<const int32_t*>(sp->lens), n,
+                                  static_cast<int64_t*>(sp->offs), s), 0);
+  } else {
+    CHECK_EQ(m.rt.sparse_scatter(&m.ws, &t, n, 0, s), 0) << "psdev_sparse_scatter failed";
+  }
   CHECK_EQ(m.rt.sparse_apply(&m.ws, &t, 0, sync, s), 0) << "psdev_sparse_apply failed";
   CHECK_EQ(m.rt.sparse_respond(&m.ws, &t, 0, sync, s), 0) << "psdev_sparse_respond failed";
   if (req.pull && req.outs && req.outs != sp->out) {
-    CHECK_EQ(m.rt.memcpy_async(req.outs, sp->out, vbytes, s), 0);
+    CHECK_EQ(m.rt.memcpy_async(req.outs, sp->out, obytes, s), 0);
+  }
+  if (sp->var_len && req.pull && req.lens_out && req.lens_out != sp->lens) {
+    // the lengths of the answer, beside it (device memory, like the keys)
+    CHECK_EQ(req.lens_out_n, static_cast<size_t>(n));
+    CHECK_EQ(m.rt.memcpy_async(req.lens_out, sp->lens, static_cast<size_t>(n) * 4, s), 0);
   }
   void* done = m.NewEvent();
   m.rt.event_record(done, s);

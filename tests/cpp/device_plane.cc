@@ -196,6 +196,64 @@ int main(int argc, char** argv) {
     for (size_t i = 0; i < back.size(); ++i) CHECK_EQ(back[i], 2 * want) << "at " << i;
     CHECK(&sp == plane->FindSparse(kApp));
   }
+
+  // 7. keyed requests with per-key lengths: key i carries 1 + i % 3 elements, packed back to
+  // back.  A push names the lengths; a pull-only request learns them from the owners and gets
+  // values and lengths back.
+  {
+    const int kApp = 4, width = 3;
+    const int64_t nk = 3000;
+    const uint64_t key_space = 1u << 18;
+    plane->DeclareSparse(kApp, key_space, nk, width, /*sum*/ 0, 0.f, 0.f, 0.f, 0.f, 0.f,
+                         /*var_len=*/true);
+    KVWorker<float> skv(kApp, 2);
+    std::vector<Key> hkeys(nk);
+    std::vector<int> hlens(nk);
+    int64_t total = 0;
+    for (int64_t i = 0; i < nk; ++i) {
+      hkeys[i] = static_cast<Key>(i) * (key_space / nk) + 3;
+      hlens[i] = 1 + static_cast<int>(i % 3);
+      total += hlens[i];
+    }
+    std::vector<float> hvals(total);
+    for (int64_t i = 0, o = 0; i < nk; ++i)
+      for (int j = 0; j < hlens[i]; ++j) hvals[o++] = static_cast<float>((R + 1) * (j + 1));
+    const int64_t koff = plane->Alloc(nk * 8), voff = plane->Alloc(total * 4),
+                  ooff = plane->Alloc(nk * width * 4), loff = plane->Alloc(nk * 4),
+                  l2off = plane->Alloc(nk * 4);
+    CHECK(koff >= 0 && voff >= 0 && ooff >= 0 && loff >= 0 && l2off >= 0);
+    Key* dkeys = static_cast<Key*>(plane->Local(koff));
+    float* dvals = static_cast<float*>(plane->Local(voff));
+    float* dout = static_cast<float*>(plane->Local(ooff));
+    int* dlens = static_cast<int*>(plane->Local(loff));
+    int* dlens_back = static_cast<int*>(plane->Local(l2off));
+    plane->Memcpy(dkeys, hkeys.data(), nk * 8);
+    plane->Memcpy(dvals, hvals.data(), total * 4);
+    plane->Memcpy(dlens, hlens.data(), nk * 4);
+    SArray<Key> sk = SArray<Key>::FromDevice(dkeys, nk);
+    SArray<float> sv = SArray<float>::FromDevice(dvals, total);
+    SArray<int> sl = SArray<int>::FromDevice(dlens, nk);
+    skv.Wait(skv.ZPush(sk, sv, sl));
+    // pull only: the caller sizes the output for the widest case and names no lengths
+    SArray<float> so = SArray<float>::FromDevice(dout, nk * width);
+    SArray<int> slb = SArray<int>::FromDevice(dlens_back, nk);
+    skv.Wait(skv.ZPull(sk, &so, &slb));
+    std::vector<int> lens_back(nk);
+    std::vector<float> back(total);
+    plane->Memcpy(lens_back.data(), dlens_back, nk * 4);
+    plane->Memcpy(back.data(), dout, total * 4);
+    const float tri = 0.5f * W * (W + 1);
+    for (int64_t i = 0, o = 0; i < nk; ++i) {
+      CHECK_EQ(lens_back[i], hlens[i]) << "length of key " << i;
+      for (int j = 0; j < hlens[i]; ++j, ++o) CHECK_EQ(back[o], tri * (j + 1)) << "key " << i;
+    }
+    // push + pull in one request, lengths named
+    SArray<float> so2 = SArray<float>::FromDevice(dout, total);
+    skv.Wait(skv.ZPushPull(sk, sv, &so2, &sl));
+    plane->Memcpy(back.data(), dout, total * 4);
+    for (int64_t i = 0, o = 0; i < nk; ++i)
+      for (int j = 0; j < hlens[i]; ++j, ++o) CHECK_EQ(back[o], 2 * tri * (j + 1)) << "key " << i;
+  }
 #endif
 
   CHECK_GT(plane->launches(), (uint64_t)0);

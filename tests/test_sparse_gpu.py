@@ -122,6 +122,74 @@ def test_sparse_wide_and_dynamic_length_values(cuda_device, world, var_len):
             t.check()
 
 
+@pytest.mark.parametrize("world", [1, 4])
+def test_pull_learns_lengths_from_owners(cuda_device, world):
+    """A pull on a table with lengths names none: the owners store the lengths they hold into
+    the requester's array, the values come back packed; a key nobody pushed has length 0."""
+    import ctypes as C
+    from ps_lite_b200 import _lib
+    from ps_lite_b200.parallel import SparseTable, SymmetricHeap
+    key_space, n, width = 1 << 14, 2000, 4
+    nbytes = 65536 + 64 * n * width + 4 * width * ((key_space + world - 1) // world) + (1 << 20)
+    heaps = (SymmetricHeap.emulated(nbytes, world, device=cuda_device) if world > 1
+             else [SymmetricHeap(nbytes, 0, 1, device=cuda_device)])
+    tables = [SparseTable(h, key_space, n, kind="sum", width=width, var_len=True) for h in heaps]
+    gen = torch.Generator(device=cuda_device)
+    gen.manual_seed(9)
+    key_len = torch.randint(1, width + 1, (key_space,), generator=gen, device=cuda_device)
+    dense = torch.zeros(key_space, width, device=cuda_device)
+    pushed = torch.zeros(key_space, dtype=torch.bool, device=cuda_device)
+    for t in tables:   # one push per rank (phases of all ranks run one after the other)
+        keys = _zipf_keys(n, key_space, gen, cuda_device)
+        keys = keys[keys % 2 == 0]          # odd keys are never pushed
+        lens = key_len[keys]
+        vals = torch.randn(int(lens.sum().item()), generator=gen, device=cuda_device)
+        t.stage(keys, vals, lens)
+        offs = torch.cumsum(lens, 0) - lens
+        for j in range(width):
+            m = lens > j
+            dense[keys[m], j] += vals[(offs + j)[m]]
+        pushed[keys] = True
+    for phase in ("scatter", "apply", "respond"):
+        for t in tables:
+            getattr(t, phase)()
+    torch.cuda.synchronize()
+    asks = [_zipf_keys(n - 11 * r, key_space, gen, cuda_device) for r in range(world)]
+    if world == 1:
+        got, lens = tables[0].pull(asks[0])
+        results = [(got.clone(), lens.clone())]
+    else:
+        s = torch.cuda.current_stream().cuda_stream
+        for t, keys in zip(tables, asks):
+            k = keys.numel()
+            t.keys[:k].copy_(keys)
+            t.count = k
+            t.lens[:k].zero_()
+            assert t.heap.lib.psdev_key_shard_lookup(t.keys.data_ptr(), k, t.range, world,
+                                                     t.pos.data_ptr(), s) == 0
+        for t in tables:
+            assert t.heap.lib.psdev_sparse_lens(C.byref(t._world), C.byref(t._t), 0, s) == 0
+        for t, keys in zip(tables, asks):
+            assert t.heap.lib.psdev_lens_to_offsets(t.lens.data_ptr(), keys.numel(),
+                                                    t.offs.data_ptr(), s) == 0
+        for phase in ("apply", "respond"):
+            for t in tables:
+                getattr(t, phase)()
+        torch.cuda.synchronize()
+        results = [(t.out[: int(t.offs[k.numel()].item())].clone(), t.lens[: k.numel()].clone())
+                   for t, k in zip(tables, asks)]
+    for keys, (got, lens) in zip(asks, results):
+        want_lens = torch.where(pushed[keys], key_len[keys], torch.zeros_like(keys)).int()
+        assert torch.equal(lens, want_lens)
+        offs = torch.cumsum(want_lens.long(), 0) - want_lens.long()
+        assert got.numel() == int(want_lens.sum().item())
+        for j in range(width):
+            m = want_lens > j
+            torch.testing.assert_close(got[(offs + j)[m]], dense[keys[m], j], rtol=1e-5, atol=1e-5)
+    for t in tables:
+        t.check()
+
+
 def test_key_shard_lookup(cuda_device):
     from ps_lite_b200 import _lib
     lib = _lib.device_lib()
