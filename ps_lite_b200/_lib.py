@@ -117,6 +117,7 @@ def _declare(lib: C.CDLL) -> None:
         "psdev_filter_int8_unpack": (i32, [vp, vp, vp, i64, i32, vp]),
         "psdev_sort_scratch_bytes": (sz, [i64, i32]),
         "psdev_sort_keys": (i32, [vp, vp, i64, i32, vp, sz, vp]),
+        "psdev_sort_status": (i32, [vp, vp]),
         "psdev_ordered_match": (i32, [vp, vp, i64, vp, vp, i64, i32, i32, i32, vp, vp]),
         "psdev_key_shard_lookup": (i32, [vp, i64, u64, i32, vp, vp]),
         "psdev_sparse_scatter": (i32, [C.POINTER(World), C.POINTER(Sparse), i64, i32, vp]),

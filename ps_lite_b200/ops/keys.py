@@ -14,11 +14,12 @@ from .. import _lib
 ASSIGN, PLUS, MINUS, TIMES, DIVIDE, AND, OR, XOR = range(8)
 
 
-def sort_keys(keys: torch.Tensor, key_bits: int = 64, return_perm: bool = False
-              ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+def sort_keys(keys: torch.Tensor, key_bits: int = 64, return_perm: bool = False,
+              check: bool = False) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """Sort uint64 keys (stored as int64 bit patterns) ascending, in place; keys must be below
     ``2**key_bits``.  With ``return_perm`` also returns the stable permutation (int32 indices
-    into the input)."""
+    into the input).  ``check`` waits for the sort and raises if one of its bounded waits (a
+    tile looking back at the tiles before it) ran out."""
     assert keys.is_cuda and keys.dtype == torch.int64 and keys.is_contiguous()
     lib = _lib.device_lib()
     n = keys.numel()
@@ -29,6 +30,10 @@ def sort_keys(keys: torch.Tensor, key_bits: int = 64, return_perm: bool = False
                              key_bits, scratch.data_ptr(), nbytes,
                              torch.cuda.current_stream(keys.device).cuda_stream)
     _lib.check(rc, "psdev_sort_keys")
+    if check:
+        _lib.check(lib.psdev_sort_status(scratch.data_ptr(),
+                                         torch.cuda.current_stream(keys.device).cuda_stream),
+                   "psdev_sort_status")
     return keys, perm
 
 

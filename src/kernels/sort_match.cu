@@ -20,22 +20,42 @@ namespace psdev {
 extern std::atomic<uint64_t> g_launches;
 
 namespace sortk {
-// Least-significant-digit radix sort with 8-bit digits.  One pass = three kernels:
-//   tile_count  every CTA counts the digits of its tile of 4096 keys (warp-aggregated shared
-//               atomics) into hist[digit][tile] and adds them to the pass's 256 digit totals;
-//   tile_scan   one CTA per digit: exclusive prefix of that digit's row over the tiles, plus
-//               the number of keys with smaller digits -> where each (digit, tile) group starts;
-//   scatter     every CTA re-reads its tile, ranks each key among the keys of the same digit
-//               in the tile, in input order (the sort is stable), and stores key and payload at
-//               group start + rank.
+// Least-significant-digit radix sort with 8-bit digits, one sweep per pass:
+//   digit_hist   reads the keys once and counts the digits of EVERY pass (shared-memory atomics,
+//                then one global add per digit and CTA);
+//   digit_scan   exclusive prefix of each pass's 256 totals -> where each digit's run starts;
+//   sweep        one launch per pass.  A CTA takes the next tile of 4096 keys from a counter (so
+//                every earlier tile belongs to a CTA that is already running), ranks each key
+//                among the keys of the same digit in the tile, in input order (the sort is
+//                stable), publishes the tile's 256 digit counts, and finds how many keys of each
+//                digit precede the tile by looking back over the earlier tiles' published words:
+//                a tile's own counts ("aggregate") until one is met whose word already holds the
+//                whole prefix ("inclusive").  Keys (and payloads) are then put in sorted order
+//                inside the tile in shared memory and stored, runs of equal digits to consecutive
+//                addresses.
 // ceil(key_bits / 8) passes: a caller that knows its keys are below 2^30 pays four passes,
-// not eight.
+// not eight.  Per pass every key is read once and written once.
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kItems = 16;                 // keys per thread
 constexpr int kTile = kThreads * kItems;   // keys per CTA
 constexpr int kRadixBits = 8;
 constexpr int kDigits = 1 << kRadixBits;
+constexpr int kMaxPasses = 64 / kRadixBits;
+
+// one word per (tile, digit): 2 flag bits and a 30-bit count
+constexpr unsigned int kFlagAggregate = 1u << 30;
+constexpr unsigned int kFlagInclusive = 2u << 30;
+constexpr unsigned int kCountMask = (1u << 30) - 1;
+constexpr unsigned long long kLookbackNs = 2000000000ull;  // bound of one look-back wait
+
+// Head of the scratch memory, cleared before every sort.
+struct SortHead {
+  int error;                                   // 1: a look-back wait ran out
+  unsigned int next_tile[kMaxPasses];          // tile counter of each pass
+  unsigned int pad[23];
+  unsigned int hist[kMaxPasses * kDigits];     // digit totals, then (digit_scan) run starts
+};
 
 __device__ __forceinline__ unsigned int digit_of(unsigned long long k, int shift) {
   return (unsigned int)((k >> shift) & (kDigits - 1));
@@ -45,76 +65,76 @@ __device__ __forceinline__ unsigned int lanemask_lt() {
   asm("mov.u32 %0, %%lanemask_lt;" : "=r"(m));
   return m;
 }
+__device__ __forceinline__ unsigned int ld_relaxed(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed(unsigned int* p, unsigned int v) {
+  asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
-// hist[d * ntiles + tile] = keys of the tile with digit d; totals[d] += the same
+// Lanes of the warp whose (valid, digit) equal this lane's: one ballot per digit bit.
+__device__ __forceinline__ unsigned int peers_of(unsigned int d, bool valid) {
+  unsigned int m = __ballot_sync(0xffffffffu, valid);
+  if (!valid) m = ~m;
+#pragma unroll
+  for (int b = 0; b < kRadixBits; ++b) {
+    const bool bit = (d >> b) & 1u;
+    const unsigned int v = __ballot_sync(0xffffffffu, bit);
+    m &= bit ? v : ~v;
+  }
+  return m;
+}
+
+// hist[pass * 256 + d] += keys whose digit of that pass is d
 __global__ void __launch_bounds__(kThreads)
-    tile_count_kernel(const unsigned long long* keys, long long n, int shift, unsigned int* hist,
-                      unsigned int* totals, int ntiles) {
+    digit_hist_kernel(const unsigned long long* keys, long long n, int passes, unsigned int* hist) {
+  __shared__ unsigned int s[kMaxPasses * kDigits];
+  for (int i = threadIdx.x; i < passes * kDigits; i += kThreads) s[i] = 0;
+  __syncthreads();
+  for (long long i = blockIdx.x * (long long)kThreads + threadIdx.x; i < n;
+       i += (long long)gridDim.x * kThreads) {
+    const unsigned long long k = keys[i];
+    for (int p = 0; p < passes; ++p) atomicAdd(&s[p * kDigits + digit_of(k, p * kRadixBits)], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < passes * kDigits; i += kThreads)
+    if (s[i]) atomicAdd(&hist[i], s[i]);
+}
+
+// One CTA per pass: totals -> exclusive prefix (the output index where each digit's run starts).
+__global__ void __launch_bounds__(kDigits) digit_scan_kernel(unsigned int* hist) {
   __shared__ unsigned int s[kDigits];
-  s[threadIdx.x] = 0;
+  unsigned int* row = hist + blockIdx.x * kDigits;
+  const unsigned int mine = row[threadIdx.x];
+  s[threadIdx.x] = mine;
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long base = (long long)blockIdx.x * kTile + (long long)warp * (32 * kItems) + lane;
-#pragma unroll 4
-  for (int j = 0; j < kItems; ++j) {
-    const long long i = base + j * 32;
-    const bool valid = i < n;
-    // lanes past the end vote with a digit no key can have
-    const unsigned int d = valid ? digit_of(keys[i], shift) : (unsigned int)kDigits;
-    const unsigned int same = __match_any_sync(0xffffffffu, d);
-    if (valid && (same & lanemask_lt()) == 0) atomicAdd(&s[d], (unsigned int)__popc(same));
+  unsigned int incl = mine;
+  for (int off = 1; off < kDigits; off <<= 1) {
+    const unsigned int v = threadIdx.x >= off ? s[threadIdx.x - off] : 0u;
+    __syncthreads();
+    incl += v;
+    s[threadIdx.x] = incl;
+    __syncthreads();
   }
-  __syncthreads();
-  const unsigned int c = s[threadIdx.x];
-  hist[(size_t)threadIdx.x * ntiles + blockIdx.x] = c;
-  if (c) atomicAdd(&totals[threadIdx.x], c);
+  row[threadIdx.x] = incl - mine;
 }
 
-// One CTA per digit: hist row -> exclusive prefix over the tiles + keys with smaller digits.
-__global__ void __launch_bounds__(1024)
-    tile_scan_kernel(unsigned int* hist, const unsigned int* totals, int ntiles) {
-  __shared__ unsigned int s[1024];
-  __shared__ unsigned int carry;
-  const int d = blockIdx.x;
-  // keys with a smaller digit
-  unsigned int below = 0;
-  for (int j = threadIdx.x; j < d; j += 1024) below += totals[j];
-  s[threadIdx.x] = below;
-  __syncthreads();
-  for (int off = 512; off > 0; off >>= 1) {
-    if (threadIdx.x < off) s[threadIdx.x] += s[threadIdx.x + off];
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) carry = s[0];
-  __syncthreads();
-  unsigned int* row = hist + (size_t)d * ntiles;
-  for (int base = 0; base < ntiles; base += 1024) {
-    const int i = base + threadIdx.x;
-    const unsigned int v = i < ntiles ? row[i] : 0u;
-    __syncthreads();
-    s[threadIdx.x] = v;
-    __syncthreads();
-    for (int off = 1; off < 1024; off <<= 1) {
-      const unsigned int t = threadIdx.x >= off ? s[threadIdx.x - off] : 0u;
-      __syncthreads();
-      s[threadIdx.x] += t;
-      __syncthreads();
-    }
-    if (i < ntiles) row[i] = carry + s[threadIdx.x] - v;
-    __syncthreads();
-    if (threadIdx.x == 1023) carry += s[1023];
-  }
-}
+// One pass.  Shared memory: the tile's keys and payloads in sorted order, per-warp digit
+// counters, and two 256-entry tables.
+constexpr int kSweepSmem = kTile * 8 + kTile * 4 + kWarps * kDigits * 4 + 2 * kDigits * 4;
 
-// Stable scatter of one 8-bit digit.  Keys (and payloads) are first put in sorted order inside
-// the tile in shared memory, then stored: consecutive threads store consecutive keys of one
-// digit, i.e. consecutive addresses.
-constexpr int kScatterSmem = kTile * 8 + kTile * 4 + kWarps * kDigits * 4 + 2 * kDigits * 4;
-
-__global__ void __launch_bounds__(kThreads)
-    scatter_kernel(const unsigned long long* keys_in, unsigned long long* keys_out,
-                   const unsigned int* pay_in, unsigned int* pay_out, long long n, int shift,
-                   const unsigned int* offsets, int ntiles) {
+__global__ void __launch_bounds__(kThreads, 3)
+    sweep_kernel(const unsigned long long* keys_in, unsigned long long* keys_out,
+                 const unsigned int* pay_in, unsigned int* pay_out, long long n, int shift,
+                 const unsigned int* run_start, unsigned int* status, unsigned int* next_tile,
+                 int* error) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   unsigned long long* skeys = reinterpret_cast<unsigned long long*>(smem_raw);
   unsigned int* spay = reinterpret_cast<unsigned int*>(smem_raw + kTile * 8);
@@ -125,11 +145,14 @@ __global__ void __launch_bounds__(kThreads)
   unsigned int* tile_start = reinterpret_cast<unsigned int*>(smem_raw + kTile * 12 +
                                                              kWarps * kDigits * 4);
   unsigned int* goff = tile_start + kDigits;  // output index of sorted position q: goff[d] + q
+  __shared__ unsigned int s_tile;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) s_tile = atomicAdd(next_tile, 1u);
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) cnt[w][threadIdx.x] = 0;
   __syncthreads();
-  const long long tile_base = (long long)blockIdx.x * kTile;
+  const unsigned int tile = s_tile;
+  const long long tile_base = (long long)tile * kTile;
   const long long base = tile_base + (long long)warp * (32 * kItems) + lane;
   const int tile_n = (int)(n - tile_base < kTile ? n - tile_base : kTile);
   unsigned long long k[kItems];
@@ -137,10 +160,13 @@ __global__ void __launch_bounds__(kThreads)
 #pragma unroll
   for (int j = 0; j < kItems; ++j) {
     const long long i = base + j * 32;
-    const bool valid = i < n;
-    k[j] = valid ? keys_in[i] : ~0ull;
-    const unsigned int d = valid ? digit_of(k[j], shift) : (unsigned int)kDigits;
-    const unsigned int same = __match_any_sync(0xffffffffu, d);
+    k[j] = i < n ? keys_in[i] : ~0ull;
+  }
+#pragma unroll
+  for (int j = 0; j < kItems; ++j) {
+    const bool valid = base + j * 32 < n;
+    const unsigned int d = digit_of(k[j], shift);
+    const unsigned int same = peers_of(d, valid);
     const unsigned int before = __popc(same & lanemask_lt());
     unsigned int seen = 0;
     if (valid) seen = cnt[warp][d];
@@ -150,22 +176,50 @@ __global__ void __launch_bounds__(kThreads)
     rank[j] = (unsigned short)(seen + before);
   }
   __syncthreads();
-  {
-    // digit threadIdx.x: each warp's start inside the digit's run, and the run's length
-    unsigned int run = 0;
+  // digit threadIdx.x: each warp's start inside the digit's run, and the run's length
+  unsigned int run = 0;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-      const unsigned int c = cnt[w][threadIdx.x];
-      cnt[w][threadIdx.x] = run;
-      run += c;
+  for (int w = 0; w < kWarps; ++w) {
+    const unsigned int c = cnt[w][threadIdx.x];
+    cnt[w][threadIdx.x] = run;
+    run += c;
+  }
+  tile_start[threadIdx.x] = run;
+  // publish this tile's count of the digit, then add up the earlier tiles' counts
+  unsigned int* mine = status + (size_t)tile * kDigits + threadIdx.x;
+  unsigned int before_tile = 0;
+  if (tile == 0) {
+    st_relaxed(mine, kFlagInclusive | run);
+  } else {
+    st_relaxed(mine, kFlagAggregate | run);
+    const unsigned int* look = mine - kDigits;
+    unsigned long long t0 = 0;
+    for (unsigned int left = tile; left > 0; --left, look -= kDigits) {
+      unsigned int v = ld_relaxed(look);
+      unsigned int polls = 0;
+      while ((v >> 30) == 0) {
+        // the earlier tile's CTA is running (it took its tile before this one did) but has not
+        // ranked its keys yet
+        if ((++polls & 63u) == 0) {
+          const unsigned long long t = now_ns();
+          if (t0 == 0) t0 = t;
+          if (t - t0 > kLookbackNs) break;
+        }
+        v = ld_relaxed(look);
+      }
+      if ((v >> 30) == 0) {
+        *error = 1;  // the output of this sort is not valid
+        break;
+      }
+      before_tile += v & kCountMask;
+      if (v & kFlagInclusive) break;
     }
-    tile_start[threadIdx.x] = run;
+    st_relaxed(mine, kFlagInclusive | ((before_tile + run) & kCountMask));
   }
   __syncthreads();
   // exclusive prefix of the run lengths over the digits (256 values, one per thread)
   {
-    const unsigned int mine = tile_start[threadIdx.x];
-    unsigned int incl = mine;
+    unsigned int incl = run;
     for (int off = 1; off < kDigits; off <<= 1) {
       const unsigned int v = threadIdx.x >= off ? tile_start[threadIdx.x - off] : 0u;
       __syncthreads();
@@ -173,10 +227,10 @@ __global__ void __launch_bounds__(kThreads)
       tile_start[threadIdx.x] = incl;
       __syncthreads();
     }
-    const unsigned int excl = incl - mine;
+    const unsigned int excl = incl - run;
     __syncthreads();
     tile_start[threadIdx.x] = excl;
-    goff[threadIdx.x] = offsets[(size_t)threadIdx.x * ntiles + blockIdx.x] - excl;
+    goff[threadIdx.x] = run_start[threadIdx.x] + before_tile - excl;
   }
   __syncthreads();
 #pragma unroll
@@ -265,70 +319,77 @@ using namespace psdev::sortk;
 
 extern "C" {
 
+static size_t round256(size_t b) { return (b + 255) & ~size_t(255); }
+
 // Bytes of scratch psdev_sort_keys needs for n keys (with or without a payload).
 size_t psdev_sort_scratch_bytes(int64_t n, int with_payload) {
-  const int64_t ntiles = (n + kTile - 1) / kTile;
-  size_t b = ((size_t)n * 8 + 255) & ~size_t(255);                 // second key buffer
-  if (with_payload) b += (((size_t)n * 4 + 255) & ~size_t(255));   // second payload buffer
-  b += (((size_t)ntiles * kDigits * 4 + 255) & ~size_t(255));      // digit counts per tile
-  b += 8 * kDigits * 4;                                            // digit totals per pass
+  const size_t ntiles = (size_t)((n + kTile - 1) / kTile);
+  size_t b = round256(sizeof(SortHead));
+  b += round256(ntiles * kDigits * 4 * kMaxPasses);   // one word per (pass, tile, digit)
+  b += round256((size_t)n * 8);                        // second key buffer
+  if (with_payload) b += round256((size_t)n * 4);      // second payload buffer
   return b + 256;
 }
 
 // Sorts `n` 64-bit keys ascending by their low `key_bits` bits (64 for full keys; fewer bits
 // = fewer passes).  `keys` is sorted in place.  If `perm` is not NULL it receives, for every
 // output position, the index the key had in the input (a stable sort permutation).
-// `scratch` is device memory of psdev_sort_scratch_bytes(n, perm != NULL) bytes.
+// `scratch` is device memory of psdev_sort_scratch_bytes(n, perm != NULL) bytes; n < 2^30.
+// psdev_sort_status(scratch) tells afterwards whether a wait inside the sort ran out.
 int psdev_sort_keys(uint64_t* keys, uint32_t* perm, int64_t n, int key_bits, void* scratch,
                     size_t scratch_bytes, void* stream) {
   if (n < 0 || key_bits < 1 || key_bits > 64 || !keys) return PSDEV_ERR_ARG;
   if (n == 0) return 0;
-  if (n >= (int64_t)1 << 32) return PSDEV_ERR_UNSUPPORTED;
+  if (n >= (int64_t)1 << 30) return PSDEV_ERR_UNSUPPORTED;
   if (!scratch || scratch_bytes < psdev_sort_scratch_bytes(n, perm != nullptr))
     return PSDEV_ERR_ARG;
   cudaStream_t s = (cudaStream_t)stream;
   const int ntiles = (int)((n + kTile - 1) / kTile);
+  const int passes = (key_bits + kRadixBits - 1) / kRadixBits;
   char* p = static_cast<char*>(scratch);
   p = reinterpret_cast<char*>(((uintptr_t)p + 255) & ~uintptr_t(255));
+  SortHead* head = reinterpret_cast<SortHead*>(p);
+  p += round256(sizeof(SortHead));
+  unsigned int* status = reinterpret_cast<unsigned int*>(p);
+  const size_t status_pass = (size_t)ntiles * kDigits;
+  // head and the status words of the passes that run are cleared together
+  const size_t clear = round256(sizeof(SortHead)) + status_pass * 4 * passes;
+  p += round256(status_pass * 4 * kMaxPasses);
   unsigned long long* alt = reinterpret_cast<unsigned long long*>(p);
-  p += ((size_t)n * 8 + 255) & ~size_t(255);
+  p += round256((size_t)n * 8);
   unsigned int* alt_pay = nullptr;
-  if (perm) {
-    alt_pay = reinterpret_cast<unsigned int*>(p);
-    p += ((size_t)n * 4 + 255) & ~size_t(255);
-    iota_kernel<<<296, 256, 0, s>>>(perm, n);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-  }
-  unsigned int* hist = reinterpret_cast<unsigned int*>(p);
-  p += ((size_t)ntiles * kDigits * 4 + 255) & ~size_t(255);
-  unsigned int* totals = reinterpret_cast<unsigned int*>(p);
-  const int passes = (key_bits + kRadixBits - 1) / kRadixBits;
+  if (perm) alt_pay = reinterpret_cast<unsigned int*>(p);
   {
-    // the scatter kernel's tile buffers exceed the default limit of dynamic shared memory
+    // the sweep kernel's tile buffers exceed the default limit of dynamic shared memory
     static std::atomic<bool> attr_set[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (!attr_set[dev & 63].load(std::memory_order_acquire)) {
-      cudaError_t e = cudaFuncSetAttribute(scatter_kernel,
+      cudaError_t e = cudaFuncSetAttribute(sweep_kernel,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           kScatterSmem);
+                                           kSweepSmem);
       if (e != cudaSuccess) return (int)e;
       attr_set[dev & 63].store(true, std::memory_order_release);
     }
   }
-  cudaMemsetAsync(totals, 0, (size_t)passes * kDigits * 4, s);
+  cudaMemsetAsync(head, 0, clear, s);
+  if (perm) {
+    iota_kernel<<<296, 256, 0, s>>>(perm, n);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
   unsigned long long* in = reinterpret_cast<unsigned long long*>(keys);
   unsigned long long* out = alt;
   unsigned int* pin = perm;
   unsigned int* pout = alt_pay;
+  const int hist_ctas = ntiles < 592 ? ntiles : 592;
+  digit_hist_kernel<<<hist_ctas, kThreads, 0, s>>>(in, n, passes, head->hist);
+  digit_scan_kernel<<<passes, kDigits, 0, s>>>(head->hist);
+  g_launches.fetch_add(2, std::memory_order_relaxed);
   for (int pass = 0; pass < passes; ++pass) {
-    const int shift = pass * kRadixBits;
-    unsigned int* tot = totals + pass * kDigits;
-    tile_count_kernel<<<ntiles, kThreads, 0, s>>>(in, n, shift, hist, tot, ntiles);
-    tile_scan_kernel<<<kDigits, 1024, 0, s>>>(hist, tot, ntiles);
-    scatter_kernel<<<ntiles, kThreads, kScatterSmem, s>>>(in, out, pin, pout, n, shift, hist,
-                                                         ntiles);
-    g_launches.fetch_add(3, std::memory_order_relaxed);
+    sweep_kernel<<<ntiles, kThreads, kSweepSmem, s>>>(
+        in, out, pin, pout, n, pass * kRadixBits, head->hist + pass * kDigits,
+        status + status_pass * pass, &head->next_tile[pass], &head->error);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     unsigned long long* t = in; in = out; out = t;
     unsigned int* tp = pin; pin = pout; pout = tp;
   }
@@ -338,6 +399,19 @@ int psdev_sort_keys(uint64_t* keys, uint32_t* perm, int64_t n, int key_bits, voi
     if (perm) cudaMemcpyAsync(perm, pin, (size_t)n * 4, cudaMemcpyDeviceToDevice, s);
   }
   return (int)cudaGetLastError();
+}
+
+// 0 when the last sort that used `scratch` completed every look-back, PSDEV_ERR_TIMEOUT_ENTRY
+// when one ran out (the output of that sort is not valid).  Waits for `stream`.
+int psdev_sort_status(const void* scratch, void* stream) {
+  if (!scratch) return PSDEV_ERR_ARG;
+  const char* p = reinterpret_cast<const char*>(((uintptr_t)scratch + 255) & ~uintptr_t(255));
+  int err = 0;
+  cudaError_t e = cudaMemcpyAsync(&err, p, sizeof(int), cudaMemcpyDeviceToHost,
+                                  (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  return err ? PSDEV_ERR_TIMEOUT_ENTRY : 0;
 }
 
 // dst_vals[j] op= src_vals[i] for every key present in both sorted unique lists; values have

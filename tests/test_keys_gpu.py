@@ -6,7 +6,8 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("n,bits", [(1, 64), (1000, 64), (300_001, 64), (2_000_000, 30),
-                                    (5000, 12)])
+                                    (5000, 12), (4096 * 3, 64), (4096 * 3 + 1, 20),
+                                    (5_000_000, 64)])
 def test_sort_keys(cuda_device, n, bits):
     from ps_lite_b200.ops.keys import sort_keys
     g = torch.Generator(device=cuda_device)
@@ -16,13 +17,39 @@ def test_sort_keys(cuda_device, n, bits):
     if bits == 64:
         keys[::7] |= torch.iinfo(torch.int64).min  # top bit set: large unsigned values
     orig = keys.clone()
-    out, perm = sort_keys(keys, bits, return_perm=True)
+    out, perm = sort_keys(keys, bits, return_perm=True, check=True)
     torch.cuda.synchronize()
     # unsigned order: compare through a sign flip
     flip = orig ^ torch.iinfo(torch.int64).min
     ref_sorted, ref_idx = torch.sort(flip, stable=True)
     assert torch.equal(out ^ torch.iinfo(torch.int64).min, ref_sorted)
     assert torch.equal(perm.long(), ref_idx)
+
+
+@pytest.mark.parametrize("kind", ["equal", "two_values", "skewed", "sorted", "reversed"])
+def test_sort_keys_hard_distributions(cuda_device, kind):
+    """Inputs that stress the ranking and the look-back: one digit everywhere, long runs, a
+    skewed distribution, and already ordered keys; keys only and with the permutation."""
+    from ps_lite_b200.ops.keys import sort_keys
+    n = 1_000_003
+    g = torch.Generator(device=cuda_device)
+    g.manual_seed(3)
+    if kind == "equal":
+        keys = torch.full((n,), 0x1234_5678_9ABC, device=cuda_device, dtype=torch.int64)
+    elif kind == "two_values":
+        keys = torch.randint(0, 2, (n,), device=cuda_device, dtype=torch.int64, generator=g) << 40
+    elif kind == "skewed":
+        u = torch.rand(n, device=cuda_device, generator=g)
+        keys = (u.pow(8) * (1 << 40)).long()
+    elif kind == "sorted":
+        keys = torch.arange(n, device=cuda_device, dtype=torch.int64) * 977
+    else:
+        keys = torch.arange(n, 0, -1, device=cuda_device, dtype=torch.int64) * 977
+    ref_sorted, ref_idx = torch.sort(keys, stable=True)
+    only, none = sort_keys(keys.clone(), 48, check=True)
+    assert none is None and torch.equal(only, ref_sorted)
+    out, perm = sort_keys(keys.clone(), 48, return_perm=True, check=True)
+    assert torch.equal(out, ref_sorted) and torch.equal(perm.long(), ref_idx)
 
 
 def test_sort_unique_sum_and_ordered_match(cuda_device):
