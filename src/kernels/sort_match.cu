@@ -98,10 +98,17 @@ __global__ void __launch_bounds__(kThreads)
   __shared__ unsigned int s[kMaxPasses * kDigits];
   for (int i = threadIdx.x; i < passes * kDigits; i += kThreads) s[i] = 0;
   __syncthreads();
-  for (long long i = blockIdx.x * (long long)kThreads + threadIdx.x; i < n;
-       i += (long long)gridDim.x * kThreads) {
-    const unsigned long long k = keys[i];
-    for (int p = 0; p < passes; ++p) atomicAdd(&s[p * kDigits + digit_of(k, p * kRadixBits)], 1u);
+  // four independent loads in flight per thread
+  const long long stride = (long long)gridDim.x * kThreads;
+  for (long long i0 = blockIdx.x * (long long)kThreads + threadIdx.x; i0 < n; i0 += 4 * stride) {
+    unsigned long long k[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) k[u] = i0 + u * stride < n ? keys[i0 + u * stride] : 0ull;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i0 + u * stride < n)
+        for (int p = 0; p < passes; ++p)
+          atomicAdd(&s[p * kDigits + digit_of(k[u], p * kRadixBits)], 1u);
   }
   __syncthreads();
   for (int i = threadIdx.x; i < passes * kDigits; i += kThreads)
@@ -128,9 +135,9 @@ __global__ void __launch_bounds__(kDigits) digit_scan_kernel(unsigned int* hist)
 
 // One pass.  Shared memory: the tile's keys and payloads in sorted order, per-warp digit
 // counters, and two 256-entry tables.
-constexpr int kSweepSmem = kTile * 8 + kTile * 4 + kWarps * kDigits * 4 + 2 * kDigits * 4;
+constexpr int kSweepSmem = kTile * 8 + kTile * 4 + kWarps * kDigits * 2 + 2 * kDigits * 4;
 
-__global__ void __launch_bounds__(kThreads, 3)
+__global__ void __launch_bounds__(kThreads, 4)
     sweep_kernel(const unsigned long long* keys_in, unsigned long long* keys_out,
                  const unsigned int* pay_in, unsigned int* pay_out, long long n, int shift,
                  const unsigned int* run_start, unsigned int* status, unsigned int* next_tile,
@@ -140,10 +147,11 @@ __global__ void __launch_bounds__(kThreads, 3)
   unsigned int* spay = reinterpret_cast<unsigned int*>(smem_raw + kTile * 8);
   // cnt[w][d]: first the number of keys with digit d seen so far by warp w, afterwards the
   // position inside the tile's digit-d run of that warp's first key with digit d
-  unsigned int (*cnt)[kDigits] =
-      reinterpret_cast<unsigned int (*)[kDigits]>(smem_raw + kTile * 12);
+  // (16 bits are enough: a warp holds 512 keys, a tile 4096)
+  unsigned short (*cnt)[kDigits] =
+      reinterpret_cast<unsigned short (*)[kDigits]>(smem_raw + kTile * 12);
   unsigned int* tile_start = reinterpret_cast<unsigned int*>(smem_raw + kTile * 12 +
-                                                             kWarps * kDigits * 4);
+                                                             kWarps * kDigits * 2);
   unsigned int* goff = tile_start + kDigits;  // output index of sorted position q: goff[d] + q
   __shared__ unsigned int s_tile;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -171,7 +179,7 @@ __global__ void __launch_bounds__(kThreads, 3)
     unsigned int seen = 0;
     if (valid) seen = cnt[warp][d];
     __syncwarp();
-    if (valid && before == 0) cnt[warp][d] = seen + __popc(same);
+    if (valid && before == 0) cnt[warp][d] = (unsigned short)(seen + __popc(same));
     __syncwarp();
     rank[j] = (unsigned short)(seen + before);
   }
@@ -181,7 +189,7 @@ __global__ void __launch_bounds__(kThreads, 3)
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) {
     const unsigned int c = cnt[w][threadIdx.x];
-    cnt[w][threadIdx.x] = run;
+    cnt[w][threadIdx.x] = (unsigned short)run;
     run += c;
   }
   tile_start[threadIdx.x] = run;
@@ -240,7 +248,7 @@ __global__ void __launch_bounds__(kThreads, 3)
       const unsigned int d = digit_of(k[j], shift);
       const unsigned int q = tile_start[d] + cnt[warp][d] + rank[j];
       skeys[q] = k[j];
-      if (pay_in) spay[q] = pay_in[i];
+      if (pay_out) spay[q] = pay_in ? pay_in[i] : (unsigned int)i;
     }
   }
   __syncthreads();
@@ -251,15 +259,9 @@ __global__ void __launch_bounds__(kThreads, 3)
       const unsigned long long key = skeys[q];
       const unsigned int p = goff[digit_of(key, shift)] + (unsigned int)q;
       keys_out[p] = key;
-      if (pay_in) pay_out[p] = spay[q];
+      if (pay_out) pay_out[p] = spay[q];
     }
   }
-}
-
-__global__ void iota_kernel(unsigned int* p, long long n) {
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x)
-    p[i] = (unsigned int)i;
 }
 
 // ---- ordered match -------------------------------------------------------------------------
@@ -373,10 +375,6 @@ int psdev_sort_keys(uint64_t* keys, uint32_t* perm, int64_t n, int key_bits, voi
     }
   }
   cudaMemsetAsync(head, 0, clear, s);
-  if (perm) {
-    iota_kernel<<<296, 256, 0, s>>>(perm, n);
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-  }
   unsigned long long* in = reinterpret_cast<unsigned long long*>(keys);
   unsigned long long* out = alt;
   unsigned int* pin = perm;
@@ -386,8 +384,10 @@ int psdev_sort_keys(uint64_t* keys, uint32_t* perm, int64_t n, int key_bits, voi
   digit_scan_kernel<<<passes, kDigits, 0, s>>>(head->hist);
   g_launches.fetch_add(2, std::memory_order_relaxed);
   for (int pass = 0; pass < passes; ++pass) {
+    // the first pass makes the payload: the index of every key in the input
     sweep_kernel<<<ntiles, kThreads, kSweepSmem, s>>>(
-        in, out, pin, pout, n, pass * kRadixBits, head->hist + pass * kDigits,
+        in, out, pass == 0 ? nullptr : pin, pout, n, pass * kRadixBits,
+        head->hist + pass * kDigits,
         status + status_pass * pass, &head->next_tile[pass], &head->error);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     unsigned long long* t = in; in = out; out = t;
