@@ -100,7 +100,7 @@ def measure_ps(ctx, workload, steps, warmup, batch=0, ctas=0, sample_clocks=Fals
     if sampler:
         sampler.start()
     l0 = lib.psdev_launch_count()
-    slices0 = dopt.launched_slices
+    slices0, launches0 = dopt.launched_slices, dopt.launches
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     losses = []
@@ -120,6 +120,8 @@ def measure_ps(ctx, workload, steps, warmup, batch=0, ctas=0, sample_clocks=Fals
         "config": {"model": workload, "global_batch": per_step * world,
                    "parameters": nparam, "parallelism": f"dp{world}, server-side optimizer",
                    "slices_per_step": (dopt.launched_slices - slices0) // max(1, steps),
+                   "exchange_launches_per_step": (dopt.launches - launches0) // max(1, steps),
+                   "batch_bytes": dopt.batch_bytes,
                    "pull_fused_with_first_gemm": bool(fused),
                    "timing": "end to end: pinned-host inputs copied in and loss read back "
                              "every step"},

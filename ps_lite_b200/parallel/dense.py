@@ -301,6 +301,7 @@ class DenseTable:
         self.step = int(ck["step"])
 
     MAX_SEGS = 1024
+    SEG_SLOTS = 16
 
     def run_multi(self, op: int, segments, *, sync: bool = True, stream=None, timeout_s=None) -> None:
         """Run ``op`` on several slices ``(begin, end, priority)`` in one launch and one
@@ -311,24 +312,34 @@ class DenseTable:
         if len(segments) > self.MAX_SEGS:
             raise ValueError("too many slices for one launch")
         s = stream or torch.cuda.current_stream(self.heap.device)
-        if not hasattr(self, "_seg_host"):
-            self._seg_host = torch.empty(self.MAX_SEGS * 3, dtype=torch.int64).pin_memory()
-            self._seg_dev = torch.empty(self.MAX_SEGS * 3, dtype=torch.int64, device=self.heap.device)
+        if not hasattr(self, "_seg_ring"):
+            # a ring of staging slots (pinned host list, device copy, device schedule): the host
+            # waits only when it comes back to a slot whose copy has not run yet
             nb = self.heap.lib.psdev_sched_bytes(self.MAX_SEGS)
-            self._sched_dev = torch.empty(nb, dtype=torch.uint8, device=self.heap.device)
-            self._seg_free = torch.cuda.Event()
-            self._seg_free.record(s)
-        self._seg_free.synchronize()   # the previous launch has read the staging buffer
+            dev = self.heap.device
+            self._seg_ring = [
+                (torch.empty(self.MAX_SEGS * 3, dtype=torch.int64).pin_memory(),
+                 torch.empty(self.MAX_SEGS * 3, dtype=torch.int64, device=dev),
+                 torch.empty(nb, dtype=torch.uint8, device=dev), torch.cuda.Event())
+                for _ in range(self.SEG_SLOTS)]
+            self._seg_next = 0
+            self._seg_used = [False] * self.SEG_SLOTS
+        slot = self._seg_next
+        self._seg_next = (slot + 1) % self.SEG_SLOTS
+        seg_host, seg_dev, sched_dev, seg_free = self._seg_ring[slot]
+        if self._seg_used[slot]:
+            seg_free.synchronize()   # that slot's previous launch has read the staging buffer
+        self._seg_used[slot] = True
         flat = [int(v) for seg in segments for v in seg]
-        self._seg_host[: len(flat)] = torch.tensor(flat, dtype=torch.int64)
+        seg_host[: len(flat)] = torch.tensor(flat, dtype=torch.int64)
         with torch.cuda.stream(s):
-            self._seg_dev[: len(flat)].copy_(self._seg_host[: len(flat)], non_blocking=True)
-        self._seg_free.record(s)
+            seg_dev[: len(flat)].copy_(seg_host[: len(flat)], non_blocking=True)
+        seg_free.record(s)
         o = self._opt_struct()
         tmo = int((timeout_s if timeout_s is not None else self._default_timeout) * 1e9)
         rc = self.heap.lib.psdev_dense_op_multi(
-            C.byref(self._world), C.byref(self._table), op, self._seg_dev.data_ptr(),
-            len(segments), self._sched_dev.data_ptr(), C.byref(o), self.channel, self.num_ctas,
+            C.byref(self._world), C.byref(self._table), op, seg_dev.data_ptr(),
+            len(segments), sched_dev.data_ptr(), C.byref(o), self.channel, self.num_ctas,
             tmo, (1 if sync else 0) | (2 if self.nvls else 0), s.cuda_stream)
         _lib.check(rc, "psdev_dense_op_multi")
 

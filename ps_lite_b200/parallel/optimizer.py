@@ -12,7 +12,11 @@ and that its users build on ``KVWorker::Push/Pull`` with per-message priorities
   its slices to a priority scheduler; slices are at most ``slice_bytes`` long (4 MB by
   default) and their priority is the reverse of the layer order, so the weights the next
   forward pass needs first are exchanged first among the slices that are pending;
-* every slice is one fused push+pull kernel on a side stream, overlapping the rest of backward.
+* slices are exchanged by fused push+pull kernels on a side stream, overlapping the rest of
+  backward: as soon as ``batch_bytes`` (4 MiB by default, ``PSB200_BATCH_BYTES``) of gradients
+  are pending, everything pending goes out in ONE launch whose CTAs take the slices in priority
+  order, so small tensors share a rendezvous; with ``batch_bytes=0`` every hook launches up to
+  ``slices_per_event`` single-slice kernels and the rest waits in the host queue.
 
 Every rank makes the same scheduling decisions because they depend only on the order in which
 gradient hooks fire, which is the same on every rank for the same model.
@@ -37,6 +41,7 @@ class P3Scheduler:
         self.slice_elems = max(8, int(slice_elems) & ~7)
         self._heap: List[Tuple[int, int, int, int]] = []
         self._seq = 0
+        self.pending_elems = 0
 
     def add(self, begin: int, end: int, priority: int) -> int:
         """Cut [begin, end) into slices and queue them; returns the number of slices."""
@@ -45,6 +50,7 @@ class P3Scheduler:
         while b < end:
             e = min(b + self.slice_elems, end)
             heapq.heappush(self._heap, (-priority, self._seq, b, e))
+            self.pending_elems += e - b
             self._seq += 1
             n += 1
             b = e
@@ -54,6 +60,7 @@ class P3Scheduler:
         if not self._heap:
             return None
         negp, _, b, e = heapq.heappop(self._heap)
+        self.pending_elems -= e - b
         return b, e, -negp
 
     def __len__(self) -> int:
@@ -67,7 +74,8 @@ class DistributedOptimizer:
                  optimizer: ServerOptimizer, grad_dtype=torch.bfloat16, blk: int = 4096,
                  slice_bytes: int = 4 << 20, slices_per_event: int = 2, channel: int = 0,
                  num_ctas: int = 32, overlap: bool = True, publish_first: int = 0,
-                 nvls: Optional[bool] = None, publish_params=()):
+                 nvls: Optional[bool] = None, publish_params=(),
+                 batch_bytes: Optional[int] = None):
         self.params = [p for p in params if p.requires_grad]
         if not self.params:
             raise ValueError("no trainable parameters")
@@ -85,6 +93,14 @@ class DistributedOptimizer:
         gsz = torch.empty((), dtype=grad_dtype).element_size()
         self.sched = P3Scheduler(slice_bytes // gsz)
         self.slices_per_event = slices_per_event
+        # gradients wait in the queue until `batch_bytes` are pending, then everything pending
+        # goes out in one launch (small tensors share a rendezvous); 0 = launch from every hook
+        if batch_bytes is None:
+            import os
+            batch_bytes = int(os.environ.get("PSB200_BATCH_BYTES", str(4 << 20)))
+        self.batch_bytes = int(batch_bytes)
+        self._gsz = gsz
+        self.launches = 0
         self.overlap = overlap
         self.comm = torch.cuda.Stream(heap.device) if overlap else None
         # the first `publish_first` parameters are pushed with publish instead of push+pull:
@@ -125,7 +141,10 @@ class DistributedOptimizer:
             if self._publish[index]:
                 pri = -1 - index  # published slices carry no pull: least urgent
             self.sched.add(o, o + ((n + 7) & ~7), pri)
-            self._launch(self.slices_per_event)
+            if self.batch_bytes <= 0:
+                self._launch(self.slices_per_event)
+            elif self.sched.pending_elems * self._gsz >= self.batch_bytes:
+                self._drain()
         return hook
 
     def _launch(self, count: int) -> None:
@@ -145,10 +164,11 @@ class DistributedOptimizer:
             else:
                 self.table.push_pull(b, e, stream=stream, opt_step=False)
             self.launched_slices += 1
+            self.launches += 1
 
     def _drain(self) -> None:
-        """Everything still queued goes out in one launch per kind of operation; the kernel
-        itself takes the slices in priority order (device-side schedule)."""
+        """Everything queued goes out in one launch per kind of operation; the kernel itself
+        takes the slices in priority order (device-side schedule)."""
         if not len(self.sched):
             return
         cur = torch.cuda.current_stream(self.heap.device)
@@ -162,10 +182,17 @@ class DistributedOptimizer:
                 break
             (publish if item[2] < 0 else both).append(item)
         cap = self.table.MAX_SEGS
-        for i in range(0, len(both), cap):
-            self.table.run_multi(_lib.OP_PUSHPULL, both[i:i + cap], stream=stream)
+        if len(both) == 1:
+            b, e, _ = both[0]
+            self.table.push_pull(b, e, stream=stream, opt_step=False)
+            self.launches += 1
+        else:
+            for i in range(0, len(both), cap):
+                self.table.run_multi(_lib.OP_PUSHPULL, both[i:i + cap], stream=stream)
+                self.launches += 1
         for i in range(0, len(publish), cap):
             self.table.run_multi(_lib.OP_PUSH | _lib.OP_PUBLISH, publish[i:i + cap], stream=stream)
+            self.launches += 1
         self.launched_slices += len(both) + len(publish)
 
     def step(self) -> None:
