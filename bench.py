@@ -136,8 +136,13 @@ def run_pushpull(args):
         torch.cuda.synchronize()
         ctx.host_barrier()
         ms2 = ctx.max_over_ranks(s0.elapsed_time(s1)) / k2
+        # what the same bytes take as plain copies on this box, all ranks at once, no kernel
+        from benchmarks.host_copy_ceiling import both_directions_ms
+        ceiling_ms = both_directions_ms(ctx, hin, hout)
         e2e = {"value": round(world * 2.0 * nbytes / (ms2 * 1e-3) / 1e9, 3), "unit": "GB/s",
                "ms_per_step": round(ms2, 4), "steps": k2,
+               "plain_copies_ms": round(ceiling_ms, 4),
+               "ms_over_plain_copies": round(ms2 / ceiling_ms, 3),
                "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes,
                "slice_mib": args.slice_mb,
                "api": "KVStore.push_pull(pinned host tensor, out=pinned host tensor); wait(ts) "

@@ -21,6 +21,39 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from ps_lite_b200 import kvstore  # noqa: E402
 
 
+def both_directions_ms(ctx, hin, hout, reps=5):
+    """Milliseconds (maximum over ranks) that one whole-buffer copy of ``hin`` to the device
+    and, at the same time, one of the same size from the device into ``hout`` take when every
+    rank copies at once: the floor of a step that moves these bytes, whatever runs between."""
+    dev = ctx.device
+    din = torch.empty(hin.numel(), dtype=hin.dtype, device=dev)
+    dout = torch.zeros(hout.numel(), dtype=hout.dtype, device=dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def once():
+        with torch.cuda.stream(s_in):
+            din.copy_(hin, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            hout.copy_(dout, non_blocking=True)
+
+    for _ in range(2):
+        once()
+    torch.cuda.synchronize()
+    ctx.host_barrier()
+    cur = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    s_in.wait_stream(cur)
+    s_out.wait_stream(cur)
+    for _ in range(reps):
+        once()
+    cur.wait_stream(s_in)
+    cur.wait_stream(s_out)
+    e1.record()
+    torch.cuda.synchronize()
+    return ctx.max_over_ranks(e0.elapsed_time(e1)) / reps
+
+
 def main():
     nbytes = int(os.environ.get("COPY_MB", "256")) << 20
     ctx = kvstore.init(heap_bytes=64 << 20)
