@@ -107,6 +107,9 @@ def lib() -> C.CDLL:
             L.ps_capi_bworker_delete.argtypes = [vp]
             L.ps_capi_bworker_request.argtypes = [vp, i, i, u64p, sz, vp, sz, vp, sz, i, i]
             L.ps_capi_bworker_wait.argtypes = [vp, i]
+            f32 = C.c_float
+            L.psnvl_declare_sparse.argtypes = [i, u64, i64, i, i, f32, f32, f32, f32, f32, i]
+            L.ps_capi_bworker_keyed_request.argtypes = [vp, i, i, vp, sz, vp, sz, vp, sz, vp, vp, i]
             _lib = L
         return _lib
 

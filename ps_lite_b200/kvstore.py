@@ -114,6 +114,8 @@ class Context:
 
     def close(self) -> None:
         L = host.lib()
+        for ks in getattr(self, "_keyed", []):
+            ks.close()
         if self.worker:
             L.ps_capi_bworker_delete(self.worker)
             self.worker = None
@@ -288,3 +290,99 @@ class KVStore:
         """After a request on ``key`` failed because a peer did not arrive: make the tensor
         usable again.  Collective: every worker calls it."""
         host._ck(host.lib().psnvl_clear_status(APP_ID, int(key)))
+
+
+class KeyedStore:
+    """One keyed (sparse) table of the device plane, reached through a ``KVWorker``: sorted
+    unique uint64 keys (int64 bit patterns) and fp32 values in DEVICE memory, ``width`` values
+    per key or, with ``var_len``, ``lens[i] <= width`` values per key packed back to back (the
+    reference's ``KVPairs`` with ``lens``, include/ps/kv_app.h:24-45).
+
+    Every worker constructs its stores in the same order with the same arguments, and issues the
+    same kind of request at the same position of its request sequence (each request carries a
+    rendezvous of all workers).  ``kind``: ``"sum"``, ``"sgd"`` (``lr``) or ``"ftrl"``.
+    """
+    _KINDS = {"sum": 0, "sgd": 1, "ftrl": 2}
+    _next_customer = 1
+
+    def __init__(self, ctx: Context, app_id: int, key_space: int, max_keys: int, *,
+                 width: int = 1, kind: str = "sum", lr: float = 0.01, alpha: float = 0.05,
+                 beta: float = 1.0, l1: float = 0.0, l2: float = 0.0, var_len: bool = False):
+        if app_id == APP_ID:
+            raise ValueError(f"app {APP_ID} belongs to the dense store")
+        self.ctx, self.app_id = ctx, int(app_id)
+        self.width, self.var_len, self.max_keys = int(width), bool(var_len), int(max_keys)
+        L = host.lib()
+        host._ck(L.psnvl_declare_sparse(self.app_id, int(key_space), self.max_keys, self.width,
+                                        self._KINDS[kind], lr, alpha, beta, l1, l2,
+                                        int(self.var_len)))
+        cid = KeyedStore._next_customer
+        KeyedStore._next_customer += 1
+        self.worker = L.ps_capi_bworker_new(self.app_id, cid)
+        if not self.worker:
+            raise host.PSError(L.ps_capi_last_error().decode())
+        self._alive: Dict[int, tuple] = {}
+        if not hasattr(ctx, "_keyed"):
+            ctx._keyed = []
+        ctx._keyed.append(self)   # closed with the context, before the plane stops
+
+    def _check(self, t: Optional[torch.Tensor], dtype, what: str) -> None:
+        if t is not None and not (t.is_cuda and t.is_contiguous() and t.dtype == dtype):
+            raise ValueError(f"{what} must be a contiguous {dtype} tensor on the device")
+
+    def request(self, keys: torch.Tensor, vals: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None, lens: Optional[torch.Tensor] = None,
+                lens_out: Optional[torch.Tensor] = None) -> int:
+        """``vals`` given: push; ``out`` given: pull; both: ``ZPushPull``.  Returns a timestamp
+        for :meth:`wait`.  The tensors must stay unchanged until then."""
+        push, pull = vals is not None, out is not None
+        if not (push or pull):
+            raise ValueError("nothing to do: give vals, out or both")
+        self._check(keys, torch.int64, "keys")
+        self._check(vals, torch.float32, "vals")
+        self._check(out, torch.float32, "out")
+        self._check(lens, torch.int32, "lens")
+        self._check(lens_out, torch.int32, "lens_out")
+        n = keys.numel()
+        if n > self.max_keys:
+            raise ValueError("more keys than max_keys")
+        if push and self.var_len and (lens is None or lens.numel() != n):
+            raise ValueError("a push to a table with lengths names one length per key")
+        if not self.var_len and (lens is not None or lens_out is not None):
+            raise ValueError("this table holds fixed-width values")
+        if lens_out is not None and lens_out.numel() != n:
+            raise ValueError("lens_out needs one entry per key")
+        L = host.lib()
+        L.psnvl_set_stream(torch.cuda.current_stream(self.ctx.device).cuda_stream)
+        ts = L.ps_capi_bworker_keyed_request(
+            self.worker, int(push), int(pull), keys.data_ptr(), n,
+            vals.data_ptr() if push else None, vals.numel() * 4 if push else 0,
+            out.data_ptr() if pull else None, out.numel() * 4 if pull else 0,
+            lens.data_ptr() if (push and lens is not None) else None,
+            lens_out.data_ptr() if (pull and not push and lens_out is not None) else None, 0)
+        if ts < 0:
+            raise host.PSError(L.ps_capi_last_error().decode())
+        self._alive[ts] = (keys, vals, out, lens, lens_out)
+        return ts
+
+    def push(self, keys, vals, lens=None) -> int:
+        return self.request(keys, vals=vals, lens=lens)
+
+    def pull(self, keys, out, lens_out=None) -> int:
+        return self.request(keys, out=out, lens_out=lens_out)
+
+    def push_pull(self, keys, vals, out, lens=None) -> int:
+        return self.request(keys, vals=vals, out=out, lens=lens)
+
+    def wait(self, ts: int) -> None:
+        L = host.lib()
+        try:
+            if L.ps_capi_bworker_wait(self.worker, int(ts)) < 0:
+                raise host.PSError(L.ps_capi_last_error().decode())
+        finally:
+            self._alive.pop(ts, None)
+
+    def close(self) -> None:
+        if self.worker:
+            host.lib().ps_capi_bworker_delete(self.worker)
+            self.worker = None

@@ -175,4 +175,38 @@ int ps_capi_bworker_wait(void* worker, int timestamp) {
   });
 }
 
+int psnvl_declare_sparse(int app_id, uint64_t key_space, int64_t max_keys, int width, int kind,
+                         float lr, float alpha, float beta, float l1, float l2, int var_len) {
+  return Guard([&] {
+    Plane::Get()->DeclareSparse(app_id, key_space, max_keys, width, kind, lr, alpha, beta, l1, l2,
+                                var_len != 0);
+    return 0;
+  });
+}
+
+int ps_capi_bworker_keyed_request(void* worker, int push, int pull, const uint64_t* keys_dev,
+                                  size_t nkeys, const void* vals_dev, size_t vals_bytes,
+                                  void* outs_dev, size_t outs_bytes, const int* lens_dev,
+                                  int* lens_out_dev, int cmd) {
+  return Guard([&] {
+    auto* kv = static_cast<KVWorker<char>*>(worker);
+    SArray<Key> k = SArray<Key>::FromDevice(
+        const_cast<Key*>(reinterpret_cast<const Key*>(keys_dev)), nkeys);
+    SArray<char> v = SArray<char>::FromDevice(
+        const_cast<char*>(static_cast<const char*>(vals_dev)), vals_bytes);
+    SArray<int> l;
+    if (lens_dev) l = SArray<int>::FromDevice(const_cast<int*>(lens_dev), nkeys);
+    if (push && !pull) return kv->ZPush(k, v, l, cmd);
+    // output views live until the request has completed
+    auto* o = new SArray<char>(SArray<char>::FromDevice(static_cast<char*>(outs_dev), outs_bytes));
+    if (push) {
+      auto* lp = lens_dev ? new SArray<int>(l) : nullptr;
+      return kv->ZPushPull(k, v, o, lp, cmd, [o, lp]() { delete o; delete lp; });
+    }
+    auto* lo = lens_out_dev ? new SArray<int>(SArray<int>::FromDevice(lens_out_dev, nkeys))
+                            : nullptr;
+    return kv->ZPull(k, o, lo, cmd, [o, lo]() { delete o; delete lo; });
+  });
+}
+
 }  // extern "C"

@@ -64,6 +64,20 @@ int ps_capi_bworker_request(void* worker, int push, int pull, const uint64_t* ke
                             int cmd, int priority);
 int ps_capi_bworker_wait(void* worker, int timestamp);
 
+/* ---- keyed (sparse) tables ---- */
+/* Plane::DeclareSparse: one keyed table for `app_id` (collective).  kind 0 sum, 1 SGD,
+ * 2 FTRL-proximal; var_len != 0: values have per-key lengths of at most `width`. */
+int psnvl_declare_sparse(int app_id, uint64_t key_space, int64_t max_keys, int width, int kind,
+                         float lr, float alpha, float beta, float l1, float l2, int var_len);
+/* One keyed request of a worker created for that app; every array is DEVICE memory and stays
+ * valid until the wait returns.  keys: sorted unique uint64.  Push: vals (fp32) and, on a table
+ * with lengths, lens (int32 per key).  Pull: outs, and on a table with lengths lens_out receives
+ * the stored length of every key.  Returns the timestamp. */
+int ps_capi_bworker_keyed_request(void* worker, int push, int pull, const uint64_t* keys_dev,
+                                  size_t nkeys, const void* vals_dev, size_t vals_bytes,
+                                  void* outs_dev, size_t outs_bytes, const int* lens_dev,
+                                  int* lens_out_dev, int cmd);
+
 #ifdef __cplusplus
 }
 #endif

@@ -113,3 +113,51 @@ def test_cpp_program_through_ps_start(cuda_device):
     env.pop("DMLC_ROLE", None)
     r = subprocess.run([out], capture_output=True, text=True, timeout=120, env=env)
     assert r.returncode == 0 and "DEVICE_PLANE_OK rank 0 of 1" in r.stderr, r.stderr[-3000:]
+
+
+def test_keyed_store_through_kvworker(cuda_device):
+    """Keyed tables from Python through KVWorker requests with device-resident keys: fixed
+    width with the SGD handle, and per-key lengths with the sum handle (a pull returns the
+    lengths that the owner holds)."""
+    r = _run("""
+        import torch
+        from ps_lite_b200 import kvstore
+        ctx = kvstore.init(heap_bytes=256 << 20)
+        dev = ctx.device
+        g = torch.Generator(device=dev); g.manual_seed(1)
+        # fixed width 4, SGD lr 0.5 on values that start at 0
+        ks = kvstore.KeyedStore(ctx, 7, 1 << 20, 5000, width=4, kind="sgd", lr=0.5)
+        keys = torch.unique(torch.randint(0, 1 << 20, (4000,), device=dev, generator=g))
+        vals = torch.randn(keys.numel() * 4, device=dev, generator=g)
+        out = torch.empty_like(vals)
+        ks.wait(ks.push_pull(keys, vals, out))
+        torch.testing.assert_close(out, -0.5 * vals)
+        ks.wait(ks.push(keys, vals))
+        sub = keys[::3].contiguous()
+        out2 = torch.empty(sub.numel() * 4, device=dev)
+        ks.wait(ks.pull(sub, out2))
+        torch.testing.assert_close(out2.view(-1, 4), (-1.0 * vals).view(-1, 4)[::3])
+        # per-key lengths 1..3, sum handle
+        kv = kvstore.KeyedStore(ctx, 8, 1 << 16, 3000, width=3, kind="sum", var_len=True)
+        keys = torch.unique(torch.randint(0, 1 << 16, (2500,), device=dev, generator=g))
+        lens = (keys % 3 + 1).int()
+        total = int(lens.sum())
+        vals = torch.randn(total, device=dev, generator=g)
+        kv.wait(kv.push(keys, vals, lens))
+        ask = torch.unique(torch.cat([keys[::2], torch.tensor([1, 5, 9], device=dev)]))
+        out = torch.zeros(ask.numel() * 3, device=dev)
+        lens_back = torch.full((ask.numel(),), -1, device=dev, dtype=torch.int32)
+        kv.wait(kv.pull(ask, out, lens_back))
+        known = torch.isin(ask, keys)
+        want_lens = torch.where(known, (ask % 3 + 1).int(), torch.zeros_like(lens_back))
+        assert torch.equal(lens_back, want_lens), (lens_back[:10], want_lens[:10])
+        offs = torch.cumsum(lens.long(), 0) - lens.long()
+        pos = torch.searchsorted(keys, ask[known])
+        got_offs = (torch.cumsum(want_lens.long(), 0) - want_lens.long())[known]
+        for j in range(3):
+            m = lens[pos] > j
+            torch.testing.assert_close(out[(got_offs + j)[m]], vals[(offs[pos] + j)[m]])
+        kvstore.finalize()
+        print("KEYED_OK")
+    """)
+    assert r.returncode == 0 and "KEYED_OK" in r.stdout, (r.stdout + r.stderr)[-4000:]
