@@ -177,6 +177,11 @@ def finalize() -> None:
         _ctx = None
 
 
+# Requests whose tensors are kept alive without the caller having waited for them; beyond this
+# the oldest one is waited for on the caller's behalf.
+MAX_UNWAITED = 4096
+
+
 class KVStore:
     """Dense key-value store over the device data plane."""
 
@@ -256,6 +261,8 @@ class KVStore:
         if ts < 0:
             raise host.PSError(L.ps_capi_last_error().decode())
         self._alive[ts] = (value, out, t)   # zero-copy: kept until the request completed
+        if len(self._alive) > MAX_UNWAITED:
+            self.wait(min(self._alive))   # a caller that never waits: retire the oldest
         return ts
 
     def push(self, key: int, value: Optional[torch.Tensor] = None, publish: bool = False) -> int:
@@ -363,6 +370,8 @@ class KeyedStore:
         if ts < 0:
             raise host.PSError(L.ps_capi_last_error().decode())
         self._alive[ts] = (keys, vals, out, lens, lens_out)
+        if len(self._alive) > MAX_UNWAITED:
+            self.wait(min(self._alive))
         return ts
 
     def push(self, keys, vals, lens=None) -> int:
