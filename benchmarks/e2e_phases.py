@@ -73,6 +73,14 @@ def main():
                          ("pull", lambda: kv.wait(kv.pull(0, hout))),
                          ("push_pull", lambda: kv.wait(kv.push_pull(0, hin, hout)))):
             emit(case=name, slice_mib=mb, ms=round(timed(fn), 3))
+        # host time of the call that queues a whole request (copies, kernels, events)
+        import time
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        ts = kv.push_pull(0, hin, hout)
+        t1 = time.perf_counter()
+        kv.wait(ts)
+        emit(case="push_pull: host time of the call", slice_mib=mb, ms=round((t1 - t0) * 1e3, 3))
     t.check()
     kvstore.finalize()
 

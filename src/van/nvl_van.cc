@@ -437,6 +437,7 @@ thread_local bool tls_has_stream = false;
 // ================================================================================================
 struct Plane::Impl {
   PlaneOptions opts;
+  bool copy_out_lag = true;  // PSB200_COPY_OUT_LAG=0: copy out as soon as the kernel is done
   bool started = false;
   bool sim = false;
   std::string backend_name;
@@ -619,6 +620,7 @@ void Plane::Start(const PlaneOptions& options) {
 
   const int R = m.rank, W = m.world;
   auto gather = [this](const std::string& s) { return AllGather(s); };
+  if (const char* env = getenv("PSB200_COPY_OUT_LAG")) m.copy_out_lag = atoi(env) != 0;
   std::string backend = m.sim ? "sim" : options.backend;
   if (backend == "auto") {
     const char* env = getenv("PSB200_HEAP");
@@ -1287,6 +1289,21 @@ void Plane::Submit(const DeviceRequest& req) {
     const int64_t small_g = std::max<int64_t>(
         8, std::min<int64_t>(step_g, std::max<int64_t>(step_g / 16, (256 << 10) / gsz)) &
                ~int64_t(7));
+    // A slice's copy out needs its copy in and its kernel, and the next slice's copy in ends
+    // at about the moment the previous copy out does: issued as soon as possible, every copy
+    // out would start one kernel and one event hand-over late, with the link idle in that
+    // direction meanwhile.  So the copy out of slice k is held until the copy in of slice k+1
+    // has finished as well: from then on its own dependencies are met long before its turn.
+    const bool lagged = m.copy_out_lag && host_in && host_out && req.push && req.pull && outs;
+    struct Held {
+      char* dst; const char* src; size_t bytes; void* after_kernel;
+    } held{nullptr, nullptr, 0, nullptr};
+    bool holding = false;
+    auto copy_out = [&](const Held& h, void* also_after) {
+      m.rt.stream_wait_event(m.s_d2h, h.after_kernel);
+      if (also_after) m.rt.stream_wait_event(m.s_d2h, also_after);
+      CHECK_EQ(m.rt.memcpy_async(h.dst, h.src, h.bytes, m.s_d2h), 0);
+    };
     size_t elem_off = 0;  // position in the request's value list
     for (const Run& r : runs) {
       const std::vector<int64_t> cuts = SliceEnds(r.begin, r.end, small_g, step_g);
@@ -1305,6 +1322,10 @@ void Plane::Submit(const DeviceRequest& req) {
             m.rt.event_record(ev, m.s_h2d);
             m.rt.stream_wait_event(m.s_compute, ev);
             pend.events_to_recycle.push_back(ev);
+            if (holding) {
+              copy_out(held, ev);
+              holding = false;
+            }
           }
         }
         const int rc = m.rt.dense_op(&m.ws, &t, op, b, pad8(e), &opt, d->channel, d->num_ctas,
@@ -1314,9 +1335,14 @@ void Plane::Submit(const DeviceRequest& req) {
           if (host_out) {
             void* ev = m.NewEvent();
             m.rt.event_record(ev, m.s_compute);
-            m.rt.stream_wait_event(m.s_d2h, ev);
             pend.events_to_recycle.push_back(ev);
-            CHECK_EQ(m.rt.memcpy_async(outs + at * osz, weight + b * osz, cnt * osz, m.s_d2h), 0);
+            const Held h{outs + at * osz, weight + b * osz, cnt * osz, ev};
+            if (lagged) {
+              held = h;
+              holding = true;
+            } else {
+              copy_out(h, nullptr);
+            }
           } else if (outs + at * osz != weight + b * osz) {
             CHECK_EQ(
                 m.rt.memcpy_async(outs + at * osz, weight + b * osz, cnt * osz, m.s_compute), 0);
@@ -1326,6 +1352,7 @@ void Plane::Submit(const DeviceRequest& req) {
       }
       elem_off += static_cast<size_t>(r.end - r.begin);
     }
+    if (holding) copy_out(held, nullptr);
     // the request is complete when the last kernel and the last copy out are
     void* tail = m.NewEvent();
     m.rt.event_record(tail, m.s_d2h);
