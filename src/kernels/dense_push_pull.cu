@@ -219,7 +219,9 @@ static int dense_op_impl(const psdev_world_t* w, const psdev_table_t* t, int op,
   a.s2 = t->state2;
   if (opt) a.opt = *opt;
   a.channel = channel;
-  a.sync = sync & 1;
+  // one rank has nobody to meet: no flag round and none of the system-scope fences that go
+  // with it (they are slow while copy engines are busy, which is when a staged request runs)
+  a.sync = (sync & 1) && W > 1;
   a.mc_base = (sync & 2) ? w->mc_base : nullptr;  // bit 1: use the NVSwitch multicast alias
   if (op == (PSDEV_OP_PUSH | PSDEV_OP_PUBLISH)) {
     // push, and store the new values of the owned blocks into this rank's own weight

@@ -128,16 +128,20 @@ def test_entry_wait_runs_out_and_reports(cuda_device):
     assert torch.all(t1.master[:2048] == 5.0)
 
 
-def test_world1_sync_flags_advance_epoch(cuda_device):
+def test_world1_has_nobody_to_meet(cuda_device):
+    """One rank: a synchronising request runs no flag round (the channel's epoch stays where it
+    is); the device barrier, which is its own kernel, still counts its rounds."""
     from ps_lite_b200.parallel import DenseTable, ServerOptimizer, SymmetricHeap
     heap = SymmetricHeap(1 << 22, 0, 1, device=cuda_device)
     t = DenseTable(heap, 100_000, optimizer=ServerOptimizer("sum"), channel=1)
     t.grad.fill_(1.0)
     for _ in range(5):
         t.push_pull(sync=True)
-    heap.barrier()
+    heap.barrier(channel=2)
+    heap.barrier(channel=2)
     torch.cuda.synchronize()
-    assert heap.channel_status(1) == (0, 5)
+    assert heap.channel_status(1) == (0, 0)
+    assert heap.channel_status(2) == (0, 2)
     assert torch.all(t.weight[:100_000] == 5.0)
     heap.close()
 
