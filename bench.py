@@ -150,13 +150,8 @@ def run_pushpull(args):
     # the sampler ran through both timed regions (device-timed and end-to-end)
     clocks = sampler.stop() if reporter else None
 
-    extras = {}
-    if not args.no_extras:
-        from benchmarks import extras as extras_mod
-        extras = extras_mod.run(ctx, kv, args, time.time() - T_START)
-
-    if reporter:
-        out = {
+    def headline():
+        return {
             "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 5),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -175,8 +170,36 @@ def run_pushpull(args):
                        "l2": "inputs larger than L2 (gradient+weight+master per step > 126 MB)"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
         }
-        out.update(extras)
-        print(json.dumps(out), flush=True)
+
+    def record(extras):
+        return dict(headline(), **extras)
+
+    extras = {}
+    if not args.no_extras:
+        from benchmarks import extras as extras_mod
+        # the extra records must never cost the headline: if they are still running long after
+        # their budget (a rank that left one of them early leaves the others waiting for it),
+        # the headline is printed without them and the process ends
+        import threading
+
+        def give_up():
+            if reporter:
+                print(json.dumps(record({"extras": "abandoned: still running "
+                                         f"{time.time() - T_START:.0f} s after start"})),
+                      flush=True)
+            from ps_lite_b200.launch import bootstrap
+            bootstrap.abandon()
+            os._exit(0)
+
+        watchdog = threading.Timer(max(60.0, args.extras_budget_s + 180.0 -
+                                       (time.time() - T_START)), give_up)
+        watchdog.daemon = True
+        watchdog.start()
+        extras = extras_mod.run(ctx, kv, args, time.time() - T_START)
+        watchdog.cancel()
+
+    if reporter:
+        print(json.dumps(record(extras)), flush=True)
     kvstore.finalize()
 
 

@@ -150,6 +150,8 @@ def _install_exit_hook() -> None:
             sys.stdout.flush()
         finally:
             if _ctx is not None and tp is not KeyboardInterrupt:
+                from .launch import bootstrap
+                bootstrap.abandon()
                 os._exit(1)
             prev(tp, val, tb)
 

@@ -52,6 +52,24 @@ def _cleanup() -> None:
             p.kill()
 
 
+def abandon() -> None:
+    """For a process that is about to leave without the orderly shutdown (``os._exit``): stops
+    the scheduler it started, which would otherwise wait for nodes that will never report."""
+    f = _state.get("file")
+    if f and os.path.exists(f):
+        try:
+            os.remove(f)
+        except OSError:
+            pass
+    p = _state.get("scheduler")
+    if p is not None and p.poll() is None:
+        p.kill()
+        try:
+            p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            pass
+
+
 def ensure_env(timeout_s: float = 120.0) -> str:
     """Set the ``DMLC_*`` variables if the launcher did not; returns "dmlc", "torchrun" or
     "single"."""
