@@ -51,7 +51,7 @@ def _sweep(ctx, rounds=30):
         out.append({"bytes": n * 4, "us_per_round": round(ms * 1e3, 2),
                     "goodput_GBps_per_gpu": round(2 * n * 4 / (ms * 1e-3) / 1e9, 2),
                     "path": "low-latency" if t.ll_cap >= n and world > 1 else
-                            ("multicast" if t.nvls and n * 4 <= t.nvls_max_bytes else "peer")})
+                            ("multicast" if t.nvls and t._multicast_pays(n * 4) else "peer")})
         t.free()
         nbytes *= 4
     return out

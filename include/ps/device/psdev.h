@@ -219,6 +219,9 @@ void psdev_count_launch(void);
 int psdev_handle_states(int kind);
 
 /* Flag-only rendezvous of all ranks on a channel (device barrier). */
+/* 1 when a dense request of `bytes` gradient bytes among `world` ranks is faster on the NVSwitch
+ * multicast path than on plain peer accesses (measured limits; PSB200_NVLS_MAX_BYTES overrides). */
+int psdev_multicast_pays(int world, uint64_t bytes);
 int psdev_device_barrier(const psdev_world_t* w, int channel, uint64_t timeout_ns,
                          void* stream);
 

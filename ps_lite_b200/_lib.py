@@ -103,6 +103,7 @@ def _declare(lib: C.CDLL) -> None:
         "psdev_ll_bytes": (sz, [i32, i64]),
         "psdev_handle_states": (i32, [i32]),
         "psdev_device_barrier": (i32, [C.POINTER(World), i32, u64, vp]),
+        "psdev_multicast_pays": (i32, [i32, u64]),
         "psdev_link_copy": (i32, [vp, vp, sz, i32, vp]),
         "psdev_gemm_bf16": (i32, [vp, vp, vp, i64, i64, i64, i32, u64, vp]),
         "psdev_pull_gemm_bf16": (i32, [C.POINTER(World), C.POINTER(Table), i64, vp, vp, i64, i64,

@@ -124,7 +124,9 @@ class DenseTable:
             env = os.environ.get("PSB200_NVLS")
             nvls = (W >= 4) if env is None else (env == "1")
         self.nvls = bool(nvls and heap.mc_base and W > 1)
-        self.nvls_max_bytes = 512 << 20
+        # largest request that takes the multicast path; None = the library's measured rule
+        # (psdev_multicast_pays: 4 MiB with up to 4 ranks, 512 MiB with more)
+        self.nvls_max_bytes: Optional[int] = None
         gsz = torch.empty((), dtype=grad_dtype).element_size()
         osz = torch.empty((), dtype=out_dtype).element_size()
         self.grad_off = heap.alloc(self.n * gsz)
@@ -229,9 +231,7 @@ class DenseTable:
         tmo = int((timeout_s if timeout_s is not None else self._default_timeout) * 1e9)
         if _nvtx_enabled():
             torch.cuda.nvtx.range_push(f"{_OP_NAMES.get(op, 'ps.op')}[{begin}:{end}]")
-        # measured on 8 GPUs: the multicast path wins up to 256 MiB per request (855 vs 741
-        # GB/s per GPU) and loses at 1 GiB (648 vs 763), so very large requests use peer accesses
-        nvls = self.nvls and (int(end) - int(begin)) * self.grad.element_size() <= self.nvls_max_bytes
+        nvls = self.nvls and self._multicast_pays((int(end) - int(begin)) * self.grad.element_size())
         rc = self.heap.lib.psdev_dense_op(C.byref(self._world), C.byref(self._table), op,
                                           int(begin), int(end), C.byref(o), self.channel,
                                           self.num_ctas, tmo,
@@ -240,6 +240,11 @@ class DenseTable:
         if _nvtx_enabled():
             torch.cuda.nvtx.range_pop()
         _lib.check(rc, "psdev_dense_op")
+
+    def _multicast_pays(self, nbytes: int) -> bool:
+        if self.nvls_max_bytes is not None:
+            return nbytes <= self.nvls_max_bytes
+        return bool(self.heap.lib.psdev_multicast_pays(self.heap.world, int(nbytes)))
 
     def _opt_struct(self) -> _lib.Opt:
         """The handle's parameters for the current step (rebuilt only when something changed:
@@ -336,11 +341,13 @@ class DenseTable:
             seg_dev[: len(flat)].copy_(seg_host[: len(flat)], non_blocking=True)
         seg_free.record(s)
         o = self._opt_struct()
+        gsz = self.grad.element_size()
+        nvls = self.nvls and self._multicast_pays(sum(int(e) - int(b) for b, e, _ in segments) * gsz)
         tmo = int((timeout_s if timeout_s is not None else self._default_timeout) * 1e9)
         rc = self.heap.lib.psdev_dense_op_multi(
             C.byref(self._world), C.byref(self._table), op, seg_dev.data_ptr(),
             len(segments), sched_dev.data_ptr(), C.byref(o), self.channel, self.num_ctas,
-            tmo, (1 if sync else 0) | (2 if self.nvls else 0), s.cuda_stream)
+            tmo, (1 if sync else 0) | (2 if nvls else 0), s.cuda_stream)
         _lib.check(rc, "psdev_dense_op_multi")
 
     def check(self) -> None:

@@ -173,6 +173,22 @@ static bool ll_enabled() {
   return on;
 }
 
+// Whether a request of `bytes` gradient bytes should take the NVSwitch multicast path when the
+// arena has a multicast alias.  Measured: with 4 ranks multicast wins up to 4 MiB (one flag-free
+// reduce-load and one store per vector instead of three of each) and loses from 16 MiB up, where
+// the peer path keeps both directions of every link busy (883 against 860 GB/s per GPU at 256
+// MiB); with 8 ranks it wins up to 256 MiB (855 against 741) and loses at 1 GiB.
+// PSB200_NVLS_MAX_BYTES overrides the limit.
+extern "C" int psdev_multicast_pays(int world, uint64_t bytes) {
+  static const long long env = [] {
+    const char* e = getenv("PSB200_NVLS_MAX_BYTES");
+    return e ? atoll(e) : -1ll;
+  }();
+  if (world < 2) return 0;
+  const uint64_t cap = env >= 0 ? (uint64_t)env : (world > 4 ? 512ull << 20 : 4ull << 20);
+  return bytes <= cap ? 1 : 0;
+}
+
 extern "C" size_t psdev_sched_bytes(int nseg) { return sizeof(SchedEntry) * (size_t)(nseg + 1); }
 
 static int dense_op_impl(const psdev_world_t* w, const psdev_table_t* t, int op, int64_t begin,

@@ -67,6 +67,7 @@ struct Rt {
   int (*key_shard_lookup)(const uint64_t*, int64_t, uint64_t, int, int64_t*, void*) = nullptr;
   int (*lens_to_offsets)(const int32_t*, int64_t, int64_t*, void*) = nullptr;
   int (*device_barrier)(const psdev_world_t*, int, uint64_t, void*) = nullptr;
+  int (*multicast_pays)(int, uint64_t) = nullptr;
   int (*is_device_pointer)(const void*) = nullptr;
   int (*heap_create)(size_t, void**, unsigned char*) = nullptr;
   int (*heap_open)(const unsigned char*, void**) = nullptr;
@@ -138,6 +139,7 @@ void* LoadRt(const std::string& configured, Rt* rt) {
   Bind(lib, "psdev_key_shard_lookup", &rt->key_shard_lookup);
   Bind(lib, "psdev_lens_to_offsets", &rt->lens_to_offsets);
   Bind(lib, "psdev_device_barrier", &rt->device_barrier);
+  Bind(lib, "psdev_multicast_pays", &rt->multicast_pays);
   Bind(lib, "psdev_rt_is_device_pointer", &rt->is_device_pointer);
   Bind(lib, "psdev_heap_create", &rt->heap_create);
   Bind(lib, "psdev_heap_open", &rt->heap_open);
@@ -1222,7 +1224,13 @@ void Plane::Submit(const DeviceRequest& req) {
       opt.bias2 = static_cast<float>(std::sqrt(1.0 - std::pow(static_cast<double>(opt.beta2), s)));
     }
   }
-  const int sync = 1 | (d->nvls ? 2 : 0);
+  // bit 0: rendezvous with the other ranks; bit 1: NVSwitch multicast path, chosen per launch
+  // by the size of what that launch moves
+  auto sync_for = [&](int64_t elems) {
+    const bool mc = d->nvls && m.rt.multicast_pays &&
+                    m.rt.multicast_pays(m.world, static_cast<uint64_t>(elems) * gsz);
+    return 1 | (mc ? 2 : 0);
+  };
   // the kernel works on multiples of 8 values; the padding of the last shard belongs to it
   auto pad8 = [&](int64_t e) { return e >= d->n_user ? t.n : e; };
 
@@ -1259,7 +1267,8 @@ void Plane::Submit(const DeviceRequest& req) {
         CHECK_EQ(m.rt.memcpy_async(grad + r.begin * gsz, vals + eoff * gsz, cnt * gsz, s), 0);
       }
       const int rc = m.rt.dense_op(&m.ws, &t, op, r.begin, pad8(r.end), &opt, d->channel,
-                                   d->num_ctas, m.opts.timeout_ns, sync, s);
+                                   d->num_ctas, m.opts.timeout_ns,
+                                   sync_for(pad8(r.end) - r.begin), s);
       CHECK_EQ(rc, 0) << "psdev_dense_op failed";
       if (req.pull && outs && outs + eoff * osz != weight + r.begin * osz) {
         CHECK_EQ(m.rt.memcpy_async(outs + eoff * osz, weight + r.begin * osz, cnt * osz, s), 0);
@@ -1329,7 +1338,7 @@ void Plane::Submit(const DeviceRequest& req) {
           }
         }
         const int rc = m.rt.dense_op(&m.ws, &t, op, b, pad8(e), &opt, d->channel, d->num_ctas,
-                                     m.opts.timeout_ns, sync, m.s_compute);
+                                     m.opts.timeout_ns, sync_for(pad8(e) - b), m.s_compute);
         CHECK_EQ(rc, 0) << "psdev_dense_op failed";
         if (req.pull && outs) {
           if (host_out) {
