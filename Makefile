@@ -29,9 +29,11 @@ test: $(TESTS)
 	build/make/tests/shm_frames
 	python -m ps_lite_b200.launch.local -n 2 -s 2 build/make/tests/kv_config1
 
+# -MMD -MP: every object records the headers it was compiled against, so that a changed header
+# rebuilds what includes it
 build/make/%.o: %.cc
 	@mkdir -p $(dir $@)
-	$(CXX) $(CXXFLAGS) -c $< -o $@
+	$(CXX) $(CXXFLAGS) -MMD -MP -c $< -o $@
 build/make/%.o: %.cu
 	@mkdir -p $(dir $@)
 	$(NVCC) $(NVFLAGS) -c $< -o $@
@@ -43,7 +45,8 @@ build/make/libpsb200_device.so: $(DEV_OBJ)
 	$(NVCC) -shared -gencode arch=compute_100a,code=sm_100a -o $@ $^ -lcudart
 build/make/tests/%: tests/cpp/%.cc build/make/libps.a
 	@mkdir -p $(dir $@)
-	$(CXX) $(CXXFLAGS) $< build/make/libps.a -o $@
+	$(CXX) $(CXXFLAGS) -MMD -MP -MF $@.d $< build/make/libps.a -o $@
+-include $(CORE_OBJ:.o=.d) $(addsuffix .d,$(TESTS))
 lint:
 	python tests/lint.py
 clean:
