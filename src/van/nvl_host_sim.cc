@@ -156,6 +156,247 @@ int DenseOp(const psdev_world_t* w, const psdev_table_t* t, int op, int64_t begi
   return 0;
 }
 
+// ---- keyed tables ------------------------------------------------------------------------------
+namespace {
+
+// First half of a rendezvous: announce this rank, wait for every rank.  Returns the epoch of the
+// round, or 0 when the channel is out of service or a rank did not arrive.
+unsigned long long Enter(const psdev_world_t* w, int channel, uint64_t timeout_ns) {
+  const int W = w->world, R = w->rank;
+  psdev_ctrl_t* my = CtrlOf(w->peer_base[R]);
+  if (__atomic_load_n(&my->status[channel], __ATOMIC_RELAXED) != 0) return 0;
+  const unsigned long long e = my->epoch[channel] + 1ull;
+  for (int p = 0; p < W; ++p)
+    __atomic_store_n(&CtrlOf(w->peer_base[p])->flag_in[channel][R], e, __ATOMIC_RELEASE);
+  bool ok = true;
+  for (int p = 0; p < W; ++p) {
+    if (!WaitGe(&my->flag_in[channel][p], e, timeout_ns)) {
+      Fail(my, channel, PSDEV_ERR_TIMEOUT_ENTRY, p);
+      ok = false;
+    }
+  }
+  return ok ? e : 0;
+}
+
+// Second half: announce that this rank is done, wait for every rank, advance the epoch.
+void Leave(const psdev_world_t* w, int channel, uint64_t timeout_ns, unsigned long long e) {
+  const int W = w->world, R = w->rank;
+  psdev_ctrl_t* my = CtrlOf(w->peer_base[R]);
+  if (e == 0 || __atomic_load_n(&my->status[channel], __ATOMIC_RELAXED) != 0) return;
+  for (int p = 0; p < W; ++p)
+    __atomic_store_n(&CtrlOf(w->peer_base[p])->flag_out[channel][R], e, __ATOMIC_RELEASE);
+  for (int p = 0; p < W; ++p) {
+    if (!WaitGe(&my->flag_out[channel][p], e, timeout_ns))
+      Fail(my, channel, PSDEV_ERR_TIMEOUT_EXIT, p);
+  }
+  my->epoch[channel] = e;
+}
+
+inline char* Heap(const psdev_world_t* w, int rank) {
+  return static_cast<char*>(w->peer_base[rank]);
+}
+
+bool SparseOk(const psdev_world_t* w, const psdev_sparse_t* t) {
+  return w && t && w->world >= 1 && w->world <= PSDEV_MAX_RANKS && t->range != 0 && t->w &&
+         t->capacity == 0 && t->width >= 1 && t->channel >= 0 &&
+         t->channel < PSDEV_NUM_CHANNELS && (t->kind != 2 || (t->z && t->n)) &&
+         (t->lens_off == 0 || (t->offs_off != 0 && t->klen));
+}
+
+// Length and value offset of request entry i of worker r.
+void ValueSpan(const psdev_world_t* w, const psdev_sparse_t* t, int r, int64_t i, int64_t* off,
+               int* len) {
+  if (t->lens_off == 0) {
+    *off = i * t->width;
+    *len = t->width;
+    return;
+  }
+  int l = reinterpret_cast<const int32_t*>(Heap(w, r) + t->lens_off)[i];
+  if (l < 0) l = 0;
+  if (l > t->width) l = t->width;
+  *off = reinterpret_cast<const int64_t*>(Heap(w, r) + t->offs_off)[i];
+  *len = l;
+}
+
+void AtomicAddF32(float* p, float v) {
+  uint32_t* u = reinterpret_cast<uint32_t*>(p);
+  uint32_t cur = __atomic_load_n(u, __ATOMIC_RELAXED);
+  for (;;) {
+    float f;
+    memcpy(&f, &cur, 4);
+    f += v;
+    uint32_t want;
+    memcpy(&want, &f, 4);
+    if (__atomic_compare_exchange_n(u, &cur, want, false, __ATOMIC_RELAXED, __ATOMIC_RELAXED))
+      return;
+  }
+}
+
+uint64_t TimeoutOf(const psdev_sparse_t* t) {
+  return t->timeout_ns ? t->timeout_ns : 20000000000ull;
+}
+
+}  // namespace
+
+int KeyShardLookup(const uint64_t* keys, int64_t n, uint64_t range, int world, int64_t* pos) {
+  if (world < 1 || world > PSDEV_MAX_RANKS || range == 0 || !pos || (n > 0 && !keys))
+    return PSDEV_ERR_ARG;
+  for (int s = 0; s <= world; ++s) {
+    const uint64_t bound = range * static_cast<uint64_t>(s);
+    int64_t lo = 0, hi = n;
+    while (lo < hi) {
+      const int64_t m = (lo + hi) >> 1;
+      if (keys[m] < bound) lo = m + 1; else hi = m;
+    }
+    pos[s] = lo;
+  }
+  pos[world + 1] = n;
+  return 0;
+}
+
+int LensToOffsets(const int32_t* lens, int64_t n, int64_t* offs) {
+  if (!lens || !offs || n < 0) return PSDEV_ERR_ARG;
+  int64_t run = 0;
+  for (int64_t i = 0; i < n; ++i) {
+    offs[i] = run;
+    run += lens[i] > 0 ? lens[i] : 0;
+  }
+  offs[n] = run;
+  return 0;
+}
+
+int SparseScatter(const psdev_world_t* w, const psdev_sparse_t* t, int64_t n) {
+  if (!SparseOk(w, t) || n < 0 || n > t->max_n) return PSDEV_ERR_ARG;
+  const int W = w->world, R = w->rank;
+  char* mine = Heap(w, R);
+  const uint64_t* keys = reinterpret_cast<const uint64_t*>(mine + t->keys_off);
+  if (t->lens_off)
+    LensToOffsets(reinterpret_cast<const int32_t*>(mine + t->lens_off), n,
+                  reinterpret_cast<int64_t*>(mine + t->offs_off));
+  KeyShardLookup(keys, n, t->range, W, reinterpret_cast<int64_t*>(mine + t->pos_off));
+  const float* grads = reinterpret_cast<const float*>(mine + t->grads_off);
+  for (int64_t i = 0; i < n; ++i) {
+    const uint64_t s = keys[i] / t->range;
+    if (s >= static_cast<uint64_t>(W)) continue;  // outside every range: dropped
+    const int64_t idx = static_cast<int64_t>(keys[i] - s * t->range);
+    if (idx >= t->slots) continue;
+    int64_t off;
+    int len;
+    ValueSpan(w, t, R, i, &off, &len);
+    if (off < 0 || off + len > t->max_vals) continue;
+    float* acc = reinterpret_cast<float*>(Heap(w, static_cast<int>(s)) + t->acc_off);
+    for (int j = 0; j < len; ++j) AtomicAddF32(acc + idx * t->width + j, grads[off + j]);
+  }
+  // the cut points and the additions are visible before this rank announces itself
+  __atomic_thread_fence(__ATOMIC_RELEASE);
+  return 0;
+}
+
+int SparseApply(const psdev_world_t* w, const psdev_sparse_t* t, int sync) {
+  if (!SparseOk(w, t)) return PSDEV_ERR_ARG;
+  const int W = w->world, R = w->rank;
+  if (sync && Enter(w, t->channel, TimeoutOf(t)) == 0) return 0;
+  float* acc = reinterpret_cast<float*>(Heap(w, R) + t->acc_off);
+  for (int r = 0; r < W; ++r) {
+    const int64_t* pos = reinterpret_cast<const int64_t*>(Heap(w, r) + t->pos_off);
+    const int64_t lo = pos[R], hi = pos[R + 1];
+    if (lo < 0 || hi < lo || hi > t->max_n) continue;
+    const uint64_t* keys = reinterpret_cast<const uint64_t*>(Heap(w, r) + t->keys_off);
+    for (int64_t i = lo; i < hi; ++i) {
+      const int64_t idx = static_cast<int64_t>(keys[i] - static_cast<uint64_t>(R) * t->range);
+      if (idx < 0 || idx >= t->slots) continue;
+      if (t->klen && t->lens_off) {
+        int64_t off;
+        int len;
+        ValueSpan(w, t, r, i, &off, &len);
+        if (len > 0) t->klen[idx] = len;
+      }
+      for (int j = 0; j < t->width; ++j) {
+        const int64_t el = idx * t->width + j;
+        const float g = acc[el];
+        if (g == 0.f) continue;  // applied for another worker already, or nothing pushed
+        acc[el] = 0.f;
+        if (t->kind == 0) {
+          t->w[el] += g;
+        } else if (t->kind == 1) {
+          t->w[el] -= t->lr * g;
+        } else {
+          const float wv = t->w[el], nv = t->n[el];
+          const float n2 = nv + g * g;
+          const float sigma = (std::sqrt(n2) - std::sqrt(nv)) / t->alpha;
+          const float z = t->z[el] + g - sigma * wv;
+          t->z[el] = z;
+          t->n[el] = n2;
+          if (std::fabs(z) <= t->l1) {
+            t->w[el] = 0.f;
+          } else {
+            const float sgn = z > 0.f ? 1.f : -1.f;
+            t->w[el] = -(z - sgn * t->l1) / ((t->beta + std::sqrt(n2)) / t->alpha + t->l2);
+          }
+        }
+      }
+    }
+  }
+  return 0;
+}
+
+int SparseRespond(const psdev_world_t* w, const psdev_sparse_t* t, int sync) {
+  if (!SparseOk(w, t)) return PSDEV_ERR_ARG;
+  const int W = w->world, R = w->rank;
+  psdev_ctrl_t* my = CtrlOf(w->peer_base[R]);
+  const bool healthy = !sync || __atomic_load_n(&my->status[t->channel], __ATOMIC_RELAXED) == 0;
+  if (healthy) {
+    for (int rr = 0; rr < W; ++rr) {
+      const int r = (R + rr) % W;
+      const int64_t* pos = reinterpret_cast<const int64_t*>(Heap(w, r) + t->pos_off);
+      const int64_t lo = pos[R], hi = pos[R + 1];
+      if (lo < 0 || hi < lo || hi > t->max_n) continue;
+      const uint64_t* keys = reinterpret_cast<const uint64_t*>(Heap(w, r) + t->keys_off);
+      float* out = reinterpret_cast<float*>(Heap(w, r) + t->out_off);
+      for (int64_t i = lo; i < hi; ++i) {
+        int64_t off;
+        int len;
+        ValueSpan(w, t, r, i, &off, &len);
+        if (off < 0 || off + len > t->max_vals) continue;
+        const int64_t idx = static_cast<int64_t>(keys[i] - static_cast<uint64_t>(R) * t->range);
+        for (int j = 0; j < len; ++j)
+          out[off + j] = (idx >= 0 && idx < t->slots) ? t->w[idx * t->width + j] : 0.f;
+      }
+    }
+  }
+  if (sync) {
+    // the round that the apply call entered: one ahead of the last completed one
+    const unsigned long long e = healthy ? my->epoch[t->channel] + 1ull : 0ull;
+    Leave(w, t->channel, TimeoutOf(t), e);
+  }
+  return 0;
+}
+
+int SparseLens(const psdev_world_t* w, const psdev_sparse_t* t) {
+  if (!SparseOk(w, t) || !t->lens_off || !t->klen) return PSDEV_ERR_ARG;
+  const int W = w->world, R = w->rank;
+  for (int r = 0; r < W; ++r) {
+    const int64_t* pos = reinterpret_cast<const int64_t*>(Heap(w, r) + t->pos_off);
+    const int64_t lo = pos[R], hi = pos[R + 1];
+    if (lo < 0 || hi < lo || hi > t->max_n) continue;
+    const uint64_t* keys = reinterpret_cast<const uint64_t*>(Heap(w, r) + t->keys_off);
+    int32_t* lens = reinterpret_cast<int32_t*>(Heap(w, r) + t->lens_off);
+    for (int64_t i = lo; i < hi; ++i) {
+      const int64_t idx = static_cast<int64_t>(keys[i] - static_cast<uint64_t>(R) * t->range);
+      lens[i] = (idx >= 0 && idx < t->slots) ? t->klen[idx] : 0;
+    }
+  }
+  return 0;
+}
+
+int DeviceBarrier(const psdev_world_t* w, int channel, uint64_t timeout_ns) {
+  if (!w || w->world < 1 || w->world > PSDEV_MAX_RANKS || channel < 0 ||
+      channel >= PSDEV_NUM_CHANNELS)
+    return PSDEV_ERR_ARG;
+  Leave(w, channel, timeout_ns, Enter(w, channel, timeout_ns));
+  return 0;
+}
+
 int ChannelStatus(void* local_base, int channel, int32_t* status, uint64_t* epoch) {
   if (!local_base || channel < 0 || channel >= PSDEV_NUM_CHANNELS) return PSDEV_ERR_ARG;
   psdev_ctrl_t* c = CtrlOf(local_base);

@@ -197,6 +197,36 @@ int SimDenseOp(const psdev_world_t* w, const psdev_table_t* t, int op, int64_t b
   g_sim_launches.fetch_add(1, std::memory_order_relaxed);
   return sim::DenseOp(w, t, op, b, e, o, channel, tmo, sync);
 }
+int SimMemset(void* dst, int value, size_t bytes, void*) {
+  memset(dst, value, bytes);
+  return 0;
+}
+int SimSparseScatter(const psdev_world_t* w, const psdev_sparse_t* t, int64_t n, int, void*) {
+  g_sim_launches.fetch_add(1, std::memory_order_relaxed);
+  return sim::SparseScatter(w, t, n);
+}
+int SimSparseApply(const psdev_world_t* w, const psdev_sparse_t* t, int, int sync, void*) {
+  g_sim_launches.fetch_add(1, std::memory_order_relaxed);
+  return sim::SparseApply(w, t, sync);
+}
+int SimSparseRespond(const psdev_world_t* w, const psdev_sparse_t* t, int, int sync, void*) {
+  g_sim_launches.fetch_add(1, std::memory_order_relaxed);
+  return sim::SparseRespond(w, t, sync);
+}
+int SimSparseLens(const psdev_world_t* w, const psdev_sparse_t* t, int, void*) {
+  g_sim_launches.fetch_add(1, std::memory_order_relaxed);
+  return sim::SparseLens(w, t);
+}
+int SimKeyShardLookup(const uint64_t* keys, int64_t n, uint64_t range, int world, int64_t* pos,
+                      void*) {
+  return sim::KeyShardLookup(keys, n, range, world, pos);
+}
+int SimLensToOffsets(const int32_t* lens, int64_t n, int64_t* offs, void*) {
+  return sim::LensToOffsets(lens, n, offs);
+}
+int SimDeviceBarrier(const psdev_world_t* w, int channel, uint64_t tmo, void*) {
+  return sim::DeviceBarrier(w, channel, tmo);
+}
 uint64_t SimLaunchCount() { return g_sim_launches.load(std::memory_order_relaxed); }
 
 void FillSimRt(Rt* rt) {
@@ -212,6 +242,14 @@ void FillSimRt(Rt* rt) {
   rt->event_sync = SimOk1;
   rt->stream_wait_event = SimEventRecord;
   rt->memcpy_async = SimMemcpy;
+  rt->memset_async = SimMemset;
+  rt->sparse_scatter = SimSparseScatter;
+  rt->sparse_apply = SimSparseApply;
+  rt->sparse_respond = SimSparseRespond;
+  rt->sparse_lens = SimSparseLens;
+  rt->key_shard_lookup = SimKeyShardLookup;
+  rt->lens_to_offsets = SimLensToOffsets;
+  rt->device_barrier = SimDeviceBarrier;
   rt->channel_status_on = SimChannelStatusOn;
   rt->channel_clear = sim::ChannelClear;
   rt->dense_op = SimDenseOp;
@@ -1058,7 +1096,6 @@ const SparseInfo& Plane::DeclareSparse(int app_id, uint64_t key_space, int64_t m
                                        float l2, bool var_len) {
   Impl& m = *impl_;
   CHECK(m.started);
-  CHECK(!m.sim) << "keyed tables need a GPU (the CPU stand-in serves dense tensors only)";
   CHECK(key_space > 0 && max_keys > 0 && width >= 1 && kind >= 0 && kind <= 2);
   CHECK(!FindSparse(app_id)) << "app " << app_id << " already has a keyed table";
   const int W = m.world;
