@@ -128,10 +128,14 @@ class DistributedOptimizer:
     def _make_hook(self, index: int):
         n_params = len(self.params)
 
+        o = self.offsets[index]
+        n = self.params[index].numel()
+        # the parameter's slice of the gradient buffer, in the parameter's shape (made once: the
+        # hook runs on the autograd thread, between the kernels of the backward pass)
+        gview = self.table.grad[o:o + n].view(self.params[index].shape)
+
         def hook(p: torch.nn.Parameter):
-            o = self.offsets[index]
-            n = p.numel()
-            self.table.grad[o:o + n].copy_(p.grad.reshape(-1), non_blocking=True)
+            gview.copy_(p.grad, non_blocking=True)
             p.grad = None
             if not self._pending_step:
                 self._pending_step = True
