@@ -89,6 +89,55 @@ def main():
         Z[idx], Nn[idx], Wt[idx] = z, nn_, w
         expect(torch.allclose(out, Wt[reqs[rank][0]], rtol=1e-3, atol=1e-4), f"sparse step {step}")
 
+    # (2b) the same kind of table through KVWorker requests (KeyedStore): FTRL, width 2, and a
+    # table with per-key lengths whose pull returns the lengths the owners hold
+    ks = kvstore.KeyedStore(ctx, 11, key_space, nk, width=2, kind="ftrl", alpha=0.1, beta=1.0,
+                            l1=1.0, l2=1.0)
+    W2 = torch.zeros(key_space, 2, device=dev)
+    Z2, N2 = torch.zeros_like(W2), torch.zeros_like(W2)
+    for step in range(2):
+        reqs = []
+        for r in range(world):
+            g = torch.Generator(device=dev)
+            g.manual_seed(7000 * step + r)
+            keys = torch.unique(torch.randint(0, key_space, (nk // 2,), device=dev, generator=g))
+            vals = torch.randn(keys.numel(), 2, generator=g, device=dev) * 0.5
+            reqs.append((keys, vals))
+        keys, vals = reqs[rank]
+        out = torch.empty_like(vals)
+        ks.wait(ks.push_pull(keys, vals.reshape(-1).contiguous(), out.view(-1)))
+        G = torch.zeros_like(W2)
+        touched = torch.zeros(key_space, dtype=torch.bool, device=dev)
+        for k, v in reqs:
+            G.index_add_(0, k, v)
+            touched[k] = True
+        idx = touched.nonzero().squeeze(1)
+        z, nn_, w = Z2[idx], N2[idx], W2[idx]
+        ftrl_update(z, nn_, w, G[idx])
+        Z2[idx], N2[idx], W2[idx] = z, nn_, w
+        expect(torch.allclose(out, W2[keys], rtol=1e-3, atol=1e-4), f"keyed store step {step}")
+    kl = kvstore.KeyedStore(ctx, 12, 1 << 16, 4000, width=3, kind="sum", var_len=True)
+    g = torch.Generator(device=dev)
+    g.manual_seed(99)      # every rank pushes the same keys: the sum is world x the values
+    keys = torch.unique(torch.randint(0, 1 << 16, (3000,), device=dev, generator=g))
+    lens = (keys % 3 + 1).int()
+    vals = torch.randn(int(lens.sum()), device=dev, generator=g)
+    kl.wait(kl.push(keys, vals, lens))
+    ask = keys[rank::2].contiguous()       # a different request on every rank
+    out = torch.zeros(ask.numel() * 3, device=dev)
+    lens_back = torch.full((ask.numel(),), -1, device=dev, dtype=torch.int32)
+    kl.wait(kl.pull(ask, out, lens_back))
+    expect(torch.equal(lens_back, (ask % 3 + 1).int()), "lengths returned by a keyed pull")
+    offs = torch.cumsum(lens.long(), 0) - lens.long()
+    pos = torch.searchsorted(keys, ask)
+    got_offs = torch.cumsum(lens_back.long(), 0) - lens_back.long()
+    good = True
+    for j in range(3):
+        m = lens[pos] > j
+        good = good and torch.allclose(out[(got_offs + j)[m]], world * vals[(offs[pos] + j)[m]],
+                                       rtol=1e-5, atol=1e-5)
+    expect(good, "values returned by a keyed pull with lengths")
+
     # (3) data-parallel training through the server-side optimizer
     torch.manual_seed(5)
     ref = nn.Sequential(nn.Linear(32, 64), nn.Tanh(), nn.Linear(64, 8)).to(dev)
