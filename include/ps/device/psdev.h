@@ -256,6 +256,10 @@ typedef struct {
   uint64_t offs_off;   /* i64[max_n+1] value offsets (computed by the scatter call)       */
   int32_t* klen;       /* owner state: stored length per slot (with lengths), or NULL     */
   uint64_t timeout_ns; /* bound of the rendezvous waits; 0 = 20 s                         */
+  int32_t state_stride; /* floats between consecutive values in w, z and n: 0 or 1 = three
+                           arrays; 4 = one array of {w, z, n, -} per value (w, z, n point at
+                           its first three floats), so that an update touches one 16-byte
+                           group instead of three sectors                                  */
 } psdev_sparse_t;
 
 /* Cut points of a sorted key list at the W+1 shard boundaries (device pointers; pos[world+1]

@@ -58,7 +58,8 @@ class Sparse(C.Structure):
                 ("hkeys_off", C.c_uint64), ("capacity", C.c_uint64), ("overflow", C.c_void_p),
                 ("width", C.c_int32), ("channel", C.c_int32), ("max_n", C.c_int64),
                 ("max_vals", C.c_int64), ("slots", C.c_int64), ("lens_off", C.c_uint64),
-                ("offs_off", C.c_uint64), ("klen", C.c_void_p), ("timeout_ns", C.c_uint64)]
+                ("offs_off", C.c_uint64), ("klen", C.c_void_p), ("timeout_ns", C.c_uint64),
+                ("state_stride", C.c_int32)]
 
 
 class PsdevError(RuntimeError):

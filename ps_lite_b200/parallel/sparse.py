@@ -67,9 +67,17 @@ class SparseTable:
         self.pos.zero_()
         dev = heap.device
         ne = slots * self.width
-        self.w = torch.zeros(ne, dtype=torch.float32, device=dev)
-        self.z = torch.zeros(ne, dtype=torch.float32, device=dev) if kind == "ftrl" else None
-        self.n = torch.zeros(ne, dtype=torch.float32, device=dev) if kind == "ftrl" else None
+        if kind == "ftrl":
+            # three numbers per value, side by side ({w, z, n, -}): an update touches one
+            # 16-byte group instead of three sectors of three arrays; w, z, n are strided views
+            self.state = torch.zeros(ne * 4, dtype=torch.float32, device=dev)
+            sv = self.state.view(ne, 4)
+            self.w, self.z, self.n = sv[:, 0], sv[:, 1], sv[:, 2]
+            self.state_stride = 4
+        else:
+            self.w = torch.zeros(ne, dtype=torch.float32, device=dev)
+            self.z = self.n = None
+            self.state_stride = 1
         self.klen = torch.zeros(slots, dtype=torch.int32, device=dev) if var_len else None
         self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
         self._world = heap.world_struct()
@@ -87,6 +95,7 @@ class SparseTable:
         t.width, t.channel = self.width, int(barrier_channel)
         t.max_n, t.max_vals, t.slots = int(max_keys), int(max_vals), int(slots)
         t.lens_off, t.offs_off = self.lens_off, self.offs_off
+        t.state_stride = self.state_stride
         t.klen = self.klen.data_ptr() if self.klen is not None else None
         from .dense import default_timeout_s
         t.timeout_ns = int(default_timeout_s() * 1e9)

@@ -54,6 +54,7 @@ struct SparseArgs {
   long long max_n, max_vals;     // capacities of the request buffers
   long long slots;               // slots of the server's store (range, or hash capacity)
   int width;
+  int sstride;                   // floats between consecutive values in w, z, nacc
   // hash store (capacity != 0): slots are found by open addressing in a key table that lives
   // in the owner's heap, so that workers can claim slots with remote compare-and-swap
   unsigned long long hkeys_off;  // heap: u64[capacity], all ones = empty
@@ -253,18 +254,19 @@ __device__ __forceinline__ float ftrl_weight(float z, float n, const SparseArgs&
 }
 
 __device__ __forceinline__ void apply_one(const SparseArgs& a, long long e, float g) {
+  const long long s = e * a.sstride;  // the value's place in the state arrays
   if (a.kind == 0) {
-    a.w[e] += g;
+    a.w[s] += g;
   } else if (a.kind == 1) {
-    a.w[e] -= a.lr * g;
+    a.w[s] -= a.lr * g;
   } else {
-    const float w = a.w[e], n = a.nacc[e];
+    const float w = a.w[s], n = a.nacc[s];
     const float n2 = n + g * g;
     const float sigma = (sqrtf(n2) - sqrtf(n)) / a.alpha;
-    const float z = a.z[e] + g - sigma * w;
-    a.z[e] = z;
-    a.nacc[e] = n2;
-    a.w[e] = ftrl_weight(z, n2, a);
+    const float z = a.z[s] + g - sigma * w;
+    a.z[s] = z;
+    a.nacc[s] = n2;
+    a.w[s] = ftrl_weight(z, n2, a);
   }
 }
 
@@ -382,7 +384,7 @@ __global__ void sparse_respond_kernel(const __grid_constant__ SparseArgs a) {
         }
 #endif
         const long long idx = state_index(a, a.rank, k, false);
-        out[off + j] = idx >= 0 ? a.w[idx * a.width + j] : 0.f;
+        out[off + j] = idx >= 0 ? a.w[(idx * a.width + j) * a.sstride] : 0.f;
       }
     }
   }
@@ -414,6 +416,7 @@ static int fill(SparseArgs* a, const psdev_world_t* w, const psdev_sparse_t* t, 
   a->pos_off = t->pos_off; a->acc_off = t->acc_off;
   a->lens_off = t->lens_off; a->offs_off = t->offs_off;
   a->w = t->w; a->z = t->z; a->nacc = t->n; a->klen = t->klen;
+  a->sstride = t->state_stride > 1 ? t->state_stride : 1;
   a->n = n; a->kind = t->kind;
   a->max_n = t->max_n; a->max_vals = t->max_vals; a->slots = t->slots; a->width = t->width;
   a->lr = t->lr; a->alpha = t->alpha; a->beta = t->beta; a->l1 = t->l1; a->l2 = t->l2;

@@ -311,11 +311,13 @@ int SparseApply(const psdev_world_t* w, const psdev_sparse_t* t, int sync) {
         ValueSpan(w, t, r, i, &off, &len);
         if (len > 0) t->klen[idx] = len;
       }
+      const int64_t stride = t->state_stride > 1 ? t->state_stride : 1;
       for (int j = 0; j < t->width; ++j) {
-        const int64_t el = idx * t->width + j;
-        const float g = acc[el];
+        const int64_t ea = idx * t->width + j;
+        const float g = acc[ea];
         if (g == 0.f) continue;  // applied for another worker already, or nothing pushed
-        acc[el] = 0.f;
+        acc[ea] = 0.f;
+        const int64_t el = ea * stride;  // the value's place in the state arrays
         if (t->kind == 0) {
           t->w[el] += g;
         } else if (t->kind == 1) {
@@ -345,6 +347,7 @@ int SparseRespond(const psdev_world_t* w, const psdev_sparse_t* t, int sync) {
   const int W = w->world, R = w->rank;
   psdev_ctrl_t* my = CtrlOf(w->peer_base[R]);
   const bool healthy = !sync || __atomic_load_n(&my->status[t->channel], __ATOMIC_RELAXED) == 0;
+  const int64_t stride = t->state_stride > 1 ? t->state_stride : 1;
   if (healthy) {
     for (int rr = 0; rr < W; ++rr) {
       const int r = (R + rr) % W;
@@ -360,7 +363,7 @@ int SparseRespond(const psdev_world_t* w, const psdev_sparse_t* t, int sync) {
         if (off < 0 || off + len > t->max_vals) continue;
         const int64_t idx = static_cast<int64_t>(keys[i] - static_cast<uint64_t>(R) * t->range);
         for (int j = 0; j < len; ++j)
-          out[off + j] = (idx >= 0 && idx < t->slots) ? t->w[idx * t->width + j] : 0.f;
+          out[off + j] = (idx >= 0 && idx < t->slots) ? t->w[(idx * t->width + j) * stride] : 0.f;
       }
     }
   }

@@ -827,8 +827,10 @@ void Plane::Stop() {
     for (auto& kv : m.sparse) {
       psdev_sparse_t& t = kv.second->table;
       m.rt.free_(t.w);
-      if (t.z) m.rt.free_(t.z);
-      if (t.n) m.rt.free_(t.n);
+      if (t.state_stride <= 1) {  // (interleaved: z and n are inside the block that w begins)
+        if (t.z) m.rt.free_(t.z);
+        if (t.n) m.rt.free_(t.n);
+      }
       if (t.overflow) m.rt.free_(t.overflow);
     }
     m.sparse.clear();
@@ -1138,13 +1140,17 @@ const SparseInfo& Plane::DeclareSparse(int app_id, uint64_t key_space, int64_t m
   CHECK_EQ(m.rt.memset_async(pos, 0, 8 * static_cast<size_t>(W + 2), m.s_compute), 0);
   CHECK_EQ(m.rt.stream_sync(m.s_compute), 0);
   void* p = nullptr;
-  CHECK_EQ(m.rt.malloc_(&p, acc_bytes), 0);
-  t.w = static_cast<float*>(p);
   if (kind == 2) {
+    // FTRL keeps three numbers per value; they sit side by side ({w, z, n, -}), so that an
+    // update reads and writes one 16-byte group instead of three sectors of three arrays
+    CHECK_EQ(m.rt.malloc_(&p, 4 * acc_bytes), 0);
+    t.w = static_cast<float*>(p);
+    t.z = t.w + 1;
+    t.n = t.w + 2;
+    t.state_stride = 4;
+  } else {
     CHECK_EQ(m.rt.malloc_(&p, acc_bytes), 0);
-    t.z = static_cast<float*>(p);
-    CHECK_EQ(m.rt.malloc_(&p, acc_bytes), 0);
-    t.n = static_cast<float*>(p);
+    t.w = static_cast<float*>(p);
   }
   sp->keys = Local(static_cast<int64_t>(t.keys_off));
   sp->vals = Local(static_cast<int64_t>(t.grads_off));

@@ -254,6 +254,39 @@ int main(int argc, char** argv) {
       for (int j = 0; j < hlens[i]; ++j, ++o) CHECK_EQ(back[o], 2 * tri * (j + 1)) << "key " << i;
   }
 
+  // 8. keyed table with the FTRL-proximal handle (three numbers per value, kept side by side):
+  // every worker pushes gradient 1 for the same keys; from zero state the summed gradient W gives
+  // z = W, n = W^2 and w = -(z - l1) / ((beta + sqrt(n)) / alpha + l2).
+  {
+    const int kApp = 5, width = 2;
+    const int64_t nk = 1000;
+    const uint64_t key_space = 1u << 16;
+    const float alpha = 0.1f, beta = 1.f, l1 = 0.5f, l2 = 0.1f;
+    plane->DeclareSparse(kApp, key_space, nk, width, /*ftrl*/ 2, 0.f, alpha, beta, l1, l2);
+    KVWorker<float> skv(kApp, 3);
+    std::vector<Key> hkeys(nk);
+    for (int64_t i = 0; i < nk; ++i) hkeys[i] = static_cast<Key>(i) * (key_space / nk) + 1;
+    std::vector<float> hvals(nk * width, 1.f);
+    const int64_t koff = plane->Alloc(nk * 8), voff = plane->Alloc(nk * width * 4),
+                  ooff = plane->Alloc(nk * width * 4);
+    CHECK(koff >= 0 && voff >= 0 && ooff >= 0);
+    Key* dkeys = static_cast<Key*>(plane->Local(koff));
+    float* dvals = static_cast<float*>(plane->Local(voff));
+    float* dout = static_cast<float*>(plane->Local(ooff));
+    plane->Memcpy(dkeys, hkeys.data(), nk * 8);
+    plane->Memcpy(dvals, hvals.data(), nk * width * 4);
+    SArray<Key> sk = SArray<Key>::FromDevice(dkeys, nk);
+    SArray<float> sv = SArray<float>::FromDevice(dvals, nk * width);
+    SArray<float> so = SArray<float>::FromDevice(dout, nk * width);
+    skv.Wait(skv.ZPushPull(sk, sv, &so));
+    std::vector<float> back(nk * width);
+    plane->Memcpy(back.data(), dout, nk * width * 4);
+    const float g = static_cast<float>(W);
+    const float want = -(g - l1) / ((beta + std::sqrt(g * g)) / alpha + l2);
+    for (size_t i = 0; i < back.size(); ++i)
+      CHECK_LT(std::fabs(back[i] - want), 1e-6f) << "at " << i << ": " << back[i] << " vs " << want;
+  }
+
   CHECK_GT(plane->launches(), (uint64_t)0);
   LOG(INFO) << "DEVICE_PLANE_OK rank " << R << " of " << W << " backend " << plane->backend();
   plane->Stop();
