@@ -45,9 +45,23 @@ def main():
         keys = torch.sort(torch.randperm(key_space, device=dev)[:n]).values
         grads = torch.randn(n, device=dev) * 0.1
         t.stage(keys, grads)
-        out["scatter_us"] = timed(t.scatter, args.iters)
-        out["apply_us"] = timed(t.apply, args.iters)
-        out["respond_us"] = timed(t.respond, args.iters)
+        # whole steps (an apply without a scatter before it finds nothing to do); the phases are
+        # timed inside the steps
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.iters)]
+        for _ in range(2):
+            t.scatter(), t.apply(), t.respond()
+        torch.cuda.synchronize()
+        for e in ev:
+            e[0].record()
+            t.scatter()
+            e[1].record()
+            t.apply()
+            e[2].record()
+            t.respond()
+            e[3].record()
+        torch.cuda.synchronize()
+        for j, name in enumerate(("scatter_us", "apply_us", "respond_us")):
+            out[name] = round(sum(e[j].elapsed_time(e[j + 1]) for e in ev) / len(ev) * 1e3, 1)
         out["keys"] = n
         t.check()
     elif args.case == "filters":

@@ -202,7 +202,8 @@ __device__ __forceinline__ void value_span(const SparseArgs& a, int r, long long
 }
 
 // K1 + K3: cut points, then scatter-add this worker's gradients into the owners' accumulators.
-__global__ void sparse_scatter_kernel(const __grid_constant__ SparseArgs a) {
+__global__ void __launch_bounds__(256, 8)
+    sparse_scatter_kernel(const __grid_constant__ SparseArgs a) {
   const unsigned long long* keys =
       reinterpret_cast<const unsigned long long*>(heap(a, a.rank) + a.keys_off);
   if (blockIdx.x == 0 && threadIdx.x <= a.world)
@@ -272,7 +273,8 @@ __device__ __forceinline__ void apply_one(const SparseArgs& a, long long e, floa
 
 // Server: after every rank's scatter has completed, apply the handle to every key that any
 // worker pushed.
-__global__ void sparse_apply_kernel(const __grid_constant__ SparseArgs a) {
+__global__ void __launch_bounds__(256, 8)
+    sparse_apply_kernel(const __grid_constant__ SparseArgs a) {
   __shared__ unsigned long long s_epoch;
   __shared__ int s_err;
   unsigned long long e = 1;
@@ -347,7 +349,8 @@ __global__ void sparse_lens_kernel(const __grid_constant__ SparseArgs a) {
 
 // Server: write the value of every requested key into the requester's output array, then wait
 // until every server has done so.
-__global__ void sparse_respond_kernel(const __grid_constant__ SparseArgs a) {
+__global__ void __launch_bounds__(256, 8)
+    sparse_respond_kernel(const __grid_constant__ SparseArgs a) {
   __shared__ int s_last;
   Ctrl* my = ctrl_of(a.base[a.rank]);
   const bool healthy = !a.sync || *(volatile int*)&my->status[a.channel] == 0;
@@ -400,6 +403,19 @@ __global__ void sparse_respond_kernel(const __grid_constant__ SparseArgs a) {
 using namespace psdev;
 
 extern "C" {
+
+// Grid of the keyed kernels: every SM runs its full 2048 threads (8 CTAs of 256, at most 32
+// registers each).  Measured with 592, 1184 and 2368 CTAs the kernels take the same time within
+// 2 %: they are bound by the rate of random 64-byte DRAM accesses (accumulator and state group
+// of every key), not by occupancy.  PSB200_SPARSE_CTAS overrides.
+static int default_ctas() {
+  static const int n = [] {
+    const char* e = getenv("PSB200_SPARSE_CTAS");
+    const int v = e ? atoi(e) : 0;
+    return v > 0 ? v : 148 * 8;
+  }();
+  return n;
+}
 
 static int fill(SparseArgs* a, const psdev_world_t* w, const psdev_sparse_t* t, int64_t n) {
   if (!w || !t || w->world < 1 || w->world > PSDEV_MAX_RANKS || t->range == 0) return PSDEV_ERR_ARG;
@@ -481,7 +497,7 @@ int psdev_sparse_scatter(const psdev_world_t* w, const psdev_sparse_t* t, int64_
     g_launches.fetch_add(1, std::memory_order_relaxed);
   }
   // (an empty request still publishes its cut points: the servers read them)
-  sparse_scatter_kernel<<<num_ctas > 0 ? num_ctas : 592, 256, 0, s>>>(a);
+  sparse_scatter_kernel<<<num_ctas > 0 ? num_ctas : default_ctas(), 256, 0, s>>>(a);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return (int)cudaGetLastError();
 }
@@ -494,7 +510,7 @@ int psdev_sparse_apply(const psdev_world_t* w, const psdev_sparse_t* t, int num_
   int rc = fill(&a, w, t, 0);
   if (rc) return rc;
   a.sync = sync ? 1 : 0;
-  sparse_apply_kernel<<<num_ctas > 0 ? num_ctas : 592, 256, 0, (cudaStream_t)stream>>>(a);
+  sparse_apply_kernel<<<num_ctas > 0 ? num_ctas : default_ctas(), 256, 0, (cudaStream_t)stream>>>(a);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return (int)cudaGetLastError();
 }
@@ -508,7 +524,7 @@ int psdev_sparse_respond(const psdev_world_t* w, const psdev_sparse_t* t, int nu
   int rc = fill(&a, w, t, 0);
   if (rc) return rc;
   a.sync = sync ? 1 : 0;
-  sparse_respond_kernel<<<num_ctas > 0 ? num_ctas : 592, 256, 0, (cudaStream_t)stream>>>(a);
+  sparse_respond_kernel<<<num_ctas > 0 ? num_ctas : default_ctas(), 256, 0, (cudaStream_t)stream>>>(a);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return (int)cudaGetLastError();
 }
