@@ -510,7 +510,8 @@ int psdev_sparse_apply(const psdev_world_t* w, const psdev_sparse_t* t, int num_
   int rc = fill(&a, w, t, 0);
   if (rc) return rc;
   a.sync = sync ? 1 : 0;
-  sparse_apply_kernel<<<num_ctas > 0 ? num_ctas : default_ctas(), 256, 0, (cudaStream_t)stream>>>(a);
+  const int ctas = num_ctas > 0 ? num_ctas : default_ctas();
+  sparse_apply_kernel<<<ctas, 256, 0, (cudaStream_t)stream>>>(a);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return (int)cudaGetLastError();
 }
@@ -524,7 +525,8 @@ int psdev_sparse_respond(const psdev_world_t* w, const psdev_sparse_t* t, int nu
   int rc = fill(&a, w, t, 0);
   if (rc) return rc;
   a.sync = sync ? 1 : 0;
-  sparse_respond_kernel<<<num_ctas > 0 ? num_ctas : default_ctas(), 256, 0, (cudaStream_t)stream>>>(a);
+  const int ctas = num_ctas > 0 ? num_ctas : default_ctas();
+  sparse_respond_kernel<<<ctas, 256, 0, (cudaStream_t)stream>>>(a);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return (int)cudaGetLastError();
 }
