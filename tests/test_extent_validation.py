@@ -67,3 +67,17 @@ def test_sparse_descriptor_is_checked_against_the_arena():
     if not torch.cuda.is_available():            # with a GPU the good call would really launch
         rc_good = lib.psdev_sparse_scatter(C.byref(w), C.byref(good), max_keys, 1, None)
         assert rc_good != -8 and rc_good != -1
+
+
+def test_multicast_size_rule():
+    """Which path a dense launch takes, by ranks and bytes (the measured cross-overs)."""
+    lib = _lib.device_lib()
+    mib = 1 << 20
+    assert lib.psdev_multicast_pays(1, mib) == 0                # nobody to reach
+    assert lib.psdev_multicast_pays(4, 1 * mib) == 1
+    assert lib.psdev_multicast_pays(4, 4 * mib) == 1
+    assert lib.psdev_multicast_pays(4, 16 * mib) == 0           # peer path from 16 MiB on 4 ranks
+    assert lib.psdev_multicast_pays(2, 64 * mib) == 0
+    assert lib.psdev_multicast_pays(8, 256 * mib) == 1
+    assert lib.psdev_multicast_pays(8, 512 * mib) == 1
+    assert lib.psdev_multicast_pays(8, 1024 * mib) == 0         # very large: peer path again
