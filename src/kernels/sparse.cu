@@ -404,15 +404,16 @@ using namespace psdev;
 
 extern "C" {
 
-// Grid of the keyed kernels: every SM runs its full 2048 threads (8 CTAs of 256, at most 32
-// registers each).  Measured with 592, 1184 and 2368 CTAs the kernels take the same time within
-// 2 %: they are bound by the rate of random 64-byte DRAM accesses (accumulator and state group
-// of every key), not by occupancy.  PSB200_SPARSE_CTAS overrides.
+// Grid of the keyed kernels: 4 CTAs of 256 threads per SM.  On one GPU 592, 1184 and 2368 CTAs
+// take the same time within 2 % (the kernels are bound by the rate of random 64-byte DRAM
+// accesses, accumulator and state group of every key, not by occupancy); across GPUs more CTAs
+// cost more, because every CTA ends the rendezvous with a system-scope fence (2 GPUs: 0.279 ms
+// per step with 592 CTAs, 0.311 with 1184).  PSB200_SPARSE_CTAS overrides.
 static int default_ctas() {
   static const int n = [] {
     const char* e = getenv("PSB200_SPARSE_CTAS");
     const int v = e ? atoi(e) : 0;
-    return v > 0 ? v : 148 * 8;
+    return v > 0 ? v : 148 * 4;
   }();
   return n;
 }
