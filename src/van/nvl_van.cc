@@ -832,6 +832,7 @@ void Plane::Stop() {
         if (t.n) m.rt.free_(t.n);
       }
       if (t.overflow) m.rt.free_(t.overflow);
+      if (t.klen) m.rt.free_(t.klen);
     }
     m.sparse.clear();
     m.last_done.clear();
