@@ -70,16 +70,14 @@ bool Customer::WaitRequestFor(int timestamp, int timeout_ms) {
 }
 
 void Customer::FailRequest(int timestamp, const std::string& why) {
-  {
-    std::lock_guard<std::mutex> lk(tracker_mu_);
-    failed_[timestamp] = why;
-    if (failed_.size() > kTrackerWindow) failed_.erase(failed_.begin());
-    if (timestamp >= tracker_base_) {
-      auto& e = tracker_[timestamp - tracker_base_];
-      e.second = e.first;
-    }
+  std::lock_guard<std::mutex> lk(tracker_mu_);
+  failed_[timestamp] = why;
+  if (failed_.size() > kTrackerWindow) failed_.erase(failed_.begin());
+  if (timestamp >= tracker_base_) {
+    auto& e = tracker_[timestamp - tracker_base_];
+    e.second = e.first;
   }
-  tracker_cond_.notify_all();
+  tracker_cond_.notify_all();  // under the lock: see AddResponse
 }
 
 int Customer::NumResponse(int timestamp) {
@@ -90,15 +88,16 @@ int Customer::NumResponse(int timestamp) {
 }
 
 void Customer::AddResponse(int timestamp, int num) {
-  {
-    std::lock_guard<std::mutex> lk(tracker_mu_);
-    if (timestamp >= tracker_base_) tracker_[timestamp - tracker_base_].second += num;
-    // forget completed requests beyond the window of recent ones
-    while (tracker_.size() > kTrackerWindow && tracker_.front().first <= tracker_.front().second) {
-      tracker_.pop_front();
-      ++tracker_base_;
-    }
+  std::lock_guard<std::mutex> lk(tracker_mu_);
+  if (timestamp >= tracker_base_) tracker_[timestamp - tracker_base_].second += num;
+  // forget completed requests beyond the window of recent ones
+  while (tracker_.size() > kTrackerWindow && tracker_.front().first <= tracker_.front().second) {
+    tracker_.pop_front();
+    ++tracker_base_;
   }
+  // Notified under the lock.  The caller may be a thread that the customer does not own (the
+  // device plane's completion thread): the thread released from Wait may destroy the customer
+  // at once, and then must not find this thread still inside the condition variable.
   tracker_cond_.notify_all();
 }
 

@@ -18,7 +18,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.skipif(os.environ.get("PS_RUN_SANITIZERS") != "1",
                                 reason="set PS_RUN_SANITIZERS=1 to run the sanitizer builds")
 PROGRAMS = ["unit_core", "loop_kv", "shm_frames", "kv_config1", "kv_features", "multi_customer",
-            "recovery", "checkpoint"]
+            "recovery", "checkpoint", "device_plane"]
 MARKS = {"thread": "WARNING: ThreadSanitizer", "address": "ERROR: AddressSanitizer",
          "undefined": "runtime error:"}
 
@@ -44,7 +44,7 @@ def san(request):
         os.remove(lib)
     subprocess.check_call(["ar", "cr", lib, *objs])
     procs = [subprocess.Popen(["g++", *flags, os.path.join(ROOT, "tests", "cpp", p + ".cc"), lib,
-                               "-o", os.path.join(out, p)]) for p in PROGRAMS]
+                               "-ldl", "-o", os.path.join(out, p)]) for p in PROGRAMS]
     assert all(p.wait() == 0 for p in procs)
     return kind, out
 
@@ -63,7 +63,19 @@ def test_single_process_programs(san, prog, token):
     assert r.returncode == 0 and token in r.stdout + r.stderr
 
 
+def test_device_plane_on_the_cpu_stand_in(san):
+    """The device plane (arenas in shared memory, host loops for the kernels): handle exchange,
+    KVWorker routing, staged requests, completion thread, timeout path, keyed tables."""
+    kind, out = san
+    env = dict(os.environ, DMLC_PS_VAN_TYPE="loop")
+    r = subprocess.run([os.path.join(out, "device_plane")], capture_output=True, text=True,
+                       timeout=600, env=env)
+    _clean(kind, r.stdout + r.stderr)
+    assert r.returncode == 0 and "DEVICE_PLANE_OK rank 0 of 1" in r.stderr, r.stderr[-3000:]
+
+
 @pytest.mark.parametrize("prog,args,env,layout,token,count", [
+    ("device_plane", [], {"DMLC_LOCAL": "1"}, dict(num_joint=2), "DEVICE_PLANE_OK", 2),
     ("kv_config1", [], {}, dict(num_workers=2, num_servers=2), "CONFIG1_OK", 2),
     ("kv_config1", [], {"DMLC_LOCAL": "1"}, dict(num_workers=2, num_servers=2), "CONFIG1_OK", 2),
     ("kv_config1", [], {"DMLC_PS_VAN_TYPE": "p3"}, dict(num_workers=2, num_servers=2),
