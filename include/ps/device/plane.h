@@ -179,6 +179,10 @@ class Plane : public DeviceRoute {
 
   // Kernels launched through the plane (for reports).
   uint64_t launches() const;
+  // Returns when every request handed to the plane so far has completed (its callback has run
+  // and its customer has been credited).  Call before destroying a KVWorker whose requests were
+  // not all waited for.
+  void Drain();
 
   struct Impl;
 

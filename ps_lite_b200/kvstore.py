@@ -114,6 +114,8 @@ class Context:
 
     def close(self) -> None:
         L = host.lib()
+        # requests that nobody waited for finish before their workers go away
+        host._ck(L.psnvl_drain())
         for ks in getattr(self, "_keyed", []):
             ks.close()
         if self.worker:
@@ -395,5 +397,7 @@ class KeyedStore:
 
     def close(self) -> None:
         if self.worker:
+            host._ck(host.lib().psnvl_drain())
             host.lib().ps_capi_bworker_delete(self.worker)
             self.worker = None
+            self._alive.clear()

@@ -134,6 +134,12 @@ int psnvl_clear_status(int app_id, uint64_t tensor_id) {
   });
 }
 uint64_t psnvl_launches(void) { return Plane::Get()->launches(); }
+int psnvl_drain(void) {
+  return Guard([&] {
+    Plane::Get()->Drain();
+    return 0;
+  });
+}
 
 // ---- byte worker ----
 void* ps_capi_bworker_new(int app_id, int customer_id) {

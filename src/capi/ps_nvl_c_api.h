@@ -51,6 +51,8 @@ int psnvl_set_slice_bytes(uint64_t bytes);
 /* After a failed request on a tensor: clears the error word of its channel. */
 int psnvl_clear_status(int app_id, uint64_t tensor_id);
 uint64_t psnvl_launches(void);
+/* Returns when every request handed to the plane so far has completed. */
+int psnvl_drain(void);
 
 /* ---- KVWorker over raw bytes ---- */
 void* ps_capi_bworker_new(int app_id, int customer_id);

@@ -611,6 +611,9 @@ const psdev_world_t& Plane::world_struct() const { return impl_->ws; }
 const PlaneOptions& Plane::options() const { return impl_->opts; }
 const std::string& Plane::backend() const { return impl_->backend_name; }
 uint64_t Plane::launches() const { return impl_->rt.launch_count ? impl_->rt.launch_count() : 0; }
+void Plane::Drain() {
+  if (impl_->started) impl_->Drain();
+}
 void Plane::SetStream(void* stream) {
   tls_stream = stream;
   tls_has_stream = true;  // a null handle is a stream too: the legacy default stream
