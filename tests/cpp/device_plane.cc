@@ -102,6 +102,19 @@ int main(int argc, char** argv) {
     CHECK_LT(std::fabs(souts[i] - expect[i]), 1e-4f) << "at " << i;
   }
 
+  // 2b. a request that nobody waits for, by a worker that goes away: Plane::Drain returns when
+  // the request has completed (callback run, tracker credited); the worker may then be deleted
+  {
+    KVWorker<float> brief(0, 7);
+    std::atomic<int> fired{0};
+    brief.ZPush(skeys, svals, slens, 0, [&fired]() { ++fired; });
+    plane->Drain();
+    CHECK_EQ(fired.load(), 1);
+  }
+  for (int64_t i = 0; i < n; ++i) expect[i] -= 0.5f * sum_of(i);
+  kv.Wait(kv.Pull(keys, &got));
+  for (int64_t i = 0; i < n; ++i) CHECK_LT(std::fabs(got[i] - expect[i]), 1e-4f) << "at " << i;
+
   // 3. a subset of the keys touches only those shards' values
   if (W > 1) {
     const int j = W - 1;
