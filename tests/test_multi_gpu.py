@@ -1,8 +1,9 @@
 """Launches the multi-process GPU checks when the box has at least two GPUs.
 
 The checks are ordinary parameter-server jobs: one scheduler plus N joint processes (one per
-GPU) started by this package's local launcher; arena handles, barriers and verdicts travel over
-the control plane.  A log of each run is kept under ``gpurun_out/`` when that folder exists."""
+GPU) started by this package's local launcher; arena handles, barriers and the ranks' results
+travel over the control plane.  With ``PSB200_TEST_LOGS=<folder>`` the output of each job is kept
+there."""
 import os
 import sys
 
@@ -21,8 +22,8 @@ def _job(script, nproc, timeout=240, extra_env=None, log=None):
     job.start()
     rc = job.wait(timeout)
     out = job.output()
-    keep = os.path.join(ROOT, "gpurun_out")
-    if log and os.path.isdir(keep):
+    keep = os.environ.get("PSB200_TEST_LOGS", "")
+    if log and keep and os.path.isdir(keep):
         with open(os.path.join(keep, log), "w") as fh:
             fh.write(out)
     return rc, out
