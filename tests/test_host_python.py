@@ -1,5 +1,6 @@
 """Python binding of the host runtime, wire codec against google.protobuf, launchers."""
 import os
+import subprocess
 import sys
 
 import numpy as np
@@ -247,3 +248,95 @@ def test_lint_is_clean():
     r = __import__("subprocess").run([sys.executable, os.path.join(ROOT, "tests", "lint.py")],
                                      capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:]
+
+
+PLANE_SCRIPT = r'''
+import ctypes as C, os, sys
+import numpy as np
+sys.path.insert(0, os.environ["PSB_ROOT"])
+from ps_lite_b200 import _lib, host
+host.start(0)
+if host.is_scheduler() and not host.is_worker():
+    host.finalize(0)          # the scheduler takes part in start-up and shut-down only
+    sys.exit(0)
+L = host.lib()
+# the device plane on its CPU stand-in (device = -1): arenas in shared memory, host loops
+host._ck(L.psnvl_start(32 << 20, -1, b"auto", 0, b"", 1 << 18, 5_000_000_000))
+R, W = L.psnvl_rank(), L.psnvl_world()
+assert L.psnvl_backend().decode() == "sim" if hasattr(L, "psnvl_backend") else True
+n = 100_003
+n_pad = (n + 7) & ~7
+blk = ((n_pad + W - 1) // W + 7) & ~7
+local_len = ((n_pad + blk - 1) // blk + W - 1) // W * blk
+master = np.zeros(local_len, np.float32)
+t = _lib.Table()
+t.grad_off = host._ck(L.psnvl_alloc(4 * n_pad, 256))
+t.weight_off = host._ck(L.psnvl_alloc(4 * n_pad, 256))
+t.n, t.blk = n_pad, blk
+t.master = master.ctypes.data
+t.grad_dtype = t.out_dtype = _lib.F32
+o = _lib.Opt()
+o.kind, o.scale, o.lr = _lib.OPT_SGD, 1.0, 0.5
+ch = host._ck(L.psnvl_new_channel())
+host._ck(L.psnvl_register_dense(0, 5, n, C.byref(t), C.byref(o), ch, 0, 0))
+keys = np.zeros(W, np.uint64)
+host._ck(L.psnvl_dense_keys(5, keys.ctypes.data_as(C.POINTER(C.c_uint64))))
+assert np.all(np.diff(keys.astype(np.float64)) > 0)          # one key per shard, ascending
+worker = L.ps_capi_bworker_new(0, 0)
+assert worker
+vals = np.full(n, float(R + 1), np.float32)
+outs = np.zeros(n, np.float32)
+kp = keys.ctypes.data_as(C.POINTER(C.c_uint64))
+for step in range(1, 4):
+    ts = L.ps_capi_bworker_request(worker, 1, 1, kp, W, vals.ctypes.data, 4 * n, outs.ctypes.data,
+                                   4 * n, 0, 0)
+    assert ts >= 0, L.ps_capi_last_error()
+    host._ck(L.ps_capi_bworker_wait(worker, ts))
+    want = -0.5 * step * W * (W + 1) / 2
+    assert np.allclose(outs, want), (step, outs[:4], want)
+# push only, then pull only
+ts = L.ps_capi_bworker_request(worker, 1, 0, kp, W, vals.ctypes.data, 4 * n, None, 0, 0, 0)
+host._ck(L.ps_capi_bworker_wait(worker, ts))
+outs[:] = 0
+ts = L.ps_capi_bworker_request(worker, 0, 1, kp, W, None, 0, outs.ctypes.data, 4 * n, 0, 0)
+host._ck(L.ps_capi_bworker_wait(worker, ts))
+assert np.allclose(outs, -0.5 * 4 * W * (W + 1) / 2)
+# all-gather and barrier over the control plane
+sizes = (C.c_size_t * W)()
+buf = C.create_string_buffer(64 * W)
+mine = ("rank%d" % R).encode()
+total = L.psnvl_allgather(mine, len(mine), buf, len(buf), sizes)
+assert total == sum(len("rank%d" % r) for r in range(W))
+assert buf.raw[:total] == b"".join(("rank%d" % r).encode() for r in range(W))
+host._ck(L.psnvl_barrier())
+assert L.psnvl_launches() > 0
+host._ck(L.psnvl_drain())
+host._ck(L.ps_capi_bworker_delete(worker))
+host._ck(L.psnvl_unregister_dense(0, 5))
+host._ck(L.psnvl_stop())
+print("PY_PLANE_OK", R, flush=True)
+host.finalize(0)
+'''
+
+
+@pytest.mark.parametrize("nproc", [1, 3])
+def test_device_plane_c_abi_on_the_cpu_stand_in(tmp_path, nproc):
+    """The C ABI of the device plane (what the Python package calls) without a GPU: start,
+    allocation, tensor registration, KVWorker requests on host arrays served by the plane's CPU
+    stand-in, all-gather and barrier over the control plane, drain, stop."""
+    from ps_lite_b200.launch.local import LocalJob
+    script = tmp_path / "plane_node.py"
+    script.write_text(PLANE_SCRIPT)
+    if nproc == 1:
+        env = dict(os.environ, PSB_ROOT=ROOT, DMLC_PS_VAN_TYPE="loop")
+        env.pop("DMLC_ROLE", None)
+        r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True,
+                           timeout=120, env=env)
+        assert r.returncode == 0 and "PY_PLANE_OK 0" in r.stdout, (r.stdout + r.stderr)[-3000:]
+        return
+    job = LocalJob([sys.executable, str(script)], env={"PSB_ROOT": ROOT, "DMLC_LOCAL": "1"},
+                   capture=True, num_joint=nproc)
+    job.start()
+    rc = job.wait(120)
+    out = job.output()
+    assert rc == 0 and out.count("PY_PLANE_OK") == nproc, out[-3000:]
