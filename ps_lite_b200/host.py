@@ -131,10 +131,31 @@ def setenv(key: str, value) -> None:
 _started = False
 
 
-def start(customer_id: int = 0, barrier: bool = True) -> None:
+_exit_hook = False
+
+
+def _leave_without_finalize() -> None:
+    """Interpreter exit of a process that started the runtime and never finalized it (an uncaught
+    exception, an early ``sys.exit``): stop this node's van without the closing barrier, so that
+    the process ends with its own exit status instead of blocking in the destruction of a runtime
+    whose threads still run.  The other nodes of the job are the launcher's business."""
     global _started
+    if _started:
+        _started = False
+        try:
+            lib().ps_capi_finalize(0, 0)
+        except Exception:
+            pass
+
+
+def start(customer_id: int = 0, barrier: bool = True) -> None:
+    global _started, _exit_hook
     _ck(lib().ps_capi_start(customer_id, int(barrier)))
     _started = True
+    if not _exit_hook:
+        import atexit
+        atexit.register(_leave_without_finalize)
+        _exit_hook = True
 
 
 def finalize(customer_id: int = 0, barrier: bool = True) -> None:

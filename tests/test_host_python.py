@@ -340,3 +340,17 @@ def test_device_plane_c_abi_on_the_cpu_stand_in(tmp_path, nproc):
     rc = job.wait(120)
     out = job.output()
     assert rc == 0 and out.count("PY_PLANE_OK") == nproc, out[-3000:]
+
+
+def test_exit_without_finalize_ends_with_the_programs_status():
+    """A process that started the runtime and dies of an exception leaves with status 1 at once
+    (it neither blocks in the destruction of the runtime nor aborts)."""
+    code = ("import sys; sys.path.insert(0, %r)\n"
+            "from ps_lite_b200 import host\n"
+            "host.start(0)\n"
+            "raise RuntimeError('user error after start')\n" % ROOT)
+    env = dict(os.environ, DMLC_PS_VAN_TYPE="loop")
+    env.pop("DMLC_ROLE", None)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=60,
+                       env=env)
+    assert r.returncode == 1 and "user error after start" in r.stderr, r.stderr[-2000:]
