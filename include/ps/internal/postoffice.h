@@ -100,7 +100,12 @@ class Postoffice {
 
  private:
   Postoffice();
-  ~Postoffice() { delete van_; }
+  // A process that ends without Finalize still has the van's service threads running.  Tearing
+  // the van down under them blocks or aborts, so in that case it is left to the operating
+  // system, and the process ends with the status its program chose.
+  ~Postoffice() {
+    if (van_ && !van_->IsReady()) delete van_;
+  }
   void InitEnvironment();
   void BarrierImpl(int customer_id, int node_group, bool process_wide);
 

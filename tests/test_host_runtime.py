@@ -309,3 +309,15 @@ def test_reference_multi_worker_program(core_lib):
     job._spawn("server", 1)
     job._spawn("worker", 0)
     assert job.wait(90) == 0, job.output()[-3000:]
+
+
+def test_program_that_returns_without_finalize_ends(core_lib, tmp_path):
+    """A C++ program that starts the runtime and returns from main without Finalize ends with
+    its own status: the van's threads still run, so the runtime is not torn down under them."""
+    src = tmp_path / "nofin.cc"
+    src.write_text('#include "ps/ps.h"\nint main() { ps::Start(0); return 3; }\n')
+    exe = _compile(str(src), core_lib, out_name="nofin")
+    env = dict(os.environ, DMLC_PS_VAN_TYPE="loop")
+    env.pop("DMLC_ROLE", None)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=30, env=env)
+    assert r.returncode == 3, r.stderr[-2000:]
