@@ -354,3 +354,23 @@ def test_exit_without_finalize_ends_with_the_programs_status():
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=60,
                        env=env)
     assert r.returncode == 1 and "user error after start" in r.stderr, r.stderr[-2000:]
+
+
+def test_job_ends_when_a_node_dies_of_an_exception(tmp_path):
+    """One node of a job raises after start-up: it leaves with status 1, and the launcher ends
+    the others instead of letting them wait for it."""
+    from ps_lite_b200.launch.local import LocalJob
+    script = tmp_path / "failnode.py"
+    script.write_text(
+        "import os, sys\n"
+        "sys.path.insert(0, os.environ['PSB_ROOT'])\n"
+        "from ps_lite_b200 import host\n"
+        "host.start(0)\n"
+        "if host.is_worker() and host.my_rank() == 1:\n"
+        "    raise RuntimeError('worker 1 fails after start')\n"
+        "host.finalize(0)\n")
+    job = LocalJob([sys.executable, str(script)], env={"PSB_ROOT": ROOT}, capture=True,
+                   num_joint=2, fail_fast=True)
+    job.start()
+    rc = job.wait(60)
+    assert rc == 1 and "worker 1 fails after start" in job.output(), job.output()[-2000:]
