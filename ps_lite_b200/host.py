@@ -8,6 +8,8 @@ role queries, ``barrier``, :class:`KVWorker` (``push``/``pull``/``push_pull``/``
 from __future__ import annotations
 
 import ctypes as C
+import os
+import sys
 import threading
 from typing import Callable, Optional
 
@@ -266,6 +268,17 @@ class KVWorker:
             self._h = None
 
 
+def _handle_failed(what: str) -> None:
+    """A Python handle raised on the runtime's receive thread.  The request it was serving will
+    never be answered, so the requester would wait for ever: the process reports the error and
+    ends with status 1, like a C++ handle that throws, and the launcher ends the job."""
+    import traceback
+    sys.stderr.write(f"ps_lite_b200: {what} raised; the process ends\n")
+    traceback.print_exc()
+    sys.stderr.flush()
+    os._exit(1)
+
+
 class KVServer:
     """``KVServer<float>``; ``handle(server, req)`` is a Python request handle, or None for the
     built-in accumulate handle.  A Python handle must call ``server.respond(req, ...)``."""
@@ -288,7 +301,10 @@ class KVServer:
             "lens": np.ctypeslib.as_array(req.lens, (req.nlens,)).copy() if req.nlens else np.zeros(0, np.int32),
             "_raw": Request.from_buffer_copy(req),
         }
-        self._py(self, view)
+        try:
+            self._py(self, view)
+        except BaseException:  # noqa: BLE001 - nothing above this frame can handle it
+            _handle_failed("KVServer request handle")
 
     def respond(self, req: dict, keys=None, vals=None, lens=None) -> None:
         k = _u64(keys) if keys is not None else None
@@ -315,7 +331,10 @@ class SimpleApp:
             raise PSError(lib().ps_capi_last_error().decode())
 
     def _tramp(self, head, body, n, sender, _user):
-        self._py(head, C.string_at(body, n), sender)
+        try:
+            self._py(head, C.string_at(body, n), sender)
+        except BaseException:  # noqa: BLE001
+            _handle_failed("SimpleApp request handle")
 
     def request(self, head: int, body: bytes, recver: int) -> int:
         return _ck(lib().ps_capi_simple_request(self._h, head, body, len(body), recver))

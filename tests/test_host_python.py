@@ -374,3 +374,31 @@ def test_job_ends_when_a_node_dies_of_an_exception(tmp_path):
     job.start()
     rc = job.wait(60)
     assert rc == 1 and "worker 1 fails after start" in job.output(), job.output()[-2000:]
+
+
+def test_job_ends_when_a_python_handle_raises(tmp_path):
+    """A Python request handle that raises ends its server process with status 1 (the request
+    would never be answered otherwise), and the launcher ends the job."""
+    from ps_lite_b200.launch.local import LocalJob
+    script = tmp_path / "badhandle.py"
+    script.write_text(
+        "import os, sys\n"
+        "import numpy as np\n"
+        "sys.path.insert(0, os.environ['PSB_ROOT'])\n"
+        "from ps_lite_b200 import host\n"
+        "host.start(0)\n"
+        "server = None\n"
+        "if host.is_server():\n"
+        "    def handle(srv, req):\n"
+        "        raise ValueError('handle is broken')\n"
+        "    server = host.KVServer(0, handle)\n"
+        "if host.is_worker():\n"
+        "    kv = host.KVWorker(0, 0)\n"
+        "    kv.wait(kv.push(np.array([1], np.uint64), np.ones(1, np.float32)))\n"
+        "host.finalize(0)\n")
+    job = LocalJob([sys.executable, str(script)], env={"PSB_ROOT": ROOT}, capture=True,
+                   num_workers=1, num_servers=1, fail_fast=True)
+    job.start()
+    rc = job.wait(60)
+    out = job.output()
+    assert rc != 0 and "handle is broken" in out and "request handle raised" in out, out[-2000:]
