@@ -32,6 +32,12 @@ static const char* const DataTypeName[] = {
 struct bfloat16_t { uint16_t bits; };
 struct float16_t { uint16_t bits; };
 
+// True when V without const/volatile is W (source compatibility: the reference exposes it).
+template <typename V, typename W>
+inline bool SameType() {
+  return std::is_same<typename std::remove_cv<V>::type, W>::value;
+}
+
 template <typename V>
 constexpr DataType GetDataType() {
   if (std::is_same<V, bfloat16_t>::value) return BFLOAT16;
