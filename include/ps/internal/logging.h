@@ -102,10 +102,28 @@ using Error = ::ps::Error;
 #define PS_LOG_ERROR ::ps::log::Line(::ps::log::kError, __FILE__, __LINE__)
 #define PS_LOG_FATAL ::ps::log::Line(::ps::log::kFatal, __FILE__, __LINE__)
 
+#define PS_LOG_QFATAL PS_LOG_FATAL
+#ifdef NDEBUG
+#define PS_LOG_DFATAL PS_LOG_ERROR
+#else
+#define PS_LOG_DFATAL PS_LOG_FATAL
+#endif
+
 #ifndef LOG
 #define LOG(severity) PS_LOG_##severity.stream()
 #define LOG_IF(severity, cond) \
   !(cond) ? (void)0 : ::ps::log::Voidify() & LOG(severity)
+// the other logging macros that programs written for the reference may use
+#define LG LOG(INFO)
+#define VLOG(level) LOG(INFO)
+#define LOG_EVERY_N(severity, n) LOG(severity)
+#ifdef NDEBUG
+#define DLOG(severity) LOG_IF(severity, false)
+#define DLOG_IF(severity, cond) LOG_IF(severity, false)
+#else
+#define DLOG(severity) LOG(severity)
+#define DLOG_IF(severity, cond) LOG_IF(severity, cond)
+#endif
 #define CHECK(x) \
   if (x) {    \
   } else      \
