@@ -156,8 +156,15 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--repeat", type=int, default=1,
                     help="run the job this many times, stop at the first failure (a race "
                          "shaker, like tests/repeat.sh of the reference)")
+    # accepted for command lines written for the reference's tracker/dmlc_local.py
+    ap.add_argument("--log-level", default="INFO", choices=["INFO", "DEBUG"],
+                    help="logging level of the launcher itself")
+    ap.add_argument("--log-file", default=None, help="file for the launcher's own log")
     ap.add_argument("command", nargs=argparse.REMAINDER)
     args = ap.parse_args(argv)
+    import logging
+    logging.basicConfig(level=getattr(logging, args.log_level), filename=args.log_file,
+                        format="%(asctime)s %(levelname)s %(message)s")
     if not args.command:
         ap.error("no command given")
     if not args.joint and (args.num_workers <= 0 or args.num_servers <= 0):
@@ -165,8 +172,11 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     env = dict(kv.split("=", 1) for kv in args.env)
     rc = 0
     for i in range(max(1, args.repeat)):
+        logging.info("starting %s with %d workers, %d servers, %d joint nodes",
+                     " ".join(args.command), args.num_workers, args.num_servers, args.joint)
         rc, _ = run(args.command, args.num_workers, args.num_servers, args.joint, env,
                     args.timeout, args.role_as_arg, fail_fast=not args.keep_going)
+        logging.info("job ended with exit code %d", rc)
         if rc != 0:
             if args.repeat > 1:
                 print(f"run {i + 1} of {args.repeat} failed with exit code {rc}", file=sys.stderr)

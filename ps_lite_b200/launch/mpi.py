@@ -30,13 +30,25 @@ def mpirun_commands(nworker: int, nserver: int, envs: Dict[str, str], command: S
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description="launch a parameter-server job with mpirun")
-    ap.add_argument("-n", "--num-workers", type=int, required=True)
-    ap.add_argument("-s", "--num-servers", type=int, required=True)
+    # (--nworker / --server-nodes / --log-* / --host-ip: the spellings of the reference's
+    # tracker/dmlc_mpi.py)
+    ap.add_argument("-n", "--num-workers", "--nworker", type=int, required=True)
+    ap.add_argument("-s", "--num-servers", "--server-nodes", type=int, default=0)
     ap.add_argument("-H", "--hostfile", default=None)
+    ap.add_argument("--log-level", default="INFO", choices=["INFO", "DEBUG"])
+    ap.add_argument("--log-file", default=None)
+    ap.add_argument("--host-ip", default=None,
+                    help="address of this host for the scheduler (DMLC_NODE_HOST)")
     ap.add_argument("--flavor", choices=["openmpi", "mpich"], default="openmpi")
     ap.add_argument("--dry-run", action="store_true")
     ap.add_argument("command", nargs=argparse.REMAINDER)
     args = ap.parse_args(argv)
+    import logging
+    logging.basicConfig(level=getattr(logging, args.log_level), filename=args.log_file,
+                        format="%(asctime)s %(levelname)s %(message)s")
+    if args.host_ip:
+        import os
+        os.environ["DMLC_NODE_HOST"] = args.host_ip
 
     def launch(nworker, nserver, envs):
         procs = []

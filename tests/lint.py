@@ -24,7 +24,8 @@ import sys
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CPP_DIRS = ["include", "src", "tests/cpp", "tests/cuda", "baseline"]
-PY_DIRS = ["ps_lite_b200", "benchmarks", "tests", "baseline", "bench.py", "__graft_entry__.py"]
+PY_DIRS = ["ps_lite_b200", "benchmarks", "tests", "baseline", "tracker", "bench.py",
+           "__graft_entry__.py"]
 CPP_EXT = (".h", ".cuh", ".cc", ".cu", ".inl")
 SKIP_PARTS = ("baseline/_ref", "build/", "__pycache__", "baseline/shims")
 MAX_COLS = {"cpp": 100, "py": 120}

@@ -402,3 +402,22 @@ def test_job_ends_when_a_python_handle_raises(tmp_path):
     rc = job.wait(60)
     out = job.output()
     assert rc != 0 and "handle is broken" in out and "request handle raised" in out, out[-2000:]
+
+
+def test_tracker_entry_points_of_the_reference(tmp_path):
+    """Command lines written for the reference's tracker scripts work: same place, same flags."""
+    hf = tmp_path / "hosts"
+    hf.write_text("10.0.0.1\n10.0.0.2\n")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "tracker", "dmlc_mpi.py"), "--nworker",
+                        "2", "--server-nodes", "1", "-H", str(hf), "--log-level", "DEBUG",
+                        "--dry-run", "./prog"], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "DMLC_ROLE=worker" in r.stdout and "DMLC_NUM_SERVER=1" in r.stdout
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "tracker", "dmlc_ssh.py"), "-n", "2",
+                        "-s", "1", "-H", str(hf), "--dry-run", "./prog"],
+                       capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "DMLC_ROLE=server" in r.stdout, r.stdout + r.stderr
+    log = tmp_path / "launcher.log"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "tracker", "dmlc_local.py"), "-n", "1",
+                        "-s", "1", "--log-file", str(log), sys.executable, "-c", "print('hi')"],
+                       capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "job ended with exit code 0" in log.read_text()
