@@ -30,8 +30,11 @@ class LocalJob:
                  num_joint: int = 0, env: Optional[Dict[str, str]] = None,
                  port: Optional[int] = None, role_as_arg: bool = False,
                  capture: bool = False, per_role_env: Optional[Dict[str, Dict[str, str]]] = None,
-                 fail_fast: bool = False):
+                 fail_fast: bool = False, worker_processes: Optional[int] = None):
         self.cmd = list(cmd)
+        # processes started with the worker role; fewer than num_workers when one process hosts
+        # several worker customers (the reference's tests/local_multi_workers.sh starts one)
+        self.worker_processes = worker_processes
         self.num_joint = num_joint
         self.num_workers = num_joint or num_workers
         self.num_servers = num_joint or num_servers
@@ -73,7 +76,7 @@ class LocalJob:
         else:
             for i in range(self.num_servers):
                 self._spawn("server", i)
-            for i in range(self.num_workers):
+            for i in range(self.worker_processes or self.num_workers):
                 self._spawn("worker", i)
 
     def spawn_replacement(self, role: str, index: int, extra_env=None) -> dict:
@@ -132,10 +135,10 @@ class LocalJob:
 
 def run(cmd: Sequence[str], num_workers: int = 0, num_servers: int = 0, num_joint: int = 0,
         env: Optional[Dict[str, str]] = None, timeout: float = 120.0, role_as_arg: bool = False,
-        capture: bool = False, fail_fast: bool = False):
+        capture: bool = False, fail_fast: bool = False, worker_processes: Optional[int] = None):
     """Start a job, wait for it, return (exit code, LocalJob)."""
     job = LocalJob(cmd, num_workers, num_servers, num_joint, env, role_as_arg=role_as_arg,
-                   capture=capture, fail_fast=fail_fast)
+                   capture=capture, fail_fast=fail_fast, worker_processes=worker_processes)
     job.start()
     rc = job.wait(timeout)
     return rc, job
@@ -150,6 +153,9 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     ap.add_argument("--env", action="append", default=[], help="KEY=VALUE for every process")
     ap.add_argument("--role-as-arg", action="store_true",
                     help="append the role name to the command line of each process")
+    ap.add_argument("--worker-processes", type=int, default=None,
+                    help="start this many worker processes instead of one per worker (a "
+                         "process then hosts several worker customers)")
     ap.add_argument("--timeout", type=float, default=3600.0)
     ap.add_argument("--keep-going", action="store_true",
                     help="do not stop the other processes when one exits with an error")
@@ -175,7 +181,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
         logging.info("starting %s with %d workers, %d servers, %d joint nodes",
                      " ".join(args.command), args.num_workers, args.num_servers, args.joint)
         rc, _ = run(args.command, args.num_workers, args.num_servers, args.joint, env,
-                    args.timeout, args.role_as_arg, fail_fast=not args.keep_going)
+                    args.timeout, args.role_as_arg, fail_fast=not args.keep_going,
+                    worker_processes=args.worker_processes)
         logging.info("job ended with exit code %d", rc)
         if rc != 0:
             if args.repeat > 1:

@@ -321,3 +321,28 @@ def test_program_that_returns_without_finalize_ends(core_lib, tmp_path):
     env.pop("DMLC_ROLE", None)
     r = subprocess.run([exe], capture_output=True, text=True, timeout=30, env=env)
     assert r.returncode == 3, r.stderr[-2000:]
+
+
+def test_shell_entry_points_of_the_reference(core_lib):
+    """tests/local.sh and tests/repeat.sh take the command lines of the reference's scripts of
+    the same names."""
+    exe = _prog("kv_config1", core_lib)
+    r = subprocess.run(["bash", os.path.join(ROOT, "tests", "repeat.sh"), "2", "bash",
+                        os.path.join(ROOT, "tests", "local.sh"), "2", "2", exe],
+                       capture_output=True, text=True, timeout=180)
+    out = r.stdout + r.stderr
+    assert r.returncode == 0 and out.count("CONFIG1_OK") == 4 and "run 2 of 2" in out, out[-2000:]
+    r = subprocess.run(["bash", os.path.join(ROOT, "tests", "repeat.sh"), "3", "false"],
+                       capture_output=True, text=True, timeout=30)
+    assert r.returncode == 1 and "run 1 failed" in r.stdout and "run 2 of" not in r.stdout
+
+
+@pytest.mark.skipif(not os.path.isdir(REF_TESTS), reason="reference sources not mounted")
+def test_reference_multi_workers_through_its_shell_script(core_lib):
+    """tests/local_multi_workers.sh: one worker process hosting both worker customers, role as
+    last argument, on the reference's own test program."""
+    exe = _compile(os.path.join(REF_TESTS, "test_kv_app_multi_workers.cc"), core_lib,
+                   out_name="ref_multi_workers")
+    r = subprocess.run(["bash", os.path.join(ROOT, "tests", "local_multi_workers.sh"), "2", "2",
+                        exe], capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-2000:]
