@@ -10,9 +10,11 @@
 #include <algorithm>
 #include <chrono>
 #include <condition_variable>
+#include <exception>
 #include <functional>
 #include <memory>
 #include <mutex>
+#include <thread>
 #include <unordered_map>
 #include <utility>
 #include <vector>
@@ -305,6 +307,10 @@ class KVWorker : public SimpleApp {
     cb();
   }
 
+  // requests whose slices add up to at least this many bytes are sent to their servers in
+  // parallel
+  static constexpr size_t kParallelSendBytes = 1 << 20;
+
   void Send(int timestamp, bool push, bool pull, int cmd, const KVPairs<Val>& kvs) {
     SlicedKVs sliced;
     slicer_(kvs, Postoffice::Get()->GetServerKeyRanges(), &sliced);
@@ -314,10 +320,13 @@ class KVWorker : public SimpleApp {
     obj_->AddResponse(timestamp, skipped);
     if (static_cast<size_t>(skipped) == sliced.size()) RunCallback(timestamp);
 
+    std::vector<Message> msgs;
+    size_t payload = 0;
     for (size_t i = 0; i < sliced.size(); ++i) {
       if (!sliced[i].first) continue;
       const KVPairs<Val>& part = sliced[i].second;
-      Message msg;
+      msgs.emplace_back();
+      Message& msg = msgs.back();
       msg.meta.app_id = obj_->app_id();
       msg.meta.customer_id = obj_->customer_id();
       msg.meta.request = true;
@@ -332,8 +341,35 @@ class KVWorker : public SimpleApp {
         msg.AddData(part.vals);  // empty for a pure pull: the frame is still sent
         if (part.lens.size()) msg.AddData(part.lens);
       }
-      Postoffice::Get()->van()->Send(msg);
+      for (const auto& d : msg.data) payload += d.size();
     }
+    Van* van = Postoffice::Get()->van();
+    if (msgs.size() < 2 || payload < kParallelSendBytes) {
+      for (const Message& m : msgs) van->Send(m);
+      return;
+    }
+    // Large slices for several servers leave at the same time, one thread per further server:
+    // a blocking send to one server would otherwise keep the others idle until it has been
+    // received.  (Messages to one server keep their order: a server gets one slice.)
+    std::vector<std::thread> others;
+    std::vector<std::exception_ptr> failed(msgs.size());
+    for (size_t i = 1; i < msgs.size(); ++i) {
+      others.emplace_back([van, &msgs, &failed, i]() {
+        try {
+          van->Send(msgs[i]);
+        } catch (...) {
+          failed[i] = std::current_exception();
+        }
+      });
+    }
+    try {
+      van->Send(msgs[0]);
+    } catch (...) {
+      failed[0] = std::current_exception();
+    }
+    for (auto& t : others) t.join();
+    for (auto& f : failed)
+      if (f) std::rethrow_exception(f);
   }
 
   // Handles a response from a server (or a simple-app message).
