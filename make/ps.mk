@@ -8,9 +8,7 @@
 #
 # The variable names PS_LDFLAGS_SO / PS_LDFLAGS_A and the ADD_CFLAGS convention are those of the
 # reference's make/ps.mk; there they name protobuf and ZeroMQ, which this runtime does not need.
-ifeq ($(USE_KEY32), 1)
-ADD_CFLAGS += -DUSE_KEY32=1
-endif
+ADD_CFLAGS += $(if $(filter 1,$(USE_KEY32)),-DUSE_KEY32=1)
 
 PS_PATH ?= .
 PS_CFLAGS = -std=c++17 -pthread -I$(PS_PATH)/include $(ADD_CFLAGS)
